@@ -1,0 +1,102 @@
+/*
+ * litedsa_b200 -- C ABI of the B200 (sm_100a) LiteDSA sparse-attention hot path.
+ *
+ * One shared library (liblitedsa_b200.so), plain pointers and sizes, no C++ or
+ * framework types in any signature.  Every function
+ *   - takes DEVICE pointers unless a parameter says "host",
+ *   - is asynchronous on the CUDA stream passed as `stream` (a cudaStream_t cast to
+ *     void*; NULL = the legacy default stream),
+ *   - allocates nothing on the device unless its comment says otherwise,
+ *   - never throws, traps or exits: it returns one of the LITEDSA_* codes below.
+ * Outputs are caller-owned, destination-passing, exactly as in the reference
+ * operators these entry points replace.
+ */
+#ifndef LITEDSA_B200_H_
+#define LITEDSA_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  LITEDSA_OK = 0,
+  LITEDSA_ERR_ARG = 1,         /* null pointer / inconsistent optional arguments   */
+  LITEDSA_ERR_SHAPE = 2,       /* a shape rule of the operator is violated         */
+  LITEDSA_ERR_UNSUPPORTED = 3, /* valid request this build cannot serve            */
+  LITEDSA_ERR_CUDA = 4,        /* a CUDA runtime / driver call failed              */
+  LITEDSA_ERR_TIMEOUT = 5      /* a device-side bounded wait expired (status word) */
+};
+
+/* Version of this ABI (bumped on any signature change). */
+int litedsa_abi_version(void);
+
+/* Human-readable text for a LITEDSA_* code (static storage). */
+const char* litedsa_error_string(int code);
+
+/*
+ * Per-tile union + query-major membership bitmask.
+ * Replaces the reference operator
+ *   union_qm(topk_indices, u_phys, counts, memb_qm, req_pg, block_table, block_size, seq_space)
+ * (kernels/b200/dsa/litedsa.cu:31-75, kernel kernels/b200/dsa/litedsa_union.cuh:34-184).
+ *
+ *   topk_indices [T, k]  int32, logical positions, -1 (or >= seq_space) = invalid
+ *   u_phys       [ng, cap] int32 out: ascending union, physical slots; live prefix = counts[g]
+ *   counts       [ng]    int32 out
+ *   memb_qm      [ng, G, cap/32] uint32 out: bit r of row (g, q) <=> rank r in token q's list
+ *   req_pg       [ng]    int32 request id per tile, or NULL together with block_table
+ *   block_table  [bt_rows, bt_blocks] int32 logical block -> physical block, or NULL
+ *                (identity: physical slot == logical position)
+ * Shape rules (as the reference): T == ng*G, cap == G*k, cap % 128 == 0, G <= 16,
+ * G*cap/32 <= 16384, 0 < seq_space <= 2^20 and a multiple of 1024.  Additionally
+ * k % 4 == 0.
+ * fill_tail == 0: words beyond the live prefixes are left untouched (the reference's
+ * overwrite contract, litedsa_union.cuh:22-25); != 0: u_phys tail := -1, mask tail := 0.
+ */
+int litedsa_union_qm(const int32_t* topk_indices, int32_t* u_phys, int32_t* counts,
+                     uint32_t* memb_qm, const int32_t* req_pg, const int32_t* block_table,
+                     int T, int k, int ng, int cap, int G, int bt_rows, int bt_blocks,
+                     int block_size, int64_t seq_space, int fill_tail, void* stream);
+
+/*
+ * Masked FP8 MLA prefill over the per-tile union list.
+ * Replaces the reference operator
+ *   masked_mla_fp8(q, kv, indices, sm_scale, out_scale, topk_length, memb_qm, h_per_q,
+ *                  out, max_logits, lse)
+ * (kernels/b200/dsa/litedsa.cu:77-135; kernel litedsa_attention_sm100.cuh:1832-2479),
+ * same argument order; tensor shapes/strides are passed as integers.
+ *
+ *   q8       [ng, 128, 576] e4m3; row r of a tile = token r / h_per_q, head r % h_per_q;
+ *            q_row_stride = bytes between consecutive rows (576 when dense, multiple of 16)
+ *   kv8      [s_kv, 576] e4m3, kv_row_stride bytes between rows (multiple of 16)
+ *   indices  [ng, topk] int32 physical KV slots in ascending rank order,
+ *            indices_row_stride = elements between tiles (multiple of 4)
+ *   topk_length [ng] int32 live entries per tile (NULL: topk for every tile)
+ *   memb_qm  [ng, 128/h_per_q, topk/32] uint32 membership bits (bit r <=> rank r)
+ *   out      [ng, 128, 512] bf16 = out_scale * softmax(sm_scale * q.k) @ kv8[:, :512]
+ *   max_logits [ng, 128] fp32 (natural-log units) or NULL;  lse [ng, 128] fp32
+ *   debug_dump  NULL in production (bring-up aid: raw S / O of tile 0)
+ * Rules: topk % 128 == 0; h_per_q divides 128; 128 / h_per_q <= 16; bases 16-byte aligned.
+ * A row with no valid key gets out = 0, lse = +inf, max_logits = -inf.
+ */
+int litedsa_masked_mla_fp8(const void* q8, const void* kv8, const int32_t* indices,
+                           float sm_scale, float out_scale, const int32_t* topk_length,
+                           const uint32_t* memb_qm, int h_per_q, void* out, float* max_logits,
+                           float* lse, int ng, int s_kv, int topk, int64_t q_row_stride,
+                           int64_t kv_row_stride, int64_t indices_row_stride,
+                           float* debug_dump, void* stream);
+
+/*
+ * Synchronous read (and optional reset) of the attention kernels' device status word on
+ * the current device.  out4_host[0] = first bounded wait that expired (0 = none),
+ * [1] = block, [2] = loop iteration, [3] = launches completed since the last reset.
+ * Returns LITEDSA_ERR_TIMEOUT when out4_host[0] != 0.  No counterpart in the reference,
+ * whose waits are unbounded (litedsa_attention_sm100.cuh:1965, 2371).
+ */
+int litedsa_attn_status(int* out4_host, int reset);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LITEDSA_B200_H_ */

@@ -1,0 +1,188 @@
+"""Python-facing operators of the LiteDSA sparse-attention hot path on B200.
+
+Two layers, both thin wrappers over the C ABI (include/litedsa_b200.h):
+
+* ``*_out`` functions take exactly the argument lists of the reference's TVM-FFI
+  operators (kernels/b200/dsa/litedsa_jit_binding.cu:7-17) -- destination passing,
+  caller-owned outputs, nothing allocated, asynchronous on the current stream.
+* ``union_qm`` / ``masked_mla_fp8`` are the allocate-and-return forms.
+
+Dtypes, devices and contiguity are checked here (the reference checks shapes only and
+casts pointers blindly, litedsa.cu:70-72, 111-124); shape rules are checked again in C.
+There is no CPU path: tensors must live on a CUDA device.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import check
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _need(t: torch.Tensor, name: str, dtype, ndim: Optional[int] = None) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    dts = dtype if isinstance(dtype, (tuple, list)) else (dtype,)
+    if t.dtype not in dts:
+        raise TypeError(f"{name} must have dtype {dts}, got {t.dtype}")
+    if ndim is not None and t.dim() != ndim:
+        raise ValueError(f"{name} must be {ndim}-D, got shape {tuple(t.shape)}")
+
+
+def _mask_dtype_ok(t: torch.Tensor) -> bool:
+    return t.dtype in (torch.int32, torch.uint32)
+
+
+# --------------------------------------------------------------------------- union
+def union_qm_out(topk_indices: torch.Tensor, u_phys: torch.Tensor, counts: torch.Tensor,
+                 memb_qm: torch.Tensor, req_pg: Optional[torch.Tensor],
+                 block_table: Optional[torch.Tensor], block_size: int, seq_space: int,
+                 *, fill_tail: bool = False) -> None:
+    """Reference argument order (kernels/b200/dsa/litedsa.cu:31-33).
+
+    topk_indices [T,k] i32; u_phys [ng,cap] i32; counts [ng] i32; memb_qm [ng,G,cap/32]
+    u32 bits (int32 storage accepted); req_pg [ng] i32 and block_table [nreq,nblk] i32, or
+    both None for an identity table.  Entries beyond the live prefixes are left untouched
+    unless ``fill_tail``.
+    """
+    _need(topk_indices, "topk_indices", torch.int32, 2)
+    _need(u_phys, "u_phys", torch.int32, 2)
+    _need(counts, "counts", torch.int32, 1)
+    _need(memb_qm, "memb_qm", (torch.int32, torch.uint32), 3)
+    for name, t in (("topk_indices", topk_indices), ("u_phys", u_phys), ("counts", counts),
+                    ("memb_qm", memb_qm)):
+        if not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous")
+    T, k = topk_indices.shape
+    ng, cap = u_phys.shape
+    G = memb_qm.shape[1]
+    if memb_qm.shape[0] != ng or memb_qm.shape[2] * 32 != cap:
+        raise ValueError("memb_qm must be [ng, G, cap/32]")
+    if counts.shape[0] != ng:
+        raise ValueError("counts must be [ng]")
+    bt_rows = bt_blocks = 0
+    if (req_pg is None) != (block_table is None):
+        raise ValueError("req_pg and block_table must be given together")
+    if block_table is not None:
+        _need(req_pg, "req_pg", torch.int32, 1)
+        _need(block_table, "block_table", torch.int32, 2)
+        if not (req_pg.is_contiguous() and block_table.is_contiguous()):
+            raise ValueError("req_pg / block_table must be contiguous")
+        if req_pg.shape[0] != ng:
+            raise ValueError("req_pg must be [ng]")
+        bt_rows, bt_blocks = block_table.shape
+    with torch.cuda.device(topk_indices.device):
+        rc = _lib.lib().litedsa_union_qm(
+            _ptr(topk_indices), _ptr(u_phys), _ptr(counts), _ptr(memb_qm), _ptr(req_pg),
+            _ptr(block_table), T, k, ng, cap, G, bt_rows, bt_blocks, int(block_size),
+            int(seq_space), 1 if fill_tail else 0, _stream(topk_indices))
+    check(rc, "union_qm")
+
+
+def union_qm(topk_idx: torch.Tensor, tokens_per_tile: int, *, seq_space: Optional[int] = None,
+             return_counts: bool = False):
+    """Deduplicated per-tile KV index list + query-major membership bitmask.
+
+    topk_idx [T,k] int32 (-1 = padding).  Returns ``(union_idx [ng, G*k] int32, mask
+    [ng, G, G*k/32] int32 holding u32 bit words)`` and, with ``return_counts``, also
+    ``counts [ng] int32``.  union_idx is ascending with -1 beyond each tile's count; mask
+    words beyond it are zero.  ``seq_space`` bounds valid positions (default: 2^20, the
+    operator's maximum).
+    """
+    _need(topk_idx, "topk_idx", torch.int32, 2)
+    T, k = topk_idx.shape
+    G = int(tokens_per_tile)
+    if G <= 0 or T % G != 0:
+        raise ValueError("number of tokens must be a multiple of tokens_per_tile")
+    ng, cap = T // G, G * k
+    dev = topk_idx.device
+    u = torch.empty((ng, cap), dtype=torch.int32, device=dev)
+    cnt = torch.empty((ng,), dtype=torch.int32, device=dev)
+    mask = torch.empty((ng, G, cap // 32), dtype=torch.int32, device=dev)
+    space = 1 << 20 if seq_space is None else ((int(seq_space) + 1023) // 1024) * 1024
+    union_qm_out(topk_idx.contiguous(), u, cnt, mask, None, None, 1, space, fill_tail=True)
+    return (u, mask, cnt) if return_counts else (u, mask)
+
+
+# --------------------------------------------------------------------------- FP8 attention
+def masked_mla_fp8_out(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, sm_scale: float,
+                       out_scale: float, topk_length: Optional[torch.Tensor],
+                       memb_qm: torch.Tensor, h_per_q: int, out: torch.Tensor,
+                       max_logits: Optional[torch.Tensor], lse: torch.Tensor,
+                       *, _debug_dump: Optional[torch.Tensor] = None) -> None:
+    """Reference argument order (kernels/b200/dsa/litedsa.cu:77-80).
+
+    q [ng,128,576] e4m3 (uint8 storage accepted); kv [s_kv,1,576] or [s_kv,576] e4m3, row
+    pitch = kv.stride(0); indices [ng,1,topk] or [ng,topk] i32 physical slots; topk_length
+    [ng] i32 (None: every tile uses topk); memb_qm [ng,G,topk/32] u32 bits; out
+    [ng,128,512] bf16; max_logits [ng,128] f32 or None; lse [ng,128] f32.
+    logits = sm_scale * (q . k); out = out_scale * softmax(logits) @ kv[:, :512].
+    """
+    f8 = (torch.float8_e4m3fn, torch.uint8)
+    _need(q, "q", f8, 3)
+    _need(kv, "kv", f8)
+    _need(indices, "indices", torch.int32)
+    _need(memb_qm, "memb_qm", (torch.int32, torch.uint32))
+    _need(out, "out", torch.bfloat16, 3)
+    _need(lse, "lse", torch.float32)
+    if kv.dim() == 3:
+        if kv.shape[1] != 1:
+            raise ValueError("kv must be [s_kv, 1, 576]")
+        kv = kv[:, 0]
+    if indices.dim() == 3:
+        if indices.shape[1] != 1:
+            raise ValueError("indices must be [ng, 1, topk]")
+        indices = indices[:, 0]
+    ng, rows, d = q.shape
+    if rows != 128 or d != 576 or kv.shape[1] != 576:
+        raise ValueError("q must be [ng,128,576] and kv [s_kv,(1,)576]")
+    if q.stride(2) != 1 or q.stride(1) * 128 != q.stride(0) or kv.stride(1) != 1 or indices.stride(1) != 1:
+        raise ValueError("q rows must be evenly pitched; q/kv/indices need unit inner stride")
+    topk = indices.shape[1]
+    G = 128 // int(h_per_q)
+    if indices.shape[0] != ng:
+        raise ValueError("indices rows must match q rows")
+    if memb_qm.numel() != ng * G * (topk // 32) or not memb_qm.is_contiguous():
+        raise ValueError("memb_qm must be a contiguous [ng, G, topk/32]")
+    if tuple(out.shape) != (ng, 128, 512) or not out.is_contiguous():
+        raise ValueError("out must be a contiguous [ng,128,512]")
+    if lse.numel() != ng * 128 or not lse.is_contiguous():
+        raise ValueError("lse must be a contiguous [ng,128]")
+    if topk_length is not None:
+        _need(topk_length, "topk_length", torch.int32, 1)
+        if topk_length.shape[0] != ng or not topk_length.is_contiguous():
+            raise ValueError("topk_length must be a contiguous [ng]")
+    if max_logits is not None:
+        _need(max_logits, "max_logits", torch.float32)
+        if max_logits.numel() != ng * 128 or not max_logits.is_contiguous():
+            raise ValueError("max_logits must be a contiguous [ng,128]")
+    with torch.cuda.device(q.device):
+        rc = _lib.lib().litedsa_masked_mla_fp8(
+            _ptr(q), _ptr(kv), _ptr(indices), float(sm_scale), float(out_scale),
+            _ptr(topk_length), _ptr(memb_qm), int(h_per_q), _ptr(out), _ptr(max_logits),
+            _ptr(lse), ng, kv.shape[0], topk, q.stride(1), kv.stride(0), indices.stride(0),
+            _ptr(_debug_dump), _stream(q))
+    check(rc, "masked_mla_fp8")
+
+
+def attn_status(reset: bool = False, device=None) -> Tuple[int, int, int, int]:
+    """Synchronise and read the attention kernels' device status word:
+    (first expired wait site or 0, block, iteration, launches completed)."""
+    import ctypes
+    buf = (ctypes.c_int * 4)()
+    with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
+        torch.cuda.synchronize()
+        _lib.lib().litedsa_attn_status(buf, 1 if reset else 0)
+    return tuple(int(x) for x in buf)

@@ -1,0 +1,45 @@
+// Host-side construction of TMA tensor maps without linking libcuda: the encoder is
+// looked up through the runtime (cudaGetDriverEntryPoint).  The reference builds the
+// same kind of 2-D byte-typed maps over its KV cache with cuTensorMapEncodeTiled
+// (kernels/b200/dsa/litedsa_attention_sm100.cuh:2538-2573).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace lt {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) !=
+            cudaSuccess || qr != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// 2-D row-major tensor [rows, cols] of `elem_bytes`-wide elements, row pitch in bytes,
+// box = box_cols x box_rows, 128-byte swizzle, out-of-bounds elements read as zero.
+inline bool make_map_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dtype,
+                        uint64_t cols, uint64_t rows, uint64_t pitch_bytes, uint32_t box_cols,
+                        uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  cuuint64_t size[2] = {cols, rows};
+  cuuint64_t stride[1] = {pitch_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, dtype, 2, const_cast<void*>(base), size, stride, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace lt
