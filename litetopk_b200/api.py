@@ -32,11 +32,11 @@ def _stream(t: torch.Tensor) -> int:
 def _need(t: torch.Tensor, name: str, dtype, ndim: Optional[int] = None) -> None:
     if not isinstance(t, torch.Tensor):
         raise TypeError(f"{name} must be a torch.Tensor")
-    if not t.is_cuda:
-        raise ValueError(f"{name} must be a CUDA tensor (there is no CPU path)")
     dts = dtype if isinstance(dtype, (tuple, list)) else (dtype,)
     if t.dtype not in dts:
         raise TypeError(f"{name} must have dtype {dts}, got {t.dtype}")
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (there is no CPU path)")
     if ndim is not None and t.dim() != ndim:
         raise ValueError(f"{name} must be {ndim}-D, got shape {tuple(t.shape)}")
 
