@@ -25,10 +25,13 @@
 //   * no TMA multicast of any kind; the pair is signalled with two plain commits.
 #include "common.cuh"
 #include "tensor_map.cuh"
+#include <cstdlib>
 
 namespace lt {
 
-constexpr int kAttnThreads = 192;
+constexpr int kSoftmaxWarps = 8, kProducerWarps = 8;
+constexpr int kWarpMma = 16, kWarpCopy = 17, kWarpRelay = 18, kWarpValid = 19;
+constexpr int kAttnThreads = 640;
 constexpr int kBlockKeys = 128;                      // keys per softmax block (whole pair)
 constexpr int kDQK = 576, kDV = 512;
 constexpr int kChunks = 5;                           // 128-byte column chunks per row
@@ -43,7 +46,7 @@ constexpr uint32_t kOffK = kOffQ + kQBytes;
 constexpr uint32_t kOffV = kOffK + 2 * kKStage;
 constexpr uint32_t kOffP = kOffV + 2 * kVStage;
 constexpr uint32_t kOffMisc = kOffP + 2 * kPBytes;   // 204800
-constexpr uint32_t kMiscBytes = 2048;
+constexpr uint32_t kMiscBytes = 3072;
 constexpr uint32_t kAttnSmem = kOffMisc + kMiscBytes + 1024;  // + alignment slack
 static_assert(kAttnSmem <= 232448, "shared-memory plan exceeds the 227 KB per-CTA limit");
 
@@ -59,13 +62,15 @@ constexpr float kMInit = -1e30f;
 constexpr float kRescaleThreshold = 6.0f;
 
 struct Misc {
-  uint64_t q_full, k_full[2], v_full[2], qk_done[2], pv_done[2], s_free[2], p_ready[2],
-      valid_ready[2], valid_free[2];
-  unsigned long long valid[2][2];   // 128 validity bits per stage
+  // in the leader CTA only: q_full (both CTAs' Q tiles), k_peer / v_peer (peer's K / V landed),
+  // s_free / p_ready (softmax warps of both CTAs)
+  uint64_t q_full, k_peer[2], v_peer[2], s_free[2], p_ready[2];
+  // in every CTA
+  uint64_t k_land[2], v_land[2], k_copied[2], qk_done[2], pv_done[2], valid_ready[2], valid_free[2];
+  uint32_t valid[2][4];             // 128 validity bits per stage
   uint32_t tmem_base;
   uint32_t pad;
-  float maxbuf[2][128];
-  float libuf[128];
+  float xbuf[2][256];               // row-max exchange (double-buffered); row-sum exchange at the end
 };
 static_assert(sizeof(Misc) <= kMiscBytes, "Misc too large");
 
@@ -80,14 +85,23 @@ struct AttnParams {
   int ng, s_kv, cap, h_per_q, G;
   long long idx_stride;
   float scale_log2, out_scale;
+  int exp_flags;             // experiment switches (0 in production)
 };
 
 // wait sites reported in the status word
-enum { kSiteQ = 1, kSiteKFull, kSiteVFull, kSiteQkDone, kSitePvDone, kSiteSFree, kSitePReady,
-       kSiteValidReady, kSiteValidFree, kSiteKFree, kSiteVFree, kSitePFree, kSiteEpi };
+enum { kSiteQ = 1, kSiteKLand, kSiteKPeer, kSiteVLand, kSiteVPeer, kSiteQkDone, kSitePvDone,
+       kSiteSFree, kSitePReady, kSiteValidReady, kSiteValidFree, kSiteKFree, kSiteKCopied,
+       kSiteVFree, kSitePFree, kSiteEpi, kSiteRelayK, kSiteRelayV, kSiteSmemAlign };
 
 // status[0] first failing wait site, [1] block, [2] iteration, [3] launches completed
 __device__ int g_attn_status[4];
+
+// bring-up aid: cycle stamps of one tile's roles (role 0 softmax thread 0, 1 producer warp 0,
+// 2 MMA thread, 3 copy thread, 4 relay thread), 8 slots per block, written after the S/O dump
+#define LT_TS(role, k, slot)                                                              \
+  do {                                                                                    \
+    if (kDebug && ts_on && (k) < 64) ts[(((role) * 64 + (k)) << 3) + (slot)] = clock64(); \
+  } while (0)
 
 template <bool kDebug>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kAttnThreads, 1)
@@ -106,18 +120,27 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
   int count = p.counts ? p.counts[tile] : p.cap;
   count = min(max(count, 0), p.cap);
   const int nb = max((count + kBlockKeys - 1) / kBlockKeys, 1);
+  long long* ts = nullptr;
+  bool ts_on = false;
+  if (kDebug && p.dbg) {
+    ts = reinterpret_cast<long long*>(p.dbg + (size_t)p.cap * 128 + 128 * 512 + 256);
+    ts_on = (tile == p.ng / 2) && cta == 0 && lane == 0;
+  }
 
   if (threadIdx.x == 0) {
     mbar_init(&ms.q_full, 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&ms.k_full[i], 1);
-      mbar_init(&ms.v_full[i], 1);
+      mbar_init(&ms.k_peer[i], 1);
+      mbar_init(&ms.v_peer[i], 1);
+      mbar_init(&ms.s_free[i], 2 * kSoftmaxWarps);
+      mbar_init(&ms.p_ready[i], 2 * kSoftmaxWarps);
+      mbar_init(&ms.k_land[i], 1);
+      mbar_init(&ms.v_land[i], 1);
+      mbar_init(&ms.k_copied[i], 2);
       mbar_init(&ms.qk_done[i], 1);
       mbar_init(&ms.pv_done[i], 1);
-      mbar_init(&ms.s_free[i], 8);       // 4 softmax warps x 2 CTAs
-      mbar_init(&ms.p_ready[i], 8);
       mbar_init(&ms.valid_ready[i], 1);
-      mbar_init(&ms.valid_free[i], 4);
+      mbar_init(&ms.valid_free[i], kSoftmaxWarps);
     }
     fence_mbar_init();
     tma_prefetch_desc(&map_q);
@@ -125,7 +148,7 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
   }
   __syncthreads();
   cluster_sync_all();
-  if (warp == 5) {
+  if (warp == kWarpMma) {
     tmem_alloc_pair(&ms.tmem_base, kTmemCols);
     tmem_relinquish_pair();
   }
@@ -133,66 +156,69 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = ms.tmem_base;
+  const uint32_t peer = cta ^ 1u;
 
-  // leader-CTA addresses of the barriers both CTAs signal
-  const uint32_t a_q_full = mapa(smem_u32(&ms.q_full), 0);
-  const uint32_t a_k_full[2] = {mapa(smem_u32(&ms.k_full[0]), 0), mapa(smem_u32(&ms.k_full[1]), 0)};
-  const uint32_t a_v_full[2] = {mapa(smem_u32(&ms.v_full[0]), 0), mapa(smem_u32(&ms.v_full[1]), 0)};
-  const uint32_t a_s_free[2] = {mapa(smem_u32(&ms.s_free[0]), 0), mapa(smem_u32(&ms.s_free[1]), 0)};
-  const uint32_t a_p_ready[2] = {mapa(smem_u32(&ms.p_ready[0]), 0), mapa(smem_u32(&ms.p_ready[1]), 0)};
-
-  if (warp < 4) {
+  if (warp < kSoftmaxWarps) {
     // ------------------------------------------------------------ softmax + epilogue
-    const int t = threadIdx.x;
-    const int r = t & 63, h = t >> 6;             // tile-local row of this CTA, key / dim half
+    // TMEM lane tl = 32*(warp%4)+lane holds tile row r = tl%64 and key/dim half h = tl/64;
+    // the two warps sharing a lane quarter split that half's 64 columns (ch = warp/4).
+    const int t = threadIdx.x;                    // 0..255
+    const int tl = ((warp & 3) << 5) | lane;
+    const int r = tl & 63, h = tl >> 6, ch = warp >> 2;
+    const int part = 2 * h + ch;                  // which 32-key quarter of the block
     const int row = (int)cta * 64 + r;            // row of the 128-row tile
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const int capw = p.cap >> 5;
-    const uint32_t* mrow = p.memb + ((size_t)tile * p.G + row / p.h_per_q) * capw + 2 * h;
-    uint2 mk = __ldg(reinterpret_cast<const uint2*>(mrow));
+    const uint32_t* mrow = p.memb + ((size_t)tile * p.G + row / p.h_per_q) * capw + part;
+    uint32_t mk = __ldg(mrow);
     const float c = p.scale_log2;
     float m = kMInit, li = 0.f, real_m = -INFINITY;
+    const uint32_t a_s_free[2] = {mapa(smem_u32(&ms.s_free[0]), 0), mapa(smem_u32(&ms.s_free[1]), 0)};
+    const uint32_t a_p_ready[2] = {mapa(smem_u32(&ms.p_ready[0]), 0), mapa(smem_u32(&ms.p_ready[1]), 0)};
+    const int xi = part * 64 + r;                 // slot in the exchange buffer
 
     for (int k = 0; k < nb; ++k) {
       const int s = k & 1;
       const uint32_t ph = (k >> 1) & 1;
-      uint2 mk_next = mk;
-      if (k + 1 < nb) mk_next = __ldg(reinterpret_cast<const uint2*>(mrow + (size_t)(k + 1) * 4));
+      uint32_t mk_next = mk;
+      if (k + 1 < nb) mk_next = __ldg(mrow + (size_t)(k + 1) * 4);
 
+      if (warp == 0) LT_TS(0, k, 0);
       mbar_wait(&ms.qk_done[s], ph, status, kSiteQkDone, k);
+      if (warp == 0) LT_TS(0, k, 1);
       tc_fence_after();
-      float sv[64];
-      const uint32_t scol = tmem + lane_base + (s ? kTmemS1 : kTmemS0);
-      tmem_ld32(scol, sv);
-      tmem_ld32(scol + 32, sv + 32);
+      float sv[32];
+      tmem_ld32(tmem + lane_base + (s ? kTmemS1 : kTmemS0) + 32 * ch, sv);
       tmem_wait_ld();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(a_s_free[s]);
 
       if (kDebug && p.dbg && tile == 0) {
-        float* d = p.dbg + ((size_t)k * 128 + row) * 128 + 64 * h;
+        float* d = p.dbg + ((size_t)k * 128 + row) * 128 + 32 * part;
 #pragma unroll
-        for (int j = 0; j < 64; ++j) d[j] = sv[j];
+        for (int j = 0; j < 32; ++j) d[j] = sv[j];
       }
 
       mbar_wait(&ms.valid_ready[s], ph, status, kSiteValidReady, k);
-      const unsigned long long vbits = ms.valid[s][h];
+      const uint32_t bits = ms.valid[s][part] & mk;
       __syncwarp();
       if (lane == 0) mbar_arrive(&ms.valid_free[s]);
-      const unsigned long long bits = vbits & ((unsigned long long)mk.x | ((unsigned long long)mk.y << 32));
       mk = mk_next;
+      if (warp == 0) LT_TS(0, k, 2);
 
       float cur = -INFINITY;
 #pragma unroll
-      for (int j = 0; j < 64; ++j) {
-        sv[j] = ((bits >> j) & 1ull) ? sv[j] : -INFINITY;
+      for (int j = 0; j < 32; ++j) {
+        sv[j] = ((bits >> j) & 1u) ? sv[j] : -INFINITY;
         cur = fmaxf(cur, sv[j]);
       }
       cur *= c;
-      ms.maxbuf[k & 1][t] = cur;
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      cur = fmaxf(cur, ms.maxbuf[k & 1][t ^ 64]);
+      float* xb = ms.xbuf[k & 1];
+      xb[xi] = cur;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      cur = fmaxf(fmaxf(xb[r], xb[64 + r]), fmaxf(xb[128 + r], xb[192 + r]));
+      if (warp == 0) LT_TS(0, k, 3);
       real_m = fmaxf(real_m, cur);
       const bool rescale = __any_sync(0xffffffffu, cur - m > kRescaleThreshold);
       float new_m = m, scale_old = 1.f;
@@ -204,9 +230,9 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
       li *= scale_old;
 
       const float nm = -new_m + kPScaleLog2;
-      uint32_t pk[16];
+      uint32_t pk[8];
 #pragma unroll
-      for (int j = 0; j < 64; j += 4) {
+      for (int j = 0; j < 32; j += 4) {
         float2 d0, d1;
         d0.x = fast_exp2(fmaf(sv[j], c, nm));
         d0.y = fast_exp2(fmaf(sv[j + 1], c, nm));
@@ -218,13 +244,13 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         const uint32_t hi = __nv_cvt_float2_to_fp8x2(d1, __NV_SATFINITE, __NV_E4M3);
         pk[j >> 2] = lo | (hi << 16);
       }
+      if (warp == 0) LT_TS(0, k, 4);
       // P buffer s was last read by PV(k-2)
       if (k >= 2) mbar_wait(&ms.pv_done[s], ph ^ 1, status, kSitePFree, k);
-      uint8_t* pdst = sm + kOffP + s * kPBytes + (4 * h) * 1024 + r * 16;
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-        *reinterpret_cast<uint4*>(pdst + i * 1024) =
-            make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+      if (warp == 0) LT_TS(0, k, 5);
+      uint8_t* pdst = sm + kOffP + s * kPBytes + (2 * part) * 1024 + r * 16;
+      *reinterpret_cast<uint4*>(pdst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      *reinterpret_cast<uint4*>(pdst + 1024) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
 
       if (rescale && k > 0) {
         // O still holds blocks [0, k): needs PV(k-1) complete
@@ -232,8 +258,8 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         tc_fence_after();
         float o[32];
 #pragma unroll 1
-        for (int cc = 0; cc < 8; ++cc) {
-          const uint32_t ocol = tmem + lane_base + kTmemO + cc * 32;
+        for (int cc = 0; cc < 4; ++cc) {
+          const uint32_t ocol = tmem + lane_base + kTmemO + ch * 128 + cc * 32;
           tmem_ld32(ocol, o);
           tmem_wait_ld();
 #pragma unroll
@@ -243,18 +269,21 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         tmem_wait_st();
         tc_fence_before();
       }
+      if (warp == 0) LT_TS(0, k, 6);
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(a_p_ready[s]);
+      if (warp == 0) LT_TS(0, k, 7);
     }
 
     // epilogue
+    float* xb = ms.xbuf[nb & 1];
+    xb[xi] = li;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    li = (xb[r] + xb[64 + r]) + (xb[128 + r] + xb[192 + r]);
     if (real_m == -INFINITY) { li = 0.f; m = -INFINITY; }
-    ms.libuf[t] = li;
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    li += ms.libuf[t ^ 64];
     const size_t grow = (size_t)tile * 128 + row;
-    if (h == 0) {
+    if (part == 0) {
       float l = __logf(li) - kPScaleLn + m * kLn2;
       if (!(li > 0.f)) l = INFINITY;
       p.lse[grow] = l;
@@ -264,14 +293,14 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
     tc_fence_after();
     const bool empty = !(li > 0.f);
     const float oscale = empty ? 0.f : __fdividef(p.out_scale, li);
-    __nv_bfloat16* orow = p.out + grow * kDV + 256 * h;
+    __nv_bfloat16* orow = p.out + grow * kDV + 256 * h + 128 * ch;
     float o[32];
 #pragma unroll 1
-    for (int cc = 0; cc < 8; ++cc) {
-      tmem_ld32(tmem + lane_base + kTmemO + cc * 32, o);
+    for (int cc = 0; cc < 4; ++cc) {
+      tmem_ld32(tmem + lane_base + kTmemO + ch * 128 + cc * 32, o);
       tmem_wait_ld();
       if (kDebug && p.dbg && tile == 0) {
-        float* d = p.dbg + (size_t)p.cap * 128 + (size_t)row * 512 + 256 * h + cc * 32;
+        float* d = p.dbg + (size_t)p.cap * 128 + (size_t)row * 512 + 256 * h + 128 * ch + cc * 32;
 #pragma unroll
         for (int j = 0; j < 32; ++j) d[j] = o[j];
       }
@@ -287,74 +316,77 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
       for (int j = 0; j < 4; ++j) dst[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
     }
-    if (kDebug && p.dbg && tile == 0 && h == 0) {
+    if (kDebug && p.dbg && tile == 0 && part == 0) {
       float* d = p.dbg + (size_t)p.cap * 128 + 128 * 512;
       d[row] = m;
       d[128 + row] = li;
     }
     tc_fence_before();
-  } else if (warp == 4) {
-    // ------------------------------------------------------------ TMA producer
+  } else if (warp < kSoftmaxWarps + kProducerWarps) {
+    // ------------------------------------------------------------ TMA producers (K rows, Q tile)
+    // warp pw gathers row quads pw and pw+8 of this CTA's 64 keys, all five column chunks
     if (lane == 0) {
-      if (cta == 0) mbar_arrive_expect_tx(&ms.q_full, 2 * kQBytes);
-      for (int j = 0; j < kChunks; ++j)
-        tma_load_2d_pair(sbase + kOffQ + j * kChunkBytes, &map_q, 128 * j, tile * 128 + (int)cta * 64,
-                         a_q_full);
-    }
-    const int32_t* idx_row = p.indices + (size_t)tile * p.idx_stride;
-    int4 cur = __ldg(reinterpret_cast<const int4*>(idx_row) + lane);
-    for (int k = 0; k < nb; ++k) {
-      const int s = k & 1;
-      const uint32_t ph = (k >> 1) & 1;
-      int4 nxt = cur;
-      if (k + 1 < nb) nxt = __ldg(reinterpret_cast<const int4*>(idx_row + (size_t)(k + 1) * kBlockKeys) + lane);
-
-      // validity of the 4 keys this lane handles: index in range and rank below the count
-      const int rank0 = k * kBlockKeys + lane * 4;
-      auto ok = [&](int idx, int rk) -> uint32_t {
-        return (idx >= 0 && idx < p.s_kv && rk < count) ? 1u : 0u;
-      };
-      const uint32_t nib = ok(cur.x, rank0) | (ok(cur.y, rank0 + 1) << 1) |
-                           (ok(cur.z, rank0 + 2) << 2) | (ok(cur.w, rank0 + 3) << 3);
-      if (k >= 2) mbar_wait(&ms.valid_free[s], ph ^ 1, status, kSiteValidFree, k);
-      const uint32_t nib_hi = __shfl_down_sync(0xffffffffu, nib, 1);
-      if ((lane & 1) == 0)
-        reinterpret_cast<uint8_t*>(&ms.valid[s][0])[lane >> 1] = (uint8_t)(nib | (nib_hi << 4));
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ms.valid_ready[s]);
-
-      // K rows of this CTA's 64 keys (all 5 chunks); stage s was last read by QK(k-2)
-      if (k >= 2) mbar_wait(&ms.qk_done[s], ph ^ 1, status, kSiteKFree, k);
-      if (cta == 0 && lane == 0) mbar_arrive_expect_tx(&ms.k_full[s], 2 * kKStage);
-      if ((uint32_t)(lane >> 4) == cta) {
-        const uint32_t dst = sbase + kOffK + s * kKStage + (uint32_t)(lane & 15) * 4 * 128;
-#pragma unroll
+      const int pw = warp - kSoftmaxWarps;
+      if (pw == 0) {
+        if (cta == 0) mbar_arrive_expect_tx(&ms.q_full, 2 * kQBytes);
+        const uint32_t a_q_full = mapa(smem_u32(&ms.q_full), 0);
         for (int j = 0; j < kChunks; ++j)
-          tma_gather4_pair(dst + j * kChunkBytes, &map_kv, 128 * j, cur, a_k_full[s]);
+          tma_load_2d_pair(sbase + kOffQ + j * kChunkBytes, &map_q, 128 * j,
+                           tile * 128 + (int)cta * 64, a_q_full);
       }
-      // V: this CTA's 256 dims of all 128 keys; stage s was last read by PV(k-2)
-      if (k >= 2) mbar_wait(&ms.pv_done[s], ph ^ 1, status, kSiteVFree, k);
-      if (cta == 0 && lane == 0) mbar_arrive_expect_tx(&ms.v_full[s], 2 * kVStage);
-      {
-        const uint32_t dst = sbase + kOffV + s * kVStage + (uint32_t)lane * 4 * 128;
-        tma_gather4_pair(dst, &map_kv, 256 * (int)cta, cur, a_v_full[s]);
-        tma_gather4_pair(dst + kVChunk, &map_kv, 256 * (int)cta + 128, cur, a_v_full[s]);
-      }
-      cur = nxt;
-    }
-  } else if (cta == 0 && lane == 0) {
-    // ------------------------------------------------------------ MMA issue (leader CTA only)
-    constexpr uint32_t idesc_qk = umma_idesc(0, 0, false, false, 128, 128);
-    constexpr uint32_t idesc_pv = umma_idesc(0, 0, false, true, 128, 256);
-    const uint32_t a_qk_done_peer[2] = {mapa(smem_u32(&ms.qk_done[0]), 1), mapa(smem_u32(&ms.qk_done[1]), 1)};
-    const uint32_t a_pv_done_peer[2] = {mapa(smem_u32(&ms.pv_done[0]), 1), mapa(smem_u32(&ms.pv_done[1]), 1)};
-    mbar_wait(&ms.q_full, 0, status, kSiteQ, 0);
-    for (int k = 0; k <= nb; ++k) {
-      if (k < nb) {
+      const int32_t* idx_row = p.indices + (size_t)tile * p.idx_stride + 64 * cta + 4 * pw;
+      int4 c0 = __ldg(reinterpret_cast<const int4*>(idx_row));
+      int4 c1 = __ldg(reinterpret_cast<const int4*>(idx_row + 32));
+      for (int k = 0; k < nb; ++k) {
         const int s = k & 1;
         const uint32_t ph = (k >> 1) & 1;
-        mbar_wait(&ms.k_full[s], ph, status, kSiteKFull, k);
+        int4 n0 = c0, n1 = c1;
+        if (k + 1 < nb) {
+          n0 = __ldg(reinterpret_cast<const int4*>(idx_row + (size_t)(k + 1) * kBlockKeys));
+          n1 = __ldg(reinterpret_cast<const int4*>(idx_row + (size_t)(k + 1) * kBlockKeys + 32));
+        }
+        if (pw == 0) LT_TS(1, k, 0);
+        if (k >= 2) {
+          // stage s held block k-2: QK(k-2) must have read it and its V copies must be out
+          mbar_wait(&ms.qk_done[s], ph ^ 1, status, kSiteKFree, k);
+          mbar_wait(&ms.k_copied[s], ph ^ 1, status, kSiteKCopied, k);
+        }
+        if (pw == 0) LT_TS(1, k, 1);
+        if ((p.exp_flags & 1) && k >= 2) {
+          if (pw == 0) mbar_arrive(&ms.k_land[s]);
+          c0 = n0; c1 = n1;
+          continue;
+        }
+        if (pw == 0) mbar_arrive_expect_tx(&ms.k_land[s], kKStage);
+        const uint32_t bar = smem_u32(&ms.k_land[s]);
+        const uint32_t dst = sbase + kOffK + s * kKStage + (uint32_t)pw * 512;
+#pragma unroll
+        for (int j = 0; j < kChunks; ++j) {
+          tma_gather4(dst + j * kChunkBytes, &map_kv, 128 * j, c0, bar);
+          tma_gather4(dst + j * kChunkBytes + 4096, &map_kv, 128 * j, c1, bar);
+        }
+        if (pw == 0) LT_TS(1, k, 2);
+        c0 = n0; c1 = n1;
+      }
+    }
+  } else if (warp == kWarpMma) {
+    // ------------------------------------------------------------ MMA issue (leader CTA only)
+    if (cta == 0 && lane == 0) {
+      constexpr uint32_t idesc_qk = umma_idesc(0, 0, false, false, 128, 128);
+      constexpr uint32_t idesc_pv = umma_idesc(0, 0, false, true, 128, 256);
+      const uint32_t a_qk_done_peer[2] = {mapa(smem_u32(&ms.qk_done[0]), 1), mapa(smem_u32(&ms.qk_done[1]), 1)};
+      const uint32_t a_pv_done_peer[2] = {mapa(smem_u32(&ms.pv_done[0]), 1), mapa(smem_u32(&ms.pv_done[1]), 1)};
+      mbar_wait(&ms.q_full, 0, status, kSiteQ, 0);
+      // S = Q K^T of block k into S buffer k%2 (needs K stage k%2 on both CTAs, buffer drained)
+      auto issue_qk = [&](int k) {
+        const int s = k & 1;
+        const uint32_t ph = (k >> 1) & 1;
+        LT_TS(2, k, 0);
+        mbar_wait(&ms.k_land[s], ph, status, kSiteKLand, k);
+        mbar_wait(&ms.k_peer[s], ph, status, kSiteKPeer, k);
+        LT_TS(2, k, 1);
         if (k >= 2) mbar_wait(&ms.s_free[s], ph ^ 1, status, kSiteSFree, k);
+        LT_TS(2, k, 2);
         tc_fence_after();
         const uint32_t d = tmem + (s ? kTmemS1 : kTmemS0);
         const uint32_t qb = sbase + kOffQ, kb = sbase + kOffK + s * kKStage;
@@ -370,13 +402,21 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         mma_commit_pair(smem_u32(&ms.qk_done[s]));
         mma_commit_pair(a_qk_done_peer[s]);
-      }
-      if (k > 0) {
-        const int kb_ = k - 1;
+        LT_TS(2, k, 3);
+      };
+      // QK runs ahead of PV: S(k+1) is produced while the softmax warps work on block k.
+      // Issue order: QK(0), QK(1), PV(0), QK(2), PV(1), QK(3), ...
+      issue_qk(0);
+      if (nb > 1) issue_qk(1);
+      for (int kb_ = 0; kb_ < nb; ++kb_) {
         const int s = kb_ & 1;
         const uint32_t ph = (kb_ >> 1) & 1;
+        LT_TS(2, kb_, 4);
         mbar_wait(&ms.p_ready[s], ph, status, kSitePReady, kb_);
-        mbar_wait(&ms.v_full[s], ph, status, kSiteVFull, kb_);
+        LT_TS(2, kb_, 5);
+        mbar_wait(&ms.v_land[s], ph, status, kSiteVLand, kb_);
+        mbar_wait(&ms.v_peer[s], ph, status, kSiteVPeer, kb_);
+        LT_TS(2, kb_, 6);
         tc_fence_after();
         const uint32_t pb = sbase + kOffP + s * kPBytes, vb = sbase + kOffV + s * kVStage;
 #pragma unroll
@@ -390,15 +430,91 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         mma_commit_pair(smem_u32(&ms.pv_done[s]));
         mma_commit_pair(a_pv_done_peer[s]);
+        LT_TS(2, kb_, 7);
+        if (kb_ + 2 < nb) issue_qk(kb_ + 2);
       }
     }
+  } else if (warp == kWarpCopy) {
+    // ------------------------------------------------------------ V operand = copies of K chunks
+    // The value dims of a key are the first 512 bytes of the row the K gather already
+    // fetched.  Chunk pair {2d, 2d+1} of this CTA's 64 keys goes to rows [64*cta, +64) of
+    // CTA d's V stage: two copies stay local, two cross to the peer over DSMEM.
+    if (lane == 0) {
+      const uint32_t a_k_peer[2] = {mapa(smem_u32(&ms.k_peer[0]), 0), mapa(smem_u32(&ms.k_peer[1]), 0)};
+      for (int k = 0; k < nb; ++k) {
+        const int s = k & 1;
+        const uint32_t ph = (k >> 1) & 1;
+        LT_TS(3, k, 0);
+        mbar_wait(&ms.k_land[s], ph, status, kSiteRelayK, k);
+        LT_TS(3, k, 1);
+        if (cta == 1) mbar_arrive_cluster(a_k_peer[s]);
+        if (k >= 2) mbar_wait(&ms.pv_done[s], ph ^ 1, status, kSiteVFree, k);   // V stage s free
+        LT_TS(3, k, 2);
+        if ((p.exp_flags & 2) && k >= 2) {
+          mbar_arrive(&ms.v_land[s]);
+          continue;
+        }
+        mbar_arrive_expect_tx(&ms.v_land[s], kVStage);
+        const uint32_t src = sbase + kOffK + s * kKStage;
+        const uint32_t vdst = sbase + kOffV + s * kVStage + cta * (64 * 128);
+        const uint32_t vbar = smem_u32(&ms.v_land[s]);
+#pragma unroll
+        for (uint32_t d = 0; d < 2; ++d) {
+#pragma unroll
+          for (uint32_t nbk = 0; nbk < 2; ++nbk)
+            bulk_copy_s2s(mapa(vdst + nbk * kVChunk, d), src + (2 * d + nbk) * kChunkBytes,
+                          kChunkBytes, mapa(vbar, d));
+        }
+        LT_TS(3, k, 3);
+      }
+    }
+  } else if (warp == kWarpRelay) {
+    // ------------------------------------------------------------ "V landed" relay
+    if (lane == 0) {
+      const uint32_t a_v_peer[2] = {mapa(smem_u32(&ms.v_peer[0]), 0), mapa(smem_u32(&ms.v_peer[1]), 0)};
+      for (int k = 0; k < nb; ++k) {
+        const int s = k & 1;
+        const uint32_t ph = (k >> 1) & 1;
+        mbar_wait(&ms.v_land[s], ph, status, kSiteRelayV, k);
+        LT_TS(4, k, 0);
+        // all four copies INTO this CTA are done: tell both CTAs' producers (K stages are
+        // sources of those copies) and, from the peer, the MMA thread
+        mbar_arrive_cluster(mapa(smem_u32(&ms.k_copied[s]), 0));
+        mbar_arrive_cluster(mapa(smem_u32(&ms.k_copied[s]), 1));
+        if (cta == 1) mbar_arrive_cluster(a_v_peer[s]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ index-validity bits
+    const int32_t* idx_row = p.indices + (size_t)tile * p.idx_stride;
+    int4 cur = __ldg(reinterpret_cast<const int4*>(idx_row) + lane);
+    for (int k = 0; k < nb; ++k) {
+      const int s = k & 1;
+      const uint32_t ph = (k >> 1) & 1;
+      int4 nxt = cur;
+      if (k + 1 < nb) nxt = __ldg(reinterpret_cast<const int4*>(idx_row + (size_t)(k + 1) * kBlockKeys) + lane);
+      const int rank0 = k * kBlockKeys + lane * 4;
+      auto ok = [&](int idx, int rk) -> uint32_t {
+        return (idx >= 0 && idx < p.s_kv && rk < count) ? 1u : 0u;
+      };
+      const uint32_t nib = ok(cur.x, rank0) | (ok(cur.y, rank0 + 1) << 1) |
+                           (ok(cur.z, rank0 + 2) << 2) | (ok(cur.w, rank0 + 3) << 3);
+      if (k >= 2) mbar_wait(&ms.valid_free[s], ph ^ 1, status, kSiteValidFree, k);
+      const uint32_t nib_hi = __shfl_down_sync(0xffffffffu, nib, 1);
+      if ((lane & 1) == 0)
+        reinterpret_cast<uint8_t*>(&ms.valid[s][0])[lane >> 1] = (uint8_t)(nib | (nib_hi << 4));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ms.valid_ready[s]);
+      cur = nxt;
+    }
   }
+  (void)peer;
 
   // tear-down: nobody may still be reading TMEM of either CTA when it is released
   __syncthreads();
   __syncwarp();
   cluster_sync_all();
-  if (warp == 5) tmem_dealloc_pair(tmem, kTmemCols);
+  if (warp == kWarpMma) tmem_dealloc_pair(tmem, kTmemCols);
   if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&status[3], 1);
 }
 
@@ -421,6 +537,7 @@ static int launch_fp8(const void* q8, const void* kv8, const int32_t* indices, f
   p.ng = ng; p.s_kv = s_kv; p.cap = topk; p.h_per_q = h_per_q; p.G = 128 / h_per_q;
   p.idx_stride = idx_row_stride;
   p.scale_log2 = sm_scale * kLog2e; p.out_scale = out_scale;
+  { const char* e = getenv("LITEDSA_EXP"); p.exp_flags = e ? atoi(e) : 0; }
   auto kern = dbg ? masked_mla_fp8_kernel<true> : masked_mla_fp8_kernel<false>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem) !=
       cudaSuccess)

@@ -48,7 +48,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 }
 // arrive on a barrier that may live in the peer CTA (shared::cluster address)
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
                : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
@@ -60,7 +60,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(smem_u32(bar)), "r"(parity)
@@ -136,6 +136,26 @@ __device__ __forceinline__ void tma_gather4_pair(uint32_t dst_smem, const CUtens
       ".cta_group::2 [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
       ::"r"(dst_smem), "l"(map), "r"(x), "r"(rows.x), "r"(rows.y), "r"(rows.z), "r"(rows.w),
         "r"(mbar_cluster_addr)
+      : "memory");
+}
+
+// gather of 4 rows into this CTA's smem, completion on a barrier of this CTA
+__device__ __forceinline__ void tma_gather4(uint32_t dst_smem, const CUtensorMap* map, int x,
+                                            int4 rows, uint32_t mbar_smem) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+      ::"r"(dst_smem), "l"(map), "r"(x), "r"(rows.x), "r"(rows.y), "r"(rows.z), "r"(rows.w),
+        "r"(mbar_smem)
+      : "memory");
+}
+// shared -> (distributed) shared bulk copy inside the cluster; dst and mbar are shared::cluster
+// addresses of the SAME CTA, src is a shared::cta address of the issuing CTA
+__device__ __forceinline__ void bulk_copy_s2s(uint32_t dst_cluster, uint32_t src_smem,
+                                              uint32_t bytes, uint32_t mbar_cluster) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst_cluster), "r"(src_smem), "r"(bytes), "r"(mbar_cluster)
       : "memory");
 }
 
