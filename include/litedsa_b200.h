@@ -96,6 +96,26 @@ int litedsa_masked_mla_fp8(const void* q8, const void* kv8, const int32_t* indic
  */
 int litedsa_attn_status(int* out4_host, int reset);
 
+/*
+ * out_e4m3[i] = e4m3_saturating(in_bf16[i] / scale), i < n.  n % 8 == 0, 16-byte aligned
+ * pointers.  Feeds litedsa_masked_mla_fp8 from bf16 queries.  No counterpart in the
+ * reference, whose callers hand it e4m3 queries (litedsa_attention_sm100.cuh:2503).
+ */
+int litedsa_quantize_e4m3(const void* in_bf16, void* out_e4m3, int64_t n, float scale,
+                          void* stream);
+
+/*
+ * DeepSeek-V3.2 style packed cache rows (656 bytes: 512 e4m3 latent codes | 4 fp32
+ * per-128 scales | 64 bf16 rope) -> the 576-byte all-e4m3 row with one scalar scale that
+ * litedsa_masked_mla_fp8 (and the reference module, litedsa.cu:82-92) consumes.  Codes
+ * are copied, rope is re-encoded as e4m3(rope / scale).  *mismatch_flag (device int32,
+ * zeroed by the caller) is set non-zero if some per-128 scale differs from `scale`: such
+ * a cache cannot be represented without requantising and must not use this path.
+ * out_pitch = bytes between output rows (>= 576, multiple of 16).
+ */
+int litedsa_repack_kv656(const void* kv656, void* kv576, int s_kv, int64_t out_pitch,
+                         float scale, int* mismatch_flag, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -186,3 +186,106 @@ def attn_status(reset: bool = False, device=None) -> Tuple[int, int, int, int]:
         torch.cuda.synchronize()
         _lib.lib().litedsa_attn_status(buf, 1 if reset else 0)
     return tuple(int(x) for x in buf)
+
+
+# --------------------------------------------------------------------------- operand preparation
+def quantize_e4m3(x: torch.Tensor, scale: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """e4m3 codes (uint8) of ``x / scale`` for a contiguous bf16 CUDA tensor (saturating)."""
+    _need(x, "x", torch.bfloat16)
+    if not x.is_contiguous() or x.numel() % 8:
+        raise ValueError("x must be contiguous with a multiple of 8 elements")
+    if out is None:
+        out = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    else:
+        _need(out, "out", (torch.uint8, torch.float8_e4m3fn))
+        if out.numel() != x.numel() or not out.is_contiguous():
+            raise ValueError("out must be contiguous and match x")
+    with torch.cuda.device(x.device):
+        check(_lib.lib().litedsa_quantize_e4m3(_ptr(x), _ptr(out), x.numel(), float(scale),
+                                               _stream(x)), "quantize_e4m3")
+    return out
+
+
+def repack_kv656(kv_rows: torch.Tensor, scale: float, out: Optional[torch.Tensor] = None,
+                 *, check_scales: bool = True) -> torch.Tensor:
+    """Packed 656-byte cache rows -> ``[s_kv, 576]`` e4m3 codes sharing the scalar ``scale``.
+
+    Raises if some per-128 scale of the cache differs from ``scale`` (checked with one
+    device->host read unless ``check_scales`` is False)."""
+    _need(kv_rows, "kv_rows", torch.uint8, 2)
+    if kv_rows.shape[1] != 656 or not kv_rows.is_contiguous():
+        raise ValueError("kv_rows must be a contiguous [s_kv, 656] uint8 tensor")
+    s_kv = kv_rows.shape[0]
+    if out is None:
+        out = torch.empty((s_kv, 576), dtype=torch.uint8, device=kv_rows.device)
+    flag = torch.zeros((1,), dtype=torch.int32, device=kv_rows.device)
+    with torch.cuda.device(kv_rows.device):
+        check(_lib.lib().litedsa_repack_kv656(_ptr(kv_rows), _ptr(out), s_kv, out.stride(0),
+                                              float(scale), _ptr(flag), _stream(kv_rows)),
+              "repack_kv656")
+    if check_scales and int(flag.item()) != 0:
+        raise ValueError("the cache has per-128 scales different from `scale`; it cannot be "
+                         "expressed with one scalar scale (use the bf16 path)")
+    return out
+
+
+def masked_mla_fp8(q: torch.Tensor, kv_cache_fp8: torch.Tensor, union_idx: torch.Tensor,
+                   mask: torch.Tensor, sm_scale: float, *, counts: Optional[torch.Tensor] = None,
+                   kv_scale: float = 1.0, q_scale: Optional[float] = None,
+                   return_max_logits: bool = False):
+    """Masked FP8 MLA prefill over the per-tile union; returns ``(out [T,h,512] bf16, lse [T,h] f32)``.
+
+    q            [T, h, 576]; bf16 (quantised here to e4m3 with the power-of-two ``q_scale``,
+                 default: the smallest one that avoids saturation) or e4m3/uint8 codes
+                 (``q_scale`` default 1).  G = 128 // h adjacent tokens form one tile.
+    kv_cache_fp8 [s_kv, 576] e4m3/uint8 codes with the scalar ``kv_scale`` (the reference
+                 module's layout), or packed [s_kv, 656] uint8 rows whose per-128 scales all
+                 equal ``kv_scale`` (repacked here).
+    union_idx    [T/G, G*k] int32 and mask [T/G, G, G*k/32] from :func:`union_qm`;
+                 counts [T/G] int32 (default: entries before the -1 padding).
+    Numerics are the reference kernel's: logits and P in e4m3, fp32 accumulation.
+    """
+    _need(q, "q", (torch.bfloat16, torch.uint8, torch.float8_e4m3fn), 3)
+    T, h, d = q.shape
+    if d != 576 or 128 % h or 128 // h > 16:
+        raise ValueError("q must be [T, h, 576] with h dividing 128 and 128/h <= 16")
+    G = 128 // h
+    if T % G:
+        raise ValueError("token count must be a multiple of 128 // heads")
+    ng = T // G
+    if q.dtype == torch.bfloat16:
+        if q_scale is None:
+            amax = float(q.abs().amax().item())
+            q_scale = 2.0 ** max(-24, int(torch.tensor(max(amax, 1e-30) / 448.0).log2().ceil().item()))
+        q8 = quantize_e4m3(q.contiguous(), q_scale)
+    else:
+        q8 = q.contiguous()
+        q_scale = 1.0 if q_scale is None else q_scale
+    kv = kv_cache_fp8
+    if kv.dim() == 2 and kv.shape[1] == 656:
+        kv = repack_kv656(kv, kv_scale)
+    if counts is None:
+        counts = (union_idx >= 0).sum(dim=1, dtype=torch.int32)
+    out = torch.empty((ng, 128, 512), dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty((ng, 128), dtype=torch.float32, device=q.device)
+    ml = torch.empty((ng, 128), dtype=torch.float32, device=q.device) if return_max_logits else None
+    masked_mla_fp8_out(q8.view(ng, 128, 576), kv, union_idx, float(sm_scale) * q_scale * kv_scale,
+                       kv_scale, counts, mask, h, out, ml, lse)
+    res = (out.view(T, h, 512), lse.view(T, h))
+    return res + (ml.view(T, h),) if return_max_logits else res
+
+
+def sparse_prefill(q: torch.Tensor, kv_cache_fp8: torch.Tensor, topk_idx: torch.Tensor,
+                   sm_scale: float, *, kv_scale: float = 1.0, q_scale: Optional[float] = None,
+                   seq_space: Optional[int] = None):
+    """The whole hot path for one chunk of query tokens: union_qm + masked_mla_fp8.
+
+    q [T,h,576], topk_idx [T,k] int32, kv_cache_fp8 as in :func:`masked_mla_fp8` (already
+    resident on the device).  Returns ``(out [T,h,512] bf16, lse [T,h] f32)``.
+    """
+    h = q.shape[1]
+    u, m, c = union_qm(topk_idx, 128 // h,
+                       seq_space=seq_space if seq_space is not None else kv_cache_fp8.shape[0],
+                       return_counts=True)
+    return masked_mla_fp8(q, kv_cache_fp8, u, m, sm_scale, counts=c, kv_scale=kv_scale,
+                          q_scale=q_scale)

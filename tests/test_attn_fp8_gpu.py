@@ -1,0 +1,161 @@
+"""masked_mla_fp8 on the GPU against the reference-numerics oracle (and the exact oracle).
+
+Tolerances are the benchmark's: out max-abs <= 1e-2 and cosine >= 0.9999, LSE <= 1e-3,
+measured against the reference's own numerics (oracle.attention_oracle.masked_mla_refnum,
+pinned to the reference module by tests/golden/)."""
+import numpy as np
+import pytest
+import torch
+
+from litetopk_b200 import api, synth
+from oracle import attention_oracle as ao
+from oracle import union_oracle as uo
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+TOL_ABS, TOL_COS, TOL_LSE = 1e-2, 0.9999, 1e-3
+
+
+def _case(tokens, heads, topk, s_kv, overlap, seed, mutate=None):
+    w = synth.Workload("t", tokens=tokens, heads=heads, topk=topk, s_kv=s_kv, overlap=overlap)
+    idx = synth.make_topk(w, seed=seed)
+    if mutate:
+        idx = mutate(idx)
+    kv = synth.make_kv_cache(s_kv, seed=seed, mode="refcompat")
+    q = synth.make_q(tokens, heads, seed=seed, mode="refcompat")
+    return w, idx, kv, q
+
+
+def _oracle(w, idx, kv, q, counts_override=None):
+    q8, kv8, qs, ks = synth.refcompat_operands(q, kv)
+    space = (w.s_kv + 1023) // 1024 * 1024
+    u, c, m = uo.union_qm_oracle(idx.numpy(), w.group, space)
+    if counts_override is not None:
+        c = counts_override(c)
+    out, lse, ml = ao.masked_mla_refnum(
+        q8.view(torch.float8_e4m3fn).float().view(w.tiles, 128, 576),
+        kv8.view(torch.float8_e4m3fn).float(), torch.from_numpy(u), torch.from_numpy(c),
+        torch.from_numpy(m.astype(np.int64)), synth.SM_SCALE * qs * ks, ks, w.heads)
+    return (u, c, m), (out, lse, ml), (q8, kv8, qs, ks)
+
+
+def _check(out, lse, ml, ref):
+    out_r, lse_r, ml_r = ref
+    mad, cos = ao.compare(out.cpu(), out_r)
+    assert mad <= TOL_ABS and cos >= TOL_COS, (mad, cos)
+    fin = torch.isfinite(lse_r)
+    assert bool((torch.isinf(lse.cpu()) == ~fin).all())
+    assert float((lse.cpu()[fin] - lse_r[fin]).abs().max()) <= TOL_LSE
+    if ml is not None:
+        assert float((ml.cpu()[fin] - ml_r[fin]).abs().max()) <= TOL_LSE
+    assert api.attn_status()[0] == 0
+
+
+SHAPES = [  # tokens, heads, topk, s_kv, overlap
+    (256, 64, 512, 4096, (0.8, 0.8)),       # config 0 in full
+    (64, 32, 256, 4096, (0.5, 0.9)),        # 4 tokens per tile, ragged unions
+    (64, 16, 128, 2048, (0.6, 0.6)),        # 8 tokens per tile
+    (128, 8, 64, 2048, (0.3, 0.7)),         # 16 tokens per tile (maximum)
+    (8, 64, 2048, 32768, (0.75, 0.75)),     # config 1 tile shape: 20 key blocks per tile
+]
+
+
+@pytest.mark.parametrize("tokens,heads,topk,s_kv,overlap", SHAPES)
+def test_out_variant_matches_reference_numerics(tokens, heads, topk, s_kv, overlap):
+    w, idx, kv, q = _case(tokens, heads, topk, s_kv, overlap, seed=2)
+    (u, c, m), ref, (q8, kv8, qs, ks) = _oracle(w, idx, kv, q)
+    ng = w.tiles
+    out = torch.full((ng, 128, 512), float("nan"), dtype=torch.bfloat16, device=DEV)
+    lse = torch.full((ng, 128), float("nan"), dtype=torch.float32, device=DEV)
+    ml = torch.full((ng, 128), float("nan"), dtype=torch.float32, device=DEV)
+    api.attn_status(reset=True)
+    api.masked_mla_fp8_out(q8.view(ng, 128, 576).to(DEV), kv8.to(DEV).view(w.s_kv, 1, 576),
+                           torch.from_numpy(u).to(DEV).view(ng, 1, w.cap),
+                           synth.SM_SCALE * qs * ks, ks, torch.from_numpy(c).to(DEV),
+                           torch.from_numpy(m.view(np.int32)).to(DEV), heads, out, ml, lse)
+    _check(out, lse, ml, ref)
+
+
+def test_end_to_end_api_from_bf16_q_and_packed_cache():
+    # north-star call chain: union_qm -> masked_mla_fp8 on bf16 q and the 656-byte cache rows
+    w, idx, kv, q = _case(64, 64, 512, 4096, (0.8, 0.8), seed=4)
+    _, ref, (q8, kv8, qs, ks) = _oracle(w, idx, kv, q)
+    u, m = api.union_qm(idx.to(DEV), w.group, seq_space=w.s_kv)
+    api.attn_status(reset=True)
+    out, lse = api.masked_mla_fp8(q.to(DEV), kv.to(DEV), u, m, synth.SM_SCALE, kv_scale=ks, q_scale=qs)
+    _check(out.view(w.tiles, 128, 512), lse.view(w.tiles, 128), None, ref)
+    out2, lse2 = api.sparse_prefill(q.to(DEV), kv.to(DEV), idx.to(DEV), synth.SM_SCALE, kv_scale=ks)
+    assert torch.equal(out2, out) or ao.compare(out2.cpu(), out.cpu())[0] <= TOL_ABS
+    # and the semantic truth: per-token attention over each token's own top-k
+    out_e, lse_e = ao.mla_exact(q.float(), synth.dequant_kv_cache(kv), idx, synth.SM_SCALE)
+    mad, cos = ao.compare(out.cpu(), out_e)
+    assert cos >= 0.9995 and float((lse.cpu() - lse_e.float()).abs().max()) <= TOL_LSE
+
+
+def test_padding_empty_tokens_stale_tails_and_bad_indices():
+    def mutate(idx):
+        idx = idx.clone()
+        idx[0, :] = -1                     # a token with no key at all (rows of one token empty)
+        idx[2, :] = -1
+        idx[3, :] = -1                     # a whole tile empty
+        idx[5, ::3] = -1                   # ragged padding
+        return idx
+    w, idx, kv, q = _case(32, 64, 256, 2048, (0.7, 0.7), seed=6, mutate=mutate)
+    (u, c, m), ref, (q8, kv8, qs, ks) = _oracle(w, idx, kv, q)
+    ng = w.tiles
+    u_d = torch.from_numpy(u).to(DEV)
+    # stale tails: garbage beyond the live prefix must not matter
+    live = torch.arange(w.cap, device=DEV)[None, :] < torch.from_numpy(c).to(DEV)[:, None]
+    garbage = torch.randint(-5, w.s_kv + 100, u_d.shape, device=DEV, dtype=torch.int32)
+    u_d = torch.where(live, u_d, garbage)
+    out = torch.empty((ng, 128, 512), dtype=torch.bfloat16, device=DEV)
+    lse = torch.empty((ng, 128), dtype=torch.float32, device=DEV)
+    ml = torch.empty_like(lse)
+    api.attn_status(reset=True)
+    api.masked_mla_fp8_out(q8.view(ng, 128, 576).to(DEV), kv8.to(DEV), u_d, synth.SM_SCALE * qs * ks,
+                           ks, torch.from_numpy(c).to(DEV), torch.from_numpy(m.view(np.int32)).to(DEV),
+                           w.heads, out, ml, lse)
+    _check(out, lse, ml, ref)
+    o = out.cpu().view(w.tokens, w.heads, 512)
+    assert bool((o[0] == 0).all()) and bool((o[2] == 0).all()) and bool((o[3] == 0).all())
+    assert bool(torch.isinf(lse.cpu().view(w.tokens, w.heads)[0]).all())
+
+
+def test_argument_validation():
+    from litetopk_b200._lib import LiteDSAError
+    ng = 2
+    q = torch.zeros((ng, 128, 576), dtype=torch.uint8, device=DEV)
+    kv = torch.zeros((1024, 576), dtype=torch.uint8, device=DEV)
+    idx = torch.zeros((ng, 192), dtype=torch.int32, device=DEV)          # topk % 128 != 0
+    m = torch.zeros((ng, 2, 6), dtype=torch.int32, device=DEV)
+    out = torch.empty((ng, 128, 512), dtype=torch.bfloat16, device=DEV)
+    lse = torch.empty((ng, 128), dtype=torch.float32, device=DEV)
+    with pytest.raises(LiteDSAError):
+        api.masked_mla_fp8_out(q, kv, idx, 1.0, 1.0, None, m, 64, out, None, lse)
+    with pytest.raises(TypeError):
+        api.masked_mla_fp8_out(q.float(), kv, idx, 1.0, 1.0, None, m, 64, out, None, lse)
+    kv656 = synth.make_kv_cache(256, seed=1, mode="native").to(DEV)       # varying per-128 scales
+    with pytest.raises(ValueError):
+        api.repack_kv656(kv656, 2.0 ** -6)
+
+
+def test_full_size_tile_sample_linearity_in_v_scale():
+    # config 1 sized tiles (no oracle): out is linear in out_scale and idempotent across runs
+    w = synth.CONFIGS["c1"]
+    ntile = 148
+    idx = synth.make_topk(w, seed=1, device=DEV, num_tiles=ntile)
+    kv = synth.make_kv_cache(w.s_kv, seed=1, device=DEV, mode="refcompat")
+    q = synth.make_q(ntile * w.group, w.heads, seed=1, device=DEV, mode="refcompat")
+    q8, kv8, qs, ks = synth.refcompat_operands(q, kv)
+    u, m, c = api.union_qm(idx, w.group, seq_space=w.s_kv, return_counts=True)
+    outs = []
+    for scale in (ks, 2 * ks, ks):
+        out = torch.empty((ntile, 128, 512), dtype=torch.bfloat16, device=DEV)
+        lse = torch.empty((ntile, 128), dtype=torch.float32, device=DEV)
+        api.masked_mla_fp8_out(q8.view(ntile, 128, 576), kv8, u, synth.SM_SCALE * qs * ks, scale, c, m,
+                               w.heads, out, None, lse)
+        outs.append((out, lse))
+    assert torch.equal(outs[0][0], outs[2][0]) and torch.equal(outs[0][1], outs[2][1])
+    assert torch.equal(outs[1][0].float(), 2 * outs[0][0].float())
+    assert bool(torch.isfinite(outs[0][0].float()).all())
+    assert api.attn_status()[0] == 0
