@@ -116,6 +116,37 @@ int litedsa_quantize_e4m3(const void* in_bf16, void* out_e4m3, int64_t n, float 
 int litedsa_repack_kv656(const void* kv656, void* kv576, int s_kv, int64_t out_pitch,
                          float scale, int* mismatch_flag, void* stream);
 
+/*
+ * Masked FP8 MLA prefill from packed 656-byte cache rows WITHOUT any allocation.
+ * This entry point has no counterpart in the reference.  It exists for hosts that are not
+ * allowed to call cudaMalloc where attention runs (a runtime that owns all device memory
+ * through its own pool, a plugin contract that forbids the callee to allocate, a memory
+ * budget frozen at start-up): the temporary 576-byte-row cache that
+ * litedsa_repack_kv656 + litedsa_masked_mla_fp8 would need from the caller is a fixed
+ * buffer inside the library instead.
+ *
+ *   kv656   [s_kv, 656] packed rows whose per-128 scales all equal kv_scale
+ *   mismatch_flag  device int32 or NULL: set non-zero when some scale differs (result invalid)
+ *   every other argument as in litedsa_masked_mla_fp8 (sm_scale multiplies q . k of the CODES,
+ *   kv_scale is also the output scale)
+ *
+ * Limits and rules:
+ *   - s_kv <= 65536 rows; longer caches return LITEDSA_ERR_UNSUPPORTED.
+ *   - the buffer (about 36 MiB) is part of the library image: every GPU that loads the
+ *     library holds it until the process exits.
+ *   - the first call on a device looks the buffer's address up; make that call outside
+ *     stream capture.
+ *   - all calls share the buffer and it keeps the previous call's rows: calls whose GPU
+ *     work can overlap (other streams, other threads) race and must be serialised.
+ */
+int litedsa_masked_mla_fp8_kv656_noalloc(const void* q8, const void* kv656, const int32_t* indices,
+                                         float sm_scale, float kv_scale,
+                                         const int32_t* topk_length, const uint32_t* memb_qm,
+                                         int h_per_q, void* out, float* max_logits, float* lse,
+                                         int ng, int s_kv, int topk, int64_t q_row_stride,
+                                         int64_t indices_row_stride, int* mismatch_flag,
+                                         void* stream);
+
 #ifdef __cplusplus
 }
 #endif
