@@ -172,9 +172,14 @@ def main():
     ap.add_argument("--cpu-tiles", type=int, default=32)
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tokens", type=int, default=0,
+                    help="shrink the workload to this many query tokens per GPU (profiling aid; "
+                         "the default, the full configuration, is the only benchmark number)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     w = synth.CONFIGS[args.config]
+    if args.tokens:
+        w = synth.scaled(w, tokens=args.tokens)
     if w.kind != "fp8":
         raise SystemExit("bench.py times the FP8 union + masked MLA path (configs c0, c1, c2, c4)")
     if args.impl == "reference":
@@ -279,7 +284,7 @@ def main():
         out_host.copy_(o, non_blocking=True)
         lse_host.copy_(l, non_blocking=True)
 
-    for _ in range(2):
+    for _ in range(min(2, args.e2e_steps)):
         e2e_step()
     barrier()
     e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)

@@ -25,7 +25,6 @@
 //   * no TMA multicast of any kind; the pair is signalled with two plain commits.
 #include "common.cuh"
 #include "tensor_map.cuh"
-#include <cstdlib>
 
 namespace lt {
 
@@ -46,7 +45,7 @@ constexpr uint32_t kOffK = kOffQ + kQBytes;
 constexpr uint32_t kOffV = kOffK + 2 * kKStage;
 constexpr uint32_t kOffP = kOffV + 2 * kVStage;
 constexpr uint32_t kOffMisc = kOffP + 2 * kPBytes;   // 204800
-constexpr uint32_t kMiscBytes = 3072;
+constexpr uint32_t kMiscBytes = 7168;
 constexpr uint32_t kAttnSmem = kOffMisc + kMiscBytes + 1024;  // + alignment slack
 static_assert(kAttnSmem <= 232448, "shared-memory plan exceeds the 227 KB per-CTA limit");
 
@@ -67,10 +66,13 @@ struct Misc {
   uint64_t q_full, k_peer[2], v_peer[2], s_free[2], p_ready[2];
   // in every CTA
   uint64_t k_land[2], v_land[2], k_copied[2], qk_done[2], pv_done[2], valid_ready[2], valid_free[2];
+  uint64_t m_pub[2];                // running max of block k published by softmax group k%2
   uint32_t valid[2][4];             // 128 validity bits per stage
   uint32_t tmem_base;
   uint32_t pad;
-  float xbuf[2][256];               // row-max exchange (double-buffered); row-sum exchange at the end
+  float xbuf[2][2][128];            // [group][parity][lane]: row-max exchange between key halves
+  float mshare[2][128];             // [group][lane]: running max after the group's latest block
+  float fin[3][256];                // end of tile: row sums, true maxima, last running max
 };
 static_assert(sizeof(Misc) <= kMiscBytes, "Misc too large");
 
@@ -85,13 +87,12 @@ struct AttnParams {
   int ng, s_kv, cap, h_per_q, G;
   long long idx_stride;
   float scale_log2, out_scale;
-  int exp_flags;             // experiment switches (0 in production)
 };
 
 // wait sites reported in the status word
 enum { kSiteQ = 1, kSiteKLand, kSiteKPeer, kSiteVLand, kSiteVPeer, kSiteQkDone, kSitePvDone,
        kSiteSFree, kSitePReady, kSiteValidReady, kSiteValidFree, kSiteKFree, kSiteKCopied,
-       kSiteVFree, kSitePFree, kSiteEpi, kSiteRelayK, kSiteRelayV, kSiteSmemAlign };
+       kSiteVFree, kSitePFree, kSiteEpi, kSiteRelayK, kSiteRelayV, kSiteMPub, kSiteMmaIdle };
 
 // status[0] first failing wait site, [1] block, [2] iteration, [3] launches completed
 __device__ int g_attn_status[4];
@@ -100,7 +101,8 @@ __device__ int g_attn_status[4];
 // 2 MMA thread, 3 copy thread, 4 relay thread), 8 slots per block, written after the S/O dump
 #define LT_TS(role, k, slot)                                                              \
   do {                                                                                    \
-    if (kDebug && ts_on && (k) < 64) ts[(((role) * 64 + (k)) << 3) + (slot)] = clock64(); \
+    if (kDebug && ts_on && (k) < 64)                                                      \
+      ts[((((role) + 5 * (int)cta) * 64 + (k)) << 3) + (slot)] = (long long)globaltimer_ns(); \
   } while (0)
 
 template <bool kDebug>
@@ -116,7 +118,8 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
 
   const uint32_t cta = cluster_ctarank();
   const int tile = blockIdx.x >> 1;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // broadcast so the compiler knows the role index is warp-uniform
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   int count = p.counts ? p.counts[tile] : p.cap;
   count = min(max(count, 0), p.cap);
   const int nb = max((count + kBlockKeys - 1) / kBlockKeys, 1);
@@ -124,7 +127,7 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
   bool ts_on = false;
   if (kDebug && p.dbg) {
     ts = reinterpret_cast<long long*>(p.dbg + (size_t)p.cap * 128 + 128 * 512 + 256);
-    ts_on = (tile == p.ng / 2) && cta == 0 && lane == 0;
+    ts_on = (tile == p.ng / 2) && lane == 0;
   }
 
   if (threadIdx.x == 0) {
@@ -132,15 +135,16 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
     for (int i = 0; i < 2; ++i) {
       mbar_init(&ms.k_peer[i], 1);
       mbar_init(&ms.v_peer[i], 1);
-      mbar_init(&ms.s_free[i], 2 * kSoftmaxWarps);
-      mbar_init(&ms.p_ready[i], 2 * kSoftmaxWarps);
+      mbar_init(&ms.s_free[i], 8);        // 4 warps of one softmax group x 2 CTAs
+      mbar_init(&ms.p_ready[i], 8);
       mbar_init(&ms.k_land[i], 1);
       mbar_init(&ms.v_land[i], 1);
       mbar_init(&ms.k_copied[i], 2);
       mbar_init(&ms.qk_done[i], 1);
       mbar_init(&ms.pv_done[i], 1);
       mbar_init(&ms.valid_ready[i], 1);
-      mbar_init(&ms.valid_free[i], kSoftmaxWarps);
+      mbar_init(&ms.valid_free[i], 4);
+      mbar_init(&ms.m_pub[i], 4);
     }
     fence_mbar_init();
     tma_prefetch_desc(&map_q);
@@ -160,79 +164,94 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
 
   if (warp < kSoftmaxWarps) {
     // ------------------------------------------------------------ softmax + epilogue
-    // TMEM lane tl = 32*(warp%4)+lane holds tile row r = tl%64 and key/dim half h = tl/64;
-    // the two warps sharing a lane quarter split that half's 64 columns (ch = warp/4).
-    const int t = threadIdx.x;                    // 0..255
+    // Two groups of four warps work on alternate key blocks (group g: blocks g, g+2, ...), so
+    // two blocks are in flight and the latencies of one chain (TMEM load, exchanges, fences)
+    // hide behind the other.  Within a group, thread = TMEM lane tl: tile row r = tl % 64,
+    // key half h = tl / 64 (64 S columns each).  The only state that crosses groups is the
+    // running max m, handed over through shared memory right after each block's row maxima
+    // are known; the row sum l is kept per group relative to the m of the group's latest
+    // block and merged at the end.
+
+    const int g = warp >> 2;                      // softmax group = block parity it serves
     const int tl = ((warp & 3) << 5) | lane;
-    const int r = tl & 63, h = tl >> 6, ch = warp >> 2;
-    const int part = 2 * h + ch;                  // which 32-key quarter of the block
+    const int r = tl & 63, h = tl >> 6;
     const int row = (int)cta * 64 + r;            // row of the 128-row tile
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const int capw = p.cap >> 5;
-    const uint32_t* mrow = p.memb + ((size_t)tile * p.G + row / p.h_per_q) * capw + part;
-    uint32_t mk = __ldg(mrow);
+    const uint32_t* mrow = p.memb + ((size_t)tile * p.G + row / p.h_per_q) * capw + 2 * h;
     const float c = p.scale_log2;
-    float m = kMInit, li = 0.f, real_m = -INFINITY;
-    const uint32_t a_s_free[2] = {mapa(smem_u32(&ms.s_free[0]), 0), mapa(smem_u32(&ms.s_free[1]), 0)};
-    const uint32_t a_p_ready[2] = {mapa(smem_u32(&ms.p_ready[0]), 0), mapa(smem_u32(&ms.p_ready[1]), 0)};
-    const int xi = part * 64 + r;                 // slot in the exchange buffer
+    float m_mine = kMInit;      // the running max my row sum is relative to
+    float li = 0.f, real_m = -INFINITY;
+    const uint32_t a_s_free = mapa(smem_u32(&ms.s_free[g]), 0);
+    const uint32_t a_p_ready = mapa(smem_u32(&ms.p_ready[g]), 0);
+    const uint32_t scol = tmem + lane_base + (g ? kTmemS1 : kTmemS0);
+    uint2 mk = make_uint2(0u, 0u);
+    if (g < nb) mk = __ldg(reinterpret_cast<const uint2*>(mrow + (size_t)g * 4));
 
-    for (int k = 0; k < nb; ++k) {
-      const int s = k & 1;
+    for (int k = g; k < nb; k += 2) {
       const uint32_t ph = (k >> 1) & 1;
-      uint32_t mk_next = mk;
-      if (k + 1 < nb) mk_next = __ldg(mrow + (size_t)(k + 1) * 4);
+      uint2 mk_next = mk;
+      if (k + 2 < nb) mk_next = __ldg(reinterpret_cast<const uint2*>(mrow + (size_t)(k + 2) * 4));
 
-      if (warp == 0) LT_TS(0, k, 0);
-      mbar_wait(&ms.qk_done[s], ph, status, kSiteQkDone, k);
-      if (warp == 0) LT_TS(0, k, 1);
+      if ((warp & 3) == 0) LT_TS(0, k, 0);
+      mbar_wait(&ms.qk_done[g], ph, status, kSiteQkDone, k);
+      if ((warp & 3) == 0) LT_TS(0, k, 1);
       tc_fence_after();
-      float sv[32];
-      tmem_ld32(tmem + lane_base + (s ? kTmemS1 : kTmemS0) + 32 * ch, sv);
+      float sv[64];
+      tmem_ld32(scol, sv);
+      tmem_ld32(scol + 32, sv + 32);
       tmem_wait_ld();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(a_s_free[s]);
+      if (lane == 0) mbar_arrive_cluster(a_s_free);
 
       if (kDebug && p.dbg && tile == 0) {
-        float* d = p.dbg + ((size_t)k * 128 + row) * 128 + 32 * part;
+        float* d = p.dbg + ((size_t)k * 128 + row) * 128 + 64 * h;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) d[j] = sv[j];
+        for (int j = 0; j < 64; ++j) d[j] = sv[j];
       }
 
-      mbar_wait(&ms.valid_ready[s], ph, status, kSiteValidReady, k);
-      const uint32_t bits = ms.valid[s][part] & mk;
+      mbar_wait(&ms.valid_ready[g], ph, status, kSiteValidReady, k);
+      const uint32_t v0 = ms.valid[g][2 * h] & mk.x, v1 = ms.valid[g][2 * h + 1] & mk.y;
       __syncwarp();
-      if (lane == 0) mbar_arrive(&ms.valid_free[s]);
+      if (lane == 0) mbar_arrive(&ms.valid_free[g]);
       mk = mk_next;
-      if (warp == 0) LT_TS(0, k, 2);
+      if ((warp & 3) == 0) LT_TS(0, k, 2);
 
       float cur = -INFINITY;
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
-        sv[j] = ((bits >> j) & 1u) ? sv[j] : -INFINITY;
-        cur = fmaxf(cur, sv[j]);
+        sv[j] = ((v0 >> j) & 1u) ? sv[j] : -INFINITY;
+        sv[32 + j] = ((v1 >> j) & 1u) ? sv[32 + j] : -INFINITY;
+        cur = fmaxf(cur, fmaxf(sv[j], sv[32 + j]));
       }
       cur *= c;
-      float* xb = ms.xbuf[k & 1];
-      xb[xi] = cur;
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      cur = fmaxf(fmaxf(xb[r], xb[64 + r]), fmaxf(xb[128 + r], xb[192 + r]));
-      if (warp == 0) LT_TS(0, k, 3);
+      float* xb = ms.xbuf[g][ph];
+      xb[tl] = cur;
+      if (g == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+      else asm volatile("bar.sync 2, 128;" ::: "memory");
+      cur = fmaxf(cur, xb[tl ^ 64]);
+      if ((warp & 3) == 0) LT_TS(0, k, 3);
       real_m = fmaxf(real_m, cur);
-      const bool rescale = __any_sync(0xffffffffu, cur - m > kRescaleThreshold);
-      float new_m = m, scale_old = 1.f;
-      if (rescale) {
-        new_m = fmaxf(cur, m);
-        scale_old = fast_exp2(m - new_m);
+      // running max after block k-1 comes from the other group
+      float m_prev = kMInit;
+      if (k > 0) {
+        mbar_wait(&ms.m_pub[g ^ 1], ((k - 1) >> 1) & 1, status, kSiteMPub, k);
+        m_prev = ms.mshare[g ^ 1][tl];
       }
-      m = new_m;
-      li *= scale_old;
+      const bool rescale = __any_sync(0xffffffffu, cur - m_prev > kRescaleThreshold);
+      const float new_m = rescale ? fmaxf(cur, m_prev) : m_prev;
+      ms.mshare[g][tl] = new_m;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ms.m_pub[g]);
+      li *= fast_exp2(m_mine - new_m);
+      m_mine = new_m;
+      if ((warp & 3) == 0) LT_TS(0, k, 4);
 
       const float nm = -new_m + kPScaleLog2;
-      uint32_t pk[8];
+      uint32_t pk[16];
 #pragma unroll
-      for (int j = 0; j < 32; j += 4) {
+      for (int j = 0; j < 64; j += 4) {
         float2 d0, d1;
         d0.x = fast_exp2(fmaf(sv[j], c, nm));
         d0.y = fast_exp2(fmaf(sv[j + 1], c, nm));
@@ -244,46 +263,63 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         const uint32_t hi = __nv_cvt_float2_to_fp8x2(d1, __NV_SATFINITE, __NV_E4M3);
         pk[j >> 2] = lo | (hi << 16);
       }
-      if (warp == 0) LT_TS(0, k, 4);
-      // P buffer s was last read by PV(k-2)
-      if (k >= 2) mbar_wait(&ms.pv_done[s], ph ^ 1, status, kSitePFree, k);
-      if (warp == 0) LT_TS(0, k, 5);
-      uint8_t* pdst = sm + kOffP + s * kPBytes + (2 * part) * 1024 + r * 16;
-      *reinterpret_cast<uint4*>(pdst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-      *reinterpret_cast<uint4*>(pdst + 1024) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+      if ((warp & 3) == 0) LT_TS(0, k, 5);
+      // P buffer g was last read by PV(k-2)
+      if (k >= 2) mbar_wait(&ms.pv_done[g], ph ^ 1, status, kSitePFree, k);
+      uint8_t* pdst = sm + kOffP + g * kPBytes + (4 * h) * 1024 + r * 16;
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        *reinterpret_cast<uint4*>(pdst + i * 1024) =
+            make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
 
       if (rescale && k > 0) {
-        // O still holds blocks [0, k): needs PV(k-1) complete
-        mbar_wait(&ms.pv_done[(k - 1) & 1], ((k - 1) >> 1) & 1, status, kSitePvDone, k);
+        // O holds blocks [0, k) relative to m_prev: bring it to new_m once PV(k-1) is complete
+        mbar_wait(&ms.pv_done[g ^ 1], ((k - 1) >> 1) & 1, status, kSitePvDone, k);
         tc_fence_after();
+        const float f = fast_exp2(m_prev - new_m);
         float o[32];
 #pragma unroll 1
-        for (int cc = 0; cc < 4; ++cc) {
-          const uint32_t ocol = tmem + lane_base + kTmemO + ch * 128 + cc * 32;
+        for (int cc = 0; cc < 8; ++cc) {
+          const uint32_t ocol = tmem + lane_base + kTmemO + cc * 32;
           tmem_ld32(ocol, o);
           tmem_wait_ld();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) o[j] *= scale_old;
+          for (int j = 0; j < 32; ++j) o[j] *= f;
           tmem_st32(ocol, o);
         }
         tmem_wait_st();
         tc_fence_before();
       }
-      if (warp == 0) LT_TS(0, k, 6);
+      if ((warp & 3) == 0) LT_TS(0, k, 6);
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(a_p_ready[s]);
-      if (warp == 0) LT_TS(0, k, 7);
+      if (lane == 0) mbar_arrive_cluster(a_p_ready);
+      if ((warp & 3) == 0) LT_TS(0, k, 7);
     }
 
-    // epilogue
-    float* xb = ms.xbuf[nb & 1];
-    xb[xi] = li;
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    li = (xb[r] + xb[64 + r]) + (xb[128 + r] + xb[192 + r]);
+    // end of tile: merge the two groups' row sums (each relative to its own latest running max)
+    const int t = threadIdx.x;                    // 0..255 = g*128 + tl
+    ms.fin[0][t] = li;
+    ms.fin[1][t] = real_m;
+    ms.fin[2][t] = m_mine;
+    asm volatile("bar.sync 3, 256;" ::: "memory");
+    const int last_g = (nb - 1) & 1;
+    float m = ms.fin[2][last_g * 128 + tl];       // running max after the last block
+    float lsum = 0.f;
+    real_m = -INFINITY;
+#pragma unroll
+    for (int gg = 0; gg < 2; ++gg) {
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        const int o = gg * 128 + hh * 64 + r;
+        lsum += ms.fin[0][o] * fast_exp2(ms.fin[2][o] - m);
+        real_m = fmaxf(real_m, ms.fin[1][o]);
+      }
+    }
+    li = lsum;
     if (real_m == -INFINITY) { li = 0.f; m = -INFINITY; }
     const size_t grow = (size_t)tile * 128 + row;
-    if (part == 0) {
+    if (g == 0 && h == 0) {
       float l = __logf(li) - kPScaleLn + m * kLn2;
       if (!(li > 0.f)) l = INFINITY;
       p.lse[grow] = l;
@@ -293,14 +329,15 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
     tc_fence_after();
     const bool empty = !(li > 0.f);
     const float oscale = empty ? 0.f : __fdividef(p.out_scale, li);
-    __nv_bfloat16* orow = p.out + grow * kDV + 256 * h + 128 * ch;
+    // group g writes dims [256h + 128g, +128) of its row
+    __nv_bfloat16* orow = p.out + grow * kDV + 256 * h + 128 * g;
     float o[32];
 #pragma unroll 1
     for (int cc = 0; cc < 4; ++cc) {
-      tmem_ld32(tmem + lane_base + kTmemO + ch * 128 + cc * 32, o);
+      tmem_ld32(tmem + lane_base + kTmemO + g * 128 + cc * 32, o);
       tmem_wait_ld();
       if (kDebug && p.dbg && tile == 0) {
-        float* d = p.dbg + (size_t)p.cap * 128 + (size_t)row * 512 + 256 * h + 128 * ch + cc * 32;
+        float* d = p.dbg + (size_t)p.cap * 128 + (size_t)row * 512 + 256 * h + 128 * g + cc * 32;
 #pragma unroll
         for (int j = 0; j < 32; ++j) d[j] = o[j];
       }
@@ -316,7 +353,7 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
       for (int j = 0; j < 4; ++j) dst[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
     }
-    if (kDebug && p.dbg && tile == 0 && part == 0) {
+    if (kDebug && p.dbg && tile == 0 && g == 0 && h == 0) {
       float* d = p.dbg + (size_t)p.cap * 128 + 128 * 512;
       d[row] = m;
       d[128 + row] = li;
@@ -325,113 +362,125 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
   } else if (warp < kSoftmaxWarps + kProducerWarps) {
     // ------------------------------------------------------------ TMA producers (K rows, Q tile)
     // warp pw gathers row quads pw and pw+8 of this CTA's 64 keys, all five column chunks
-    if (lane == 0) {
+
+    // (the whole warp runs the loop with warp-uniform values; one elected lane issues)
+    {
       const int pw = warp - kSoftmaxWarps;
-      if (pw == 0) {
+      if (pw == 0 && lane == 0) {
         if (cta == 0) mbar_arrive_expect_tx(&ms.q_full, 2 * kQBytes);
         const uint32_t a_q_full = mapa(smem_u32(&ms.q_full), 0);
         for (int j = 0; j < kChunks; ++j)
           tma_load_2d_pair(sbase + kOffQ + j * kChunkBytes, &map_q, 128 * j,
                            tile * 128 + (int)cta * 64, a_q_full);
       }
-      const int32_t* idx_row = p.indices + (size_t)tile * p.idx_stride + 64 * cta + 4 * pw;
+      __syncwarp();
+      // lane l < 10 of warp pw owns row quad pw + 8*(l/5) and column chunk l%5: one warp-wide
+      // instruction issues the warp's ten gathers of a block
+      const int quad = pw + 8 * (lane / 5), chunk = lane % 5;
+      const bool active = lane < 10;
+      const int32_t* idx_row = p.indices + (size_t)tile * p.idx_stride + 64 * cta + 4 * (active ? quad : pw);
       int4 c0 = __ldg(reinterpret_cast<const int4*>(idx_row));
-      int4 c1 = __ldg(reinterpret_cast<const int4*>(idx_row + 32));
       for (int k = 0; k < nb; ++k) {
         const int s = k & 1;
         const uint32_t ph = (k >> 1) & 1;
-        int4 n0 = c0, n1 = c1;
-        if (k + 1 < nb) {
-          n0 = __ldg(reinterpret_cast<const int4*>(idx_row + (size_t)(k + 1) * kBlockKeys));
-          n1 = __ldg(reinterpret_cast<const int4*>(idx_row + (size_t)(k + 1) * kBlockKeys + 32));
-        }
+        int4 n0 = c0;
+        if (k + 1 < nb) n0 = __ldg(reinterpret_cast<const int4*>(idx_row + (size_t)(k + 1) * kBlockKeys));
         if (pw == 0) LT_TS(1, k, 0);
         if (k >= 2) {
           // stage s held block k-2: QK(k-2) must have read it and its V copies must be out
           mbar_wait(&ms.qk_done[s], ph ^ 1, status, kSiteKFree, k);
           mbar_wait(&ms.k_copied[s], ph ^ 1, status, kSiteKCopied, k);
         }
+        __syncwarp();
         if (pw == 0) LT_TS(1, k, 1);
-        if ((p.exp_flags & 1) && k >= 2) {
-          if (pw == 0) mbar_arrive(&ms.k_land[s]);
-          c0 = n0; c1 = n1;
-          continue;
-        }
-        if (pw == 0) mbar_arrive_expect_tx(&ms.k_land[s], kKStage);
-        const uint32_t bar = smem_u32(&ms.k_land[s]);
-        const uint32_t dst = sbase + kOffK + s * kKStage + (uint32_t)pw * 512;
-#pragma unroll
-        for (int j = 0; j < kChunks; ++j) {
-          tma_gather4(dst + j * kChunkBytes, &map_kv, 128 * j, c0, bar);
-          tma_gather4(dst + j * kChunkBytes + 4096, &map_kv, 128 * j, c1, bar);
-        }
+        if (pw == 0 && lane == 0) mbar_arrive_expect_tx(&ms.k_land[s], kKStage);
+        if (active)
+          tma_gather4(sbase + kOffK + s * kKStage + (uint32_t)quad * 512 + chunk * kChunkBytes, &map_kv,
+                      128 * chunk, c0, smem_u32(&ms.k_land[s]));
+        __syncwarp();
         if (pw == 0) LT_TS(1, k, 2);
-        c0 = n0; c1 = n1;
+        c0 = n0;
       }
     }
-  } else if (warp == kWarpMma) {
+  } else {
+
+   if (warp == kWarpMma) {
     // ------------------------------------------------------------ MMA issue (leader CTA only)
-    if (cta == 0 && lane == 0) {
+    if (cta == 0) {   // the whole warp runs this loop; one elected lane issues
       constexpr uint32_t idesc_qk = umma_idesc(0, 0, false, false, 128, 128);
       constexpr uint32_t idesc_pv = umma_idesc(0, 0, false, true, 128, 256);
       const uint32_t a_qk_done_peer[2] = {mapa(smem_u32(&ms.qk_done[0]), 1), mapa(smem_u32(&ms.qk_done[1]), 1)};
       const uint32_t a_pv_done_peer[2] = {mapa(smem_u32(&ms.pv_done[0]), 1), mapa(smem_u32(&ms.pv_done[1]), 1)};
       mbar_wait(&ms.q_full, 0, status, kSiteQ, 0);
+      __syncwarp();
       // S = Q K^T of block k into S buffer k%2 (needs K stage k%2 on both CTAs, buffer drained)
       auto issue_qk = [&](int k) {
         const int s = k & 1;
-        const uint32_t ph = (k >> 1) & 1;
-        LT_TS(2, k, 0);
-        mbar_wait(&ms.k_land[s], ph, status, kSiteKLand, k);
-        mbar_wait(&ms.k_peer[s], ph, status, kSiteKPeer, k);
-        LT_TS(2, k, 1);
-        if (k >= 2) mbar_wait(&ms.s_free[s], ph ^ 1, status, kSiteSFree, k);
         LT_TS(2, k, 2);
         tc_fence_after();
         const uint32_t d = tmem + (s ? kTmemS1 : kTmemS0);
-        const uint32_t qb = sbase + kOffQ, kb = sbase + kOffK + s * kKStage;
-#pragma unroll
-        for (int j = 0; j < kChunks; ++j) {
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            if (j * 128 + kk * 32 >= kDQK) break;
-            const uint64_t ad = umma_desc(qb + j * kChunkBytes + kk * 32, 16, 1024, kSwz128);
-            const uint64_t bd = umma_desc(kb + j * kChunkBytes + kk * 32, 16, 1024, kSwz128);
-            mma_f8_pair(d, ad, bd, idesc_qk, (j | kk) ? 1u : 0u);
-          }
-        }
-        mma_commit_pair(smem_u32(&ms.qk_done[s]));
-        mma_commit_pair(a_qk_done_peer[s]);
+        const uint64_t ad = umma_desc(sbase + kOffQ, 16, 1024, kSwz128);
+        const uint64_t bd = umma_desc(sbase + kOffK + s * kKStage, 16, 1024, kSwz128);
+        mma_f8_pair_qk18(d, idesc_qk, (uint32_t)ad, (uint32_t)bd, (uint32_t)(ad >> 32),
+                         (uint32_t)(bd >> 32));
+        mma_commit_pair_elect(smem_u32(&ms.qk_done[s]));
+        mma_commit_pair_elect(a_qk_done_peer[s]);
         LT_TS(2, k, 3);
       };
-      // QK runs ahead of PV: S(k+1) is produced while the softmax warps work on block k.
-      // Issue order: QK(0), QK(1), PV(0), QK(2), PV(1), QK(3), ...
-      issue_qk(0);
-      if (nb > 1) issue_qk(1);
-      for (int kb_ = 0; kb_ < nb; ++kb_) {
+      auto issue_pv = [&](int kb_) {
         const int s = kb_ & 1;
-        const uint32_t ph = (kb_ >> 1) & 1;
-        LT_TS(2, kb_, 4);
-        mbar_wait(&ms.p_ready[s], ph, status, kSitePReady, kb_);
-        LT_TS(2, kb_, 5);
-        mbar_wait(&ms.v_land[s], ph, status, kSiteVLand, kb_);
-        mbar_wait(&ms.v_peer[s], ph, status, kSiteVPeer, kb_);
         LT_TS(2, kb_, 6);
         tc_fence_after();
-        const uint32_t pb = sbase + kOffP + s * kPBytes, vb = sbase + kOffV + s * kVStage;
-#pragma unroll
-        for (int nbk = 0; nbk < 2; ++nbk) {
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            const uint64_t ad = umma_desc(pb + ks * 2048, 1024, 128, kSwzNone);
-            const uint64_t bd = umma_desc(vb + nbk * kVChunk + ks * 4096, kVChunk, 1024, kSwz128);
-            mma_f8_pair(tmem + kTmemO + nbk * 128, ad, bd, idesc_pv, (kb_ | ks) ? 1u : 0u);
+        const uint64_t ad = umma_desc(sbase + kOffP + s * kPBytes, 1024, 128, kSwzNone);
+        const uint64_t bd = umma_desc(sbase + kOffV + s * kVStage, kVChunk, 1024, kSwz128);
+        mma_f8_pair_pv8(tmem + kTmemO, idesc_pv, (uint32_t)ad, (uint32_t)bd, (uint32_t)(ad >> 32),
+                        (uint32_t)(bd >> 32), kb_ ? 1u : 0u);
+        mma_commit_pair_elect(smem_u32(&ms.pv_done[s]));
+        mma_commit_pair_elect(a_pv_done_peer[s]);
+        LT_TS(2, kb_, 7);
+      };
+      // Ready-driven issue: whichever of "next QK" (its K stage landed on both CTAs and its S
+      // buffer drained) and "next PV" (its P written, its V stage landed on both CTAs) is
+      // ready goes first; PV wins ties because it releases stages.  QK can run up to two
+      // blocks ahead of the softmax warps.  Bounded like every other wait.
+      int qk_i = 0, pv_i = 0;
+      unsigned long long idle_since = 0;
+      bool aborted = false;
+      while (pv_i < nb && !aborted) {
+        bool did = false;
+        {
+          const int s = pv_i & 1;
+          const uint32_t ph = (pv_i >> 1) & 1;
+          // lanes poll independently: act only on what every lane has seen (keeps the warp converged)
+          const bool ok = pv_i < qk_i && mbar_test(&ms.p_ready[s], ph) &&
+                          mbar_test(&ms.v_land[s], ph) && mbar_test(&ms.v_peer[s], ph);
+          if (__all_sync(0xffffffffu, ok)) {
+            issue_pv(pv_i++);
+            did = true;
           }
         }
-        mma_commit_pair(smem_u32(&ms.pv_done[s]));
-        mma_commit_pair(a_pv_done_peer[s]);
-        LT_TS(2, kb_, 7);
-        if (kb_ + 2 < nb) issue_qk(kb_ + 2);
+        if (qk_i < nb) {
+          const int s = qk_i & 1;
+          const uint32_t ph = (qk_i >> 1) & 1;
+          const bool ok = mbar_test(&ms.k_land[s], ph) && mbar_test(&ms.k_peer[s], ph) &&
+                          (qk_i < 2 || mbar_test(&ms.s_free[s], ph ^ 1));
+          if (__all_sync(0xffffffffu, ok)) {
+            issue_qk(qk_i++);
+            did = true;
+          }
+        }
+        if (did) {
+          idle_since = 0;
+        } else {
+          const unsigned long long now = globaltimer_ns();
+          if (idle_since == 0) idle_since = now;
+          bool stop = *reinterpret_cast<volatile int*>(status) != 0;
+          if (now - idle_since > kWaitLimitNs) {
+            if (lane == 0 && atomicCAS(status, 0, (int)kSiteMmaIdle) == 0) { status[1] = (int)blockIdx.x; status[2] = pv_i; }
+            stop = true;
+          }
+          aborted = __any_sync(0xffffffffu, stop);
+        }
       }
     }
   } else if (warp == kWarpCopy) {
@@ -450,10 +499,6 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         if (cta == 1) mbar_arrive_cluster(a_k_peer[s]);
         if (k >= 2) mbar_wait(&ms.pv_done[s], ph ^ 1, status, kSiteVFree, k);   // V stage s free
         LT_TS(3, k, 2);
-        if ((p.exp_flags & 2) && k >= 2) {
-          mbar_arrive(&ms.v_land[s]);
-          continue;
-        }
         mbar_arrive_expect_tx(&ms.v_land[s], kVStage);
         const uint32_t src = sbase + kOffK + s * kKStage;
         const uint32_t vdst = sbase + kOffV + s * kVStage + cta * (64 * 128);
@@ -508,6 +553,7 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
       cur = nxt;
     }
   }
+  }
   (void)peer;
 
   // tear-down: nobody may still be reading TMEM of either CTA when it is released
@@ -537,7 +583,6 @@ static int launch_fp8(const void* q8, const void* kv8, const int32_t* indices, f
   p.ng = ng; p.s_kv = s_kv; p.cap = topk; p.h_per_q = h_per_q; p.G = 128 / h_per_q;
   p.idx_stride = idx_row_stride;
   p.scale_log2 = sm_scale * kLog2e; p.out_scale = out_scale;
-  { const char* e = getenv("LITEDSA_EXP"); p.exp_flags = e ? atoi(e) : 0; }
   auto kern = dbg ? masked_mla_fp8_kernel<true> : masked_mla_fp8_kernel<false>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem) !=
       cudaSuccess)

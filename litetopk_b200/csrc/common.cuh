@@ -68,6 +68,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// non-blocking probe (try_wait may suspend the thread for a hardware-defined time)
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait.  Every wait in the library goes through here: it gives up after
 // `kWaitLimitNs` of wall time, or as soon as any other wait of the launch gave up
 // (the launch-wide abort word), records where, and returns false.  Callers then fall
@@ -149,6 +162,25 @@ __device__ __forceinline__ void tma_gather4(uint32_t dst_smem, const CUtensorMap
         "r"(mbar_smem)
       : "memory");
 }
+// elected-lane forms for fully converged warps: the surrounding code stays warp-uniform, so
+// the compiler can keep TMA operands in uniform registers instead of converting per lane
+__device__ __forceinline__ void tma_gather4_elect(uint32_t dst_smem, const CUtensorMap* map, int x,
+                                                  int4 rows, uint32_t mbar_smem) {
+  asm volatile(
+      "{\n\t.reg .pred pe;\n\telect.sync _|pe, 0xffffffff;\n\t"
+      "@pe cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3, %4, %5, %6}], [%7];\n\t}"
+      ::"r"(dst_smem), "l"(map), "r"(x), "r"(rows.x), "r"(rows.y), "r"(rows.z), "r"(rows.w),
+        "r"(mbar_smem)
+      : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx_elect(uint64_t* bar, uint32_t bytes) {
+  asm volatile(
+      "{\n\t.reg .pred pe;\n\telect.sync _|pe, 0xffffffff;\n\t"
+      "@pe mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t}"
+      ::"r"(smem_u32(bar)), "r"(bytes)
+      : "memory");
+}
 // shared -> (distributed) shared bulk copy inside the cluster; dst and mbar are shared::cluster
 // addresses of the SAME CTA, src is a shared::cta address of the issuing CTA
 __device__ __forceinline__ void bulk_copy_s2s(uint32_t dst_cluster, uint32_t src_smem,
@@ -190,6 +222,51 @@ __device__ __forceinline__ void mma_f16_pair(uint32_t d_tmem, uint64_t adesc, ui
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// A whole K-loop of MMAs in one instruction stream, executed by a fully converged warp whose
+// elected lane issues (warp-uniform code lets the descriptors live in uniform registers).
+// The fewest possible issue slots: the
+// issuing thread shares its scheduler with busy warps, and every extra integer instruction per
+// MMA costs tensor-pipe time.  Descriptors differ only in their low word (start address >> 4),
+// so each step is two 32-bit adds, two register-pair moves and the MMA.
+//   QK^T of one 128-key block: 18 steps over five 128-byte chunks (step (j,kk): +512*j + 2*kk)
+#define LT_QK_STEP(INC, PRED)                                  \
+  "add.u32 alo, %2, " #INC ";\n\tadd.u32 blo, %3, " #INC ";\n\t" \
+  "mov.b64 ad, {alo, %4};\n\tmov.b64 bd, {blo, %5};\n\t"        \
+  "@pe tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], ad, bd, %1, " #PRED ";\n\t"
+__device__ __forceinline__ void mma_f8_pair_qk18(uint32_t d_tmem, uint32_t idesc, uint32_t a_lo,
+                                                 uint32_t b_lo, uint32_t a_hi, uint32_t b_hi) {
+  asm volatile(
+      "{\n\t.reg .pred pz, po, pe;\n\t.reg .b32 alo, blo;\n\t.reg .b64 ad, bd;\n\t"
+      "setp.ne.b32 pz, 0, 0;\n\tsetp.eq.b32 po, 0, 0;\n\telect.sync _|pe, 0xffffffff;\n\t"
+      LT_QK_STEP(0, pz) LT_QK_STEP(2, po) LT_QK_STEP(4, po) LT_QK_STEP(6, po)
+      LT_QK_STEP(512, po) LT_QK_STEP(514, po) LT_QK_STEP(516, po) LT_QK_STEP(518, po)
+      LT_QK_STEP(1024, po) LT_QK_STEP(1026, po) LT_QK_STEP(1028, po) LT_QK_STEP(1030, po)
+      LT_QK_STEP(1536, po) LT_QK_STEP(1538, po) LT_QK_STEP(1540, po) LT_QK_STEP(1542, po)
+      LT_QK_STEP(2048, po) LT_QK_STEP(2050, po)
+      "}"
+      ::"r"(d_tmem), "r"(idesc), "r"(a_lo), "r"(b_lo), "r"(a_hi), "r"(b_hi)
+      : "memory");
+}
+//   P V of one 128-key block: two N = 256 halves (D column offset 128, V chunk +1024) x four
+//   32-key steps (P +128, V +256 per step); `first` = 0 zeroes the accumulator in step 0
+#define LT_PV_STEP(DOFF, AINC, BINC, PRED)                              \
+  "add.u32 dd, %0, " #DOFF ";\n\tadd.u32 alo, %2, " #AINC ";\n\tadd.u32 blo, %3, " #BINC ";\n\t" \
+  "mov.b64 ad, {alo, %4};\n\tmov.b64 bd, {blo, %5};\n\t"                  \
+  "@pe tcgen05.mma.cta_group::2.kind::f8f6f4 [dd], ad, bd, %1, " #PRED ";\n\t"
+__device__ __forceinline__ void mma_f8_pair_pv8(uint32_t d_tmem, uint32_t idesc, uint32_t a_lo,
+                                                uint32_t b_lo, uint32_t a_hi, uint32_t b_hi,
+                                                uint32_t accumulate_first) {
+  asm volatile(
+      "{\n\t.reg .pred pf, po, pe;\n\t.reg .b32 alo, blo, dd;\n\t.reg .b64 ad, bd;\n\t"
+      "setp.ne.b32 pf, %6, 0;\n\tsetp.eq.b32 po, 0, 0;\n\telect.sync _|pe, 0xffffffff;\n\t"
+      LT_PV_STEP(0, 0, 0, pf) LT_PV_STEP(0, 128, 256, po) LT_PV_STEP(0, 256, 512, po)
+      LT_PV_STEP(0, 384, 768, po)
+      LT_PV_STEP(128, 0, 1024, pf) LT_PV_STEP(128, 128, 1280, po) LT_PV_STEP(128, 256, 1536, po)
+      LT_PV_STEP(128, 384, 1792, po)
+      "}"
+      ::"r"(d_tmem), "r"(idesc), "r"(a_lo), "r"(b_lo), "r"(a_hi), "r"(b_hi), "r"(accumulate_first)
+      : "memory");
+}
 // all MMAs issued so far by this thread -> one arrival on the barrier at `cluster_addr`
 __device__ __forceinline__ void mma_commit_pair(uint32_t cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
@@ -198,6 +275,14 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t cluster_addr) {
 }
 
 // 32 lanes x 32 consecutive fp32 columns: thread i of the warp gets lane (base_lane + i)
+// the same, issued by one elected lane of a fully converged warp (keeps the caller warp-uniform)
+__device__ __forceinline__ void mma_commit_pair_elect(uint32_t cluster_addr) {
+  asm volatile(
+      "{\n\t.reg .pred pe;\n\telect.sync _|pe, 0xffffffff;\n\t"
+      "@pe tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+      ::"r"(cluster_addr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
   uint32_t* r = reinterpret_cast<uint32_t*>(v);
   asm volatile(
