@@ -117,6 +117,32 @@ int litedsa_repack_kv656(const void* kv656, void* kv576, int s_kv, int64_t out_p
                          float scale, int* mismatch_flag, void* stream);
 
 /*
+ * DeepSeek-V4 style packed BF16 attention over two contiguous key ranges.
+ * Replaces the reference operator
+ *   dsv4_masked_mla_bf16(q, kv, indices, pref, win_lo, win_hi, counts, sm_scale, h_per_q,
+ *                        out, lse, attn_sink)            (kernels/b200/dsa/litedsa_dsv4.cu:50-121)
+ * for callers whose ranges are contiguous in memory: the gathered union index list and the
+ * per-token rank ranges are replaced by the two KV tensors and the first query position.
+ * Token t of the call sits at position p = pos0 + t and attends to kv_comp rows
+ * [0, min(p / ratio, n_comp)) and kv_raw rows [max(0, p - window + 1), p].
+ *
+ *   q        [ng, 128, 576] bf16 (row r of a tile = token r / h_per_q, head r % h_per_q)
+ *   kv_comp  [n_comp, 576] bf16 (may be NULL when n_comp == 0);  kv_raw [s_raw, 576] bf16
+ *   *_row_stride in ELEMENTS (>= 576, multiples of 8); V = the first 512 dims of the same rows
+ *   attn_sink [128] fp32 per packed row or NULL: adds exp(sink) to the OUTPUT normaliser only
+ *   out [ng, 128, 512] bf16;  lse [ng, 128] fp32 (natural log, without the sink)
+ * Requires pos0 + ng * (128 / h_per_q) <= s_raw.
+ */
+int litedsa_dsv4_c128a_bf16(const void* q, const void* kv_comp, const void* kv_raw, int ng,
+                            int h_per_q, int n_comp, int s_raw, int pos0, int window, int ratio,
+                            float sm_scale, const float* attn_sink, void* out, float* lse,
+                            int64_t q_row_stride, int64_t kc_row_stride, int64_t kr_row_stride,
+                            void* stream);
+
+/* Status word of the DSv4 kernel; same meaning and use as litedsa_attn_status. */
+int litedsa_dsv4_status(int* out4_host, int reset);
+
+/*
  * Masked FP8 MLA prefill from packed 656-byte cache rows WITHOUT any allocation.
  * This entry point has no counterpart in the reference.  It exists for hosts that are not
  * allowed to call cudaMalloc where attention runs (a runtime that owns all device memory

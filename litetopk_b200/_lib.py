@@ -33,6 +33,10 @@ SIGNATURES = {
                                                      c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                                      c_void_p, c_int, c_int, c_int, c_int64, c_int64,
                                                      c_void_p, c_void_p]),
+    "litedsa_dsv4_c128a_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                        c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int64,
+                                        c_int64, c_int64, c_void_p]),
+    "litedsa_dsv4_status": (c_int, [c_void_p, c_int]),
 }
 
 _lib = None

@@ -289,3 +289,62 @@ def sparse_prefill(q: torch.Tensor, kv_cache_fp8: torch.Tensor, topk_idx: torch.
                        return_counts=True)
     return masked_mla_fp8(q, kv_cache_fp8, u, m, sm_scale, counts=c, kv_scale=kv_scale,
                           q_scale=q_scale)
+
+
+# --------------------------------------------------------------------------- DSv4 BF16 two-range attention
+def dsv4_c128a_bf16(q: torch.Tensor, kv_compressed: Optional[torch.Tensor], kv_raw: torch.Tensor,
+                    q_pos0: int, sm_scale: float, *, window: int = 128, ratio: int = 128,
+                    attn_sink: Optional[torch.Tensor] = None):
+    """Packed BF16 attention over (compressed prefix, sliding window).
+
+    q [T,h,576] bf16 for T consecutive tokens starting at position ``q_pos0``; token at
+    position p attends to kv_compressed rows [0, p // ratio) and kv_raw rows
+    [p - window + 1, p]; V = first 512 dims of the same rows.  ``attn_sink`` [h] fp32 adds
+    exp(sink) to the output normaliser.  Returns ``(out [T,h,512] bf16, lse [T,h] f32)``.
+    The reference's counterpart takes a gathered index list plus rank ranges
+    (kernels/b200/dsa/litedsa_dsv4.cu:50-55); here the ranges are contiguous memory.
+    """
+    _need(q, "q", torch.bfloat16, 3)
+    _need(kv_raw, "kv_raw", torch.bfloat16, 2)
+    T, h, d = q.shape
+    if d != 576 or 128 % h or 128 // h > 16 or kv_raw.shape[1] != 576:
+        raise ValueError("q must be [T,h,576] (h | 128, 128/h <= 16) and kv_raw [S,576]")
+    G = 128 // h
+    if T % G:
+        raise ValueError("token count must be a multiple of 128 // heads")
+    q = q.contiguous()
+    n_comp = 0
+    if kv_compressed is not None and kv_compressed.shape[0] > 0:
+        _need(kv_compressed, "kv_compressed", torch.bfloat16, 2)
+        if kv_compressed.shape[1] != 576 or kv_compressed.stride(1) != 1:
+            raise ValueError("kv_compressed must be [Nc,576] with unit inner stride")
+        n_comp = kv_compressed.shape[0]
+    if kv_raw.stride(1) != 1:
+        raise ValueError("kv_raw needs unit inner stride")
+    sink = None
+    if attn_sink is not None:
+        _need(attn_sink, "attn_sink", torch.float32, 1)
+        if attn_sink.shape[0] != h:
+            raise ValueError("attn_sink must be [heads]")
+        sink = attn_sink.repeat(G).contiguous()            # per packed row
+    ng = T // G
+    out = torch.empty((ng, 128, 512), dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty((ng, 128), dtype=torch.float32, device=q.device)
+    with torch.cuda.device(q.device):
+        rc = _lib.lib().litedsa_dsv4_c128a_bf16(
+            _ptr(q), _ptr(kv_compressed) if n_comp else None, _ptr(kv_raw), ng, h, n_comp,
+            kv_raw.shape[0], int(q_pos0), int(window), int(ratio), float(sm_scale), _ptr(sink),
+            _ptr(out), _ptr(lse), 576, kv_compressed.stride(0) if n_comp else 576, kv_raw.stride(0),
+            _stream(q))
+    check(rc, "dsv4_c128a_bf16")
+    return out.view(T, h, 512), lse.view(T, h)
+
+
+def dsv4_status(reset: bool = False, device=None) -> Tuple[int, int, int, int]:
+    """Status word of the DSv4 kernel (see :func:`attn_status`)."""
+    import ctypes
+    buf = (ctypes.c_int * 4)()
+    with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
+        torch.cuda.synchronize()
+        _lib.lib().litedsa_dsv4_status(buf, 1 if reset else 0)
+    return tuple(int(x) for x in buf)

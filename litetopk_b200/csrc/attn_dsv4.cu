@@ -1,0 +1,430 @@
+// DeepSeek-V4 style packed BF16 attention over two contiguous key ranges (sm_100a).
+//
+// Every query token at position p attends to the compressed-prefix entries
+// [0, p / ratio) of a small compressed KV and to the raw sliding window
+// [p - window + 1, p]; G = 128 / h adjacent tokens are packed into one 128-row tile.
+// The reference's DSv4 operator (kernels/b200/dsa/litedsa_dsv4.cu:50-121, kernel
+// kernels/b200/dsa/litedsa_attention_sm100_dsv4.cuh:1849-2485) expresses the same mask as
+// two ranges per token in the rank space of a gathered union list (range_mask32,
+// litedsa_attention_sm100_dsv4.cuh:1824-1829) and gathers rows with TMA gather4.  Here the
+// ranges are used directly: both key segments are contiguous in memory, so K and V tiles
+// come from plain tiled TMA loads (13 per 64-key block per CTA instead of 2 x 36 gathers),
+// no index list exists, and the mask is two comparisons per column.
+//
+// Organisation: cluster of 2 CTAs per tile (64 query rows each), 64-key blocks, bf16
+// tcgen05 cta_group::2 MMAs (S = Q K^T over 576 dims: 36 K-steps of 16; O += P V: two
+// N = 256 halves x 4 K-steps), S double-buffered in TMEM, O in TMEM, base-2 online softmax
+// with the same lazy running-max policy as the FP8 kernel, P stored as bf16 (no pre-scale,
+// litedsa_attention_sm100_dsv4.cuh:2072-2083), optional per-row attention sink in the
+// output normaliser only (:2138-2157).
+#include "common.cuh"
+#include "tensor_map.cuh"
+
+namespace lt {
+namespace dsv4 {
+
+constexpr int kThreads = 192;                         // 4 softmax warps, 1 TMA warp, 1 MMA warp
+constexpr int kBlockKeys = 64;
+constexpr int kD = 576, kDV = 512;
+constexpr int kQChunks = 9;                           // 64 bf16 = 128 bytes per chunk
+constexpr uint32_t kQChunkBytes = 64 * 128;           // 64 rows
+constexpr uint32_t kQBytes = kQChunks * kQChunkBytes; // 73728
+constexpr uint32_t kKChunkBytes = 32 * 128;           // 32 keys per CTA
+constexpr uint32_t kKStage = kQChunks * kKChunkBytes; // 36864
+constexpr uint32_t kVChunkBytes = 64 * 128;           // 64 keys x 64 dims
+constexpr uint32_t kVStage = 4 * kVChunkBytes;        // 64 keys x 256 dims = 32768
+constexpr uint32_t kPBytes = 64 * 64 * 2;             // 64 rows x 64 keys bf16
+constexpr uint32_t kOffQ = 0;
+constexpr uint32_t kOffK = kOffQ + kQBytes;
+constexpr uint32_t kOffV = kOffK + 2 * kKStage;
+constexpr uint32_t kOffP = kOffV + 2 * kVStage;
+constexpr uint32_t kOffMisc = kOffP + kPBytes;        // 221184
+constexpr uint32_t kMiscBytes = 2048;
+constexpr uint32_t kSmem = kOffMisc + kMiscBytes + 1024;
+static_assert(kSmem <= 232448, "shared-memory plan exceeds the 227 KB per-CTA limit");
+
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kTmemO = 0, kTmemS0 = 256, kTmemS1 = 288;   // S: 32 columns per buffer
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kMInit = -1e30f;
+constexpr float kRescaleThreshold = 6.0f;
+
+struct Misc {
+  uint64_t q_full, k_full[2], v_full[2], s_free[2], p_ready;   // used in the leader CTA
+  uint64_t qk_done[2], pv_done[2];                             // every CTA (one phase per stage use)
+  uint32_t tmem_base, pad;
+  float xbuf[2][128];
+};
+static_assert(sizeof(Misc) <= kMiscBytes, "Misc too large");
+
+struct Params {
+  __nv_bfloat16* out;        // [ng, 128, 512]
+  float* lse;                // [ng, 128]
+  const float* sink;         // [128] per packed row, or null
+  int ng, n_comp, s_raw, G, h_per_q, pos0, window, ratio;
+  float scale_log2;
+};
+
+enum { kSiteQ = 101, kSiteKFull, kSiteVFull, kSiteQkDone, kSitePvDone, kSiteSFree, kSitePReady,
+       kSiteKFree, kSiteVFree, kSitePFree, kSiteEpi };
+
+__device__ int g_status[4];
+
+// key segments of a tile: compressed blocks first, then window blocks
+struct TilePlan {
+  int p0, pref_max, wlo, count_w, nbc, nb;
+};
+__device__ __forceinline__ TilePlan plan_tile(const Params& p, int tile) {
+  TilePlan t;
+  t.p0 = p.pos0 + tile * p.G;
+  const int plast = t.p0 + p.G - 1;
+  t.pref_max = min(plast / p.ratio, p.n_comp);
+  t.wlo = max(0, t.p0 - p.window + 1);
+  t.count_w = plast - t.wlo + 1;
+  t.nbc = (t.pref_max + kBlockKeys - 1) / kBlockKeys;
+  t.nb = t.nbc + (t.count_w + kBlockKeys - 1) / kBlockKeys;
+  return t;
+}
+
+__device__ __forceinline__ void mma_f16_elect(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                              uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, pe;\n\tsetp.ne.b32 p, %4, 0;\n\telect.sync _|pe, 0xffffffff;\n\t"
+      "@pe tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kc32,
+            const __grid_constant__ CUtensorMap map_kr32, const __grid_constant__ CUtensorMap map_kc64,
+            const __grid_constant__ CUtensorMap map_kr64, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t sbase = (raw + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (sbase - raw);
+  Misc& ms = *reinterpret_cast<Misc*>(sm + kOffMisc);
+  int* status = g_status;
+
+  const uint32_t cta = cluster_ctarank();
+  const int tile = blockIdx.x >> 1;
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
+  const TilePlan tp = plan_tile(p, tile);
+  const int nb = tp.nb;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&ms.q_full, 1);
+    mbar_init(&ms.p_ready, 8);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&ms.k_full[i], 1);
+      mbar_init(&ms.v_full[i], 1);
+      mbar_init(&ms.s_free[i], 8);
+      mbar_init(&ms.qk_done[i], 1);
+      mbar_init(&ms.pv_done[i], 1);
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&map_q);
+    tma_prefetch_desc(&map_kc32);
+    tma_prefetch_desc(&map_kr32);
+    tma_prefetch_desc(&map_kc64);
+    tma_prefetch_desc(&map_kr64);
+  }
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 5) {
+    tmem_alloc_pair(&ms.tmem_base, kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ms.tmem_base;
+
+  if (warp < 4) {
+    // ------------------------------------------------------------ softmax + epilogue
+    const int tl = threadIdx.x;                   // TMEM lane
+    const int r = tl & 63, h = tl >> 6;           // row of this CTA, key half (32 columns)
+    const int row = (int)cta * 64 + r;
+    const int q = row / p.h_per_q;                // token of the tile this row belongs to
+    const int pq = tp.p0 + q;
+    const int pref_q = min(pq / p.ratio, p.n_comp);
+    const int lo_q = max(pq - p.window + 1, 0) - tp.wlo;   // window-rank range of this token
+    const int hi_q = pq - tp.wlo + 1;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const float c = p.scale_log2;
+    const uint32_t a_s_free[2] = {mapa(smem_u32(&ms.s_free[0]), 0), mapa(smem_u32(&ms.s_free[1]), 0)};
+    const uint32_t a_p_ready = mapa(smem_u32(&ms.p_ready), 0);
+    float m = kMInit, li = 0.f, real_m = -INFINITY;
+
+    for (int k = 0; k < nb; ++k) {
+      const int s = k & 1;
+      const uint32_t ph = (k >> 1) & 1;
+      mbar_wait(&ms.qk_done[s], ph, status, kSiteQkDone, k);
+      tc_fence_after();
+      float sv[32];
+      tmem_ld32(tmem + lane_base + (s ? kTmemS1 : kTmemS0), sv);
+      tmem_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(a_s_free[s]);
+
+      // columns this thread holds: keys [32h, 32h+32) of the block, as a contiguous valid range
+      int v_lo, v_hi;
+      if (k < tp.nbc) {                       // compressed block: rank = 64k + j < pref_q
+        v_lo = 0;
+        v_hi = pref_q - (k * kBlockKeys + 32 * h);
+      } else {                                // window block: lo_q <= 64(k-nbc) + j < hi_q
+        const int base = (k - tp.nbc) * kBlockKeys + 32 * h;
+        v_lo = lo_q - base;
+        v_hi = hi_q - base;
+      }
+      v_lo = max(v_lo, 0);
+      v_hi = min(v_hi, 32);
+      float cur = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        sv[j] = (j >= v_lo && j < v_hi) ? sv[j] : -INFINITY;
+        cur = fmaxf(cur, sv[j]);
+      }
+      cur *= c;
+      ms.xbuf[k & 1][tl] = cur;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      cur = fmaxf(cur, ms.xbuf[k & 1][tl ^ 64]);
+      real_m = fmaxf(real_m, cur);
+      const bool rescale = __any_sync(0xffffffffu, cur - m > kRescaleThreshold);
+      float new_m = m, scale_old = 1.f;
+      if (rescale) {
+        new_m = fmaxf(cur, m);
+        scale_old = fast_exp2(m - new_m);
+      }
+      m = new_m;
+      li *= scale_old;
+
+      uint32_t pk[16];
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        const float p0 = fast_exp2(fmaf(sv[j], c, -new_m));
+        const float p1 = fast_exp2(fmaf(sv[j + 1], c, -new_m));
+        li += p0 + p1;
+        __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
+        pk[j >> 1] = *reinterpret_cast<uint32_t*>(&b2);
+      }
+      // the single P buffer was last read by PV(k-1)
+      if (k >= 1) mbar_wait(&ms.pv_done[(k - 1) & 1], ((k - 1) >> 1) & 1, status, kSitePFree, k);
+      // P: [64 rows][64 keys] bf16, K-major core matrices: 8-key group cg at cg*1024 + row*16
+      uint8_t* pdst = sm + kOffP + (4 * h) * 1024 + r * 16;
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        *reinterpret_cast<uint4*>(pdst + i * 1024) =
+            make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+      if (rescale && k > 0) {
+        tc_fence_after();                      // PV(k-1) completion was awaited above
+        float o[32];
+#pragma unroll 1
+        for (int cc = 0; cc < 8; ++cc) {
+          const uint32_t ocol = tmem + lane_base + kTmemO + cc * 32;
+          tmem_ld32(ocol, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] *= scale_old;
+          tmem_st32(ocol, o);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(a_p_ready);
+    }
+
+    // epilogue
+    ms.xbuf[nb & 1][tl] = li;
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    li += ms.xbuf[nb & 1][tl ^ 64];
+    if (real_m == -INFINITY) { li = 0.f; m = -INFINITY; }
+    const size_t grow = (size_t)tile * 128 + row;
+    if (h == 0) {
+      float l = __logf(li) + m * kLn2;
+      if (!(li > 0.f)) l = INFINITY;
+      p.lse[grow] = l;
+    }
+    mbar_wait(&ms.pv_done[(nb - 1) & 1], ((nb - 1) >> 1) & 1, status, kSiteEpi, nb);
+    tc_fence_after();
+    float denom = li;
+    if (p.sink != nullptr && li > 0.f) denom += fast_exp2(__ldg(p.sink + row) * kLog2e - m);
+    const bool empty = !(li > 0.f);
+    const float oscale = empty ? 0.f : __fdividef(1.0f, denom);
+    __nv_bfloat16* orow = p.out + grow * kDV + 256 * h;
+    float o[32];
+#pragma unroll 1
+    for (int cc = 0; cc < 8; ++cc) {
+      tmem_ld32(tmem + lane_base + kTmemO + cc * 32, o);
+      tmem_wait_ld();
+      uint32_t w[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float a = empty ? 0.f : o[2 * j] * oscale;
+        const float b = empty ? 0.f : o[2 * j + 1] * oscale;
+        __nv_bfloat162 v2 = __floats2bfloat162_rn(a, b);
+        w[j] = *reinterpret_cast<uint32_t*>(&v2);
+      }
+      uint4* dst = reinterpret_cast<uint4*>(orow + cc * 32);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) dst[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+    }
+    tc_fence_before();
+  } else if (warp == 4) {
+    // ------------------------------------------------------------ TMA producer (tiled loads)
+    if (lane == 0) {
+      const uint32_t a_q_full = mapa(smem_u32(&ms.q_full), 0);
+      const uint32_t a_k_full[2] = {mapa(smem_u32(&ms.k_full[0]), 0), mapa(smem_u32(&ms.k_full[1]), 0)};
+      const uint32_t a_v_full[2] = {mapa(smem_u32(&ms.v_full[0]), 0), mapa(smem_u32(&ms.v_full[1]), 0)};
+      if (cta == 0) mbar_arrive_expect_tx(&ms.q_full, 2 * kQBytes);
+      for (int j = 0; j < kQChunks; ++j)
+        tma_load_2d_pair(sbase + kOffQ + j * kQChunkBytes, &map_q, 64 * j, tile * 128 + (int)cta * 64,
+                         a_q_full);
+      for (int k = 0; k < nb; ++k) {
+        const int s = k & 1;
+        const uint32_t ph = (k >> 1) & 1;
+        const bool comp = k < tp.nbc;
+        const int row0 = comp ? k * kBlockKeys : tp.wlo + (k - tp.nbc) * kBlockKeys;
+        const CUtensorMap* m32 = comp ? &map_kc32 : &map_kr32;
+        const CUtensorMap* m64 = comp ? &map_kc64 : &map_kr64;
+        if (k >= 2) mbar_wait(&ms.qk_done[s], ph ^ 1, status, kSiteKFree, k);   // K stage free
+        if (cta == 0) mbar_arrive_expect_tx(&ms.k_full[s], 2 * kKStage);
+        for (int j = 0; j < kQChunks; ++j)
+          tma_load_2d_pair(sbase + kOffK + s * kKStage + j * kKChunkBytes, m32, 64 * j,
+                           row0 + 32 * (int)cta, a_k_full[s]);
+        // V stage s was last read by PV(k-2)
+        if (k >= 2) mbar_wait(&ms.pv_done[s], ph ^ 1, status, kSiteVFree, k);
+        if (cta == 0) mbar_arrive_expect_tx(&ms.v_full[s], 2 * kVStage);
+        for (int j = 0; j < 4; ++j)
+          tma_load_2d_pair(sbase + kOffV + s * kVStage + j * kVChunkBytes, m64,
+                           256 * (int)cta + 64 * j, row0, a_v_full[s]);
+      }
+    }
+  } else if (cta == 0) {
+    // ------------------------------------------------------------ MMA issue (whole warp, elected lane)
+    constexpr uint32_t idesc_qk = umma_idesc(1, 1, false, false, 128, 64);
+    constexpr uint32_t idesc_pv = umma_idesc(1, 1, false, true, 128, 256);
+    const uint32_t a_qk_done_peer[2] = {mapa(smem_u32(&ms.qk_done[0]), 1), mapa(smem_u32(&ms.qk_done[1]), 1)};
+    const uint32_t a_pv_done_peer[2] = {mapa(smem_u32(&ms.pv_done[0]), 1), mapa(smem_u32(&ms.pv_done[1]), 1)};
+    mbar_wait(&ms.q_full, 0, status, kSiteQ, 0);
+    __syncwarp();
+    for (int k = 0; k <= nb; ++k) {
+      if (k < nb) {
+        const int s = k & 1;
+        const uint32_t ph = (k >> 1) & 1;
+        mbar_wait(&ms.k_full[s], ph, status, kSiteKFull, k);
+        if (k >= 2) mbar_wait(&ms.s_free[s], ph ^ 1, status, kSiteSFree, k);
+        __syncwarp();
+        tc_fence_after();
+        const uint32_t d = tmem + (s ? kTmemS1 : kTmemS0);
+        const uint64_t ad0 = umma_desc(sbase + kOffQ, 16, 1024, kSwz128);
+        const uint64_t bd0 = umma_desc(sbase + kOffK + s * kKStage, 16, 1024, kSwz128);
+#pragma unroll
+        for (int j = 0; j < kQChunks; ++j) {
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            mma_f16_elect(d, ad0 + (uint64_t)(j * (kQChunkBytes >> 4) + kk * 2),
+                          bd0 + (uint64_t)(j * (kKChunkBytes >> 4) + kk * 2), idesc_qk,
+                          (j | kk) ? 1u : 0u);
+        }
+        mma_commit_pair_elect(smem_u32(&ms.qk_done[s]));
+        mma_commit_pair_elect(a_qk_done_peer[s]);
+      }
+      if (k > 0) {
+        const int kb = k - 1;
+        const int s = kb & 1;
+        mbar_wait(&ms.p_ready, kb & 1, status, kSitePReady, kb);
+        mbar_wait(&ms.v_full[s], (kb >> 1) & 1, status, kSiteVFull, kb);
+        __syncwarp();
+        tc_fence_after();
+        const uint64_t ad0 = umma_desc(sbase + kOffP, 1024, 128, kSwzNone);
+        const uint64_t bd0 = umma_desc(sbase + kOffV + s * kVStage, kVChunkBytes, 1024, kSwz128);
+#pragma unroll
+        for (int nbk = 0; nbk < 2; ++nbk) {
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            mma_f16_elect(tmem + kTmemO + nbk * 128, ad0 + (uint64_t)(ks * (2048 >> 4)),
+                          bd0 + (uint64_t)(nbk * (2 * kVChunkBytes >> 4) + ks * (2048 >> 4)), idesc_pv,
+                          (kb | ks) ? 1u : 0u);
+        }
+        mma_commit_pair_elect(smem_u32(&ms.pv_done[s]));
+        mma_commit_pair_elect(a_pv_done_peer[s]);
+      }
+    }
+  }
+
+  __syncthreads();
+  __syncwarp();
+  cluster_sync_all();
+  if (warp == 5) tmem_dealloc_pair(tmem, kTmemCols);
+  if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&status[3], 1);
+}
+
+}  // namespace dsv4
+}  // namespace lt
+
+// DSv4 packed BF16 attention over (compressed prefix, sliding window).  Replaces the
+// reference operator dsv4_masked_mla_bf16 (kernels/b200/dsa/litedsa_dsv4.cu:50-55) for
+// callers whose two key ranges are contiguous: instead of a gathered union index list plus
+// per-token rank ranges it takes the two KV tensors and the first query position.
+extern "C" int litedsa_dsv4_c128a_bf16(const void* q, const void* kv_comp, const void* kv_raw,
+                                       int ng, int h_per_q, int n_comp, int s_raw, int pos0,
+                                       int window, int ratio, float sm_scale,
+                                       const float* attn_sink, void* out, float* lse,
+                                       int64_t q_row_stride, int64_t kc_row_stride,
+                                       int64_t kr_row_stride, void* stream) {
+  using namespace lt;
+  using namespace lt::dsv4;
+  if (!q || !kv_raw || !out || !lse) return LITEDSA_ERR_ARG;
+  if (n_comp > 0 && !kv_comp) return LITEDSA_ERR_ARG;
+  if (ng <= 0 || s_raw <= 0 || n_comp < 0 || pos0 < 0 || window <= 0 || ratio <= 0)
+    return LITEDSA_ERR_SHAPE;
+  if (h_per_q <= 0 || 128 % h_per_q != 0 || 128 / h_per_q > 16) return LITEDSA_ERR_SHAPE;
+  const int G = 128 / h_per_q;
+  if ((int64_t)pos0 + (int64_t)ng * G > s_raw) return LITEDSA_ERR_SHAPE;   // queries sit inside the cache
+  if (window + G - 1 > 8 * kBlockKeys * 64) return LITEDSA_ERR_UNSUPPORTED;
+  // strides are in ELEMENTS (bf16); TMA needs 16-byte aligned bases and pitches
+  if (q_row_stride < kD || kr_row_stride < kD || (q_row_stride % 8) || (kr_row_stride % 8) ||
+      (n_comp > 0 && (kc_row_stride < kD || (kc_row_stride % 8))))
+    return LITEDSA_ERR_UNSUPPORTED;
+  if (((uintptr_t)q | (uintptr_t)kv_raw | (uintptr_t)kv_comp | (uintptr_t)out) & 15)
+    return LITEDSA_ERR_UNSUPPORTED;
+  const void* kc = n_comp > 0 ? kv_comp : kv_raw;      // never dereferenced when n_comp == 0
+  const uint64_t kc_rows = n_comp > 0 ? (uint64_t)n_comp : 1;
+  const int64_t kc_pitch = n_comp > 0 ? kc_row_stride : kr_row_stride;
+  CUtensorMap mq, mkc32, mkr32, mkc64, mkr64;
+  const auto BF = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  if (!make_map_2d(&mq, q, BF, kD, (uint64_t)ng * 128, (uint64_t)q_row_stride * 2, 64, 64) ||
+      !make_map_2d(&mkc32, kc, BF, kD, kc_rows, (uint64_t)kc_pitch * 2, 64, 32) ||
+      !make_map_2d(&mkr32, kv_raw, BF, kD, (uint64_t)s_raw, (uint64_t)kr_row_stride * 2, 64, 32) ||
+      !make_map_2d(&mkc64, kc, BF, kD, kc_rows, (uint64_t)kc_pitch * 2, 64, 64) ||
+      !make_map_2d(&mkr64, kv_raw, BF, kD, (uint64_t)s_raw, (uint64_t)kr_row_stride * 2, 64, 64))
+    return LITEDSA_ERR_CUDA;
+  Params p;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out); p.lse = lse; p.sink = attn_sink;
+  p.ng = ng; p.n_comp = n_comp; p.s_raw = s_raw; p.G = G; p.h_per_q = h_per_q; p.pos0 = pos0;
+  p.window = window; p.ratio = ratio; p.scale_log2 = sm_scale * kLog2e;
+  if (cudaFuncSetAttribute(dsv4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) !=
+      cudaSuccess)
+    return LITEDSA_ERR_CUDA;
+  dsv4_kernel<<<2 * ng, kThreads, kSmem, reinterpret_cast<cudaStream_t>(stream)>>>(
+      mq, mkc32, mkr32, mkc64, mkr64, p);
+  return cudaGetLastError() == cudaSuccess ? LITEDSA_OK : LITEDSA_ERR_CUDA;
+}
+
+// Status word of the DSv4 kernel (same meaning as litedsa_attn_status).
+extern "C" int litedsa_dsv4_status(int* out4_host, int reset) {
+  using namespace lt::dsv4;
+  if (out4_host && cudaMemcpyFromSymbol(out4_host, g_status, sizeof(int) * 4) != cudaSuccess)
+    return LITEDSA_ERR_CUDA;
+  if (reset) {
+    const int z[4] = {0, 0, 0, 0};
+    if (cudaMemcpyToSymbol(g_status, z, sizeof(z)) != cudaSuccess) return LITEDSA_ERR_CUDA;
+  }
+  return (out4_host && out4_host[0] != 0) ? LITEDSA_ERR_TIMEOUT : LITEDSA_OK;
+}
