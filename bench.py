@@ -162,6 +162,51 @@ def config_dict(w, args):
             "parallelism": f"dp{args.gpus} (query-token blocks; KV replicated; NCCL all-gather of out)"}
 
 
+def run_dsv4(args, w):
+    """Config 3 (DSv4 packed BF16 two-range attention), single GPU: a secondary bench line."""
+    from litetopk_b200 import api
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    q, kc, kr = synth.make_dsv4(w, seed=1, device=dev)
+    pos0 = w.pos0
+    step = lambda: api.dsv4_c128a_bf16(q, kc, kr, pos0, synth.SM_SCALE, window=w.window, ratio=w.ratio)
+    api.dsv4_status(reset=True)
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    with ClockSampler(0) as clk:
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    if api.dsv4_status()[0] != 0:
+        raise SystemExit("device-side wait expired")
+    pairs = synth.attended_pairs(w)
+    flop = pairs * synth.FLOP_PER_PAIR
+    peaks = load_peaks()
+    ach = flop / (ms * 1e-3) / 1e12
+    # bytes a tile reads: its compressed prefix and window rows once (bf16, 576 dims)
+    G = w.group
+    p_last = torch.arange(w.pos0 + G - 1, w.pos0 + w.tokens, G, dtype=torch.int64)
+    rows = int((torch.clamp(p_last // w.ratio, max=w.n_compressed) + w.window + G - 1).sum())
+    line = {"metric": METRIC, "value": w.tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{w.name}: DSv4 packed BF16 attention, {w.tokens} query tokens at the tail of a "
+                                   f"{w.s_kv}-token context, {w.heads} heads, compressed prefix (<= {w.n_compressed} "
+                                   f"entries, ratio {w.ratio}) + window {w.window}", "seed": 1},
+            "effective_tflops": ach,
+            "roofline": {"kernel": "dsv4_kernel", "bound": "tensor", "achieved": ach, "peak": peaks["bf16_tflops"],
+                         "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops"], "traffic": None,
+                         "peak_source": f"bf16 dense of {peaks['source']}",
+                         "kv_bytes_per_step": rows * 1152, "kv_gbs": rows * 1152 / (ms * 1e-3) / 1e9},
+            "gpu_launches": args.steps, "clocks": clk.summary(), "cpu_baseline": None, "e2e": None}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -180,8 +225,8 @@ def main():
     w = synth.CONFIGS[args.config]
     if args.tokens:
         w = synth.scaled(w, tokens=args.tokens)
-    if w.kind != "fp8":
-        raise SystemExit("bench.py times the FP8 union + masked MLA path (configs c0, c1, c2, c4)")
+    if w.kind == "dsv4":
+        return run_dsv4(args, w)
     if args.impl == "reference":
         return run_reference(args, w)
 
@@ -211,37 +256,39 @@ def main():
     u = torch.empty((ng, cap), dtype=torch.int32, device=dev)
     cnt = torch.empty((ng,), dtype=torch.int32, device=dev)
     msk = torch.empty((ng, G, cap // 32), dtype=torch.int32, device=dev)
-    out_all = torch.empty((world, ng, 128, 512), dtype=torch.bfloat16, device=dev)
-    out = out_all[rank]
+    out = torch.empty((ng, 128, 512), dtype=torch.bfloat16, device=dev) if world == 1 else None
     lse = torch.empty((ng, 128), dtype=torch.float32, device=dev)
     sm = synth.SM_SCALE * qs * ks
     n_chunks = 4 if world > 1 else 1
-    bounds = [ng * i // n_chunks for i in range(n_chunks + 1)]
-    comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
+    gatherer = None
+    if world > 1:
+        from litetopk_b200 import dist as ldist
+        gatherer = ldist.ChunkedAllGather(ng, (128, 512), torch.bfloat16, dev, n_chunks=n_chunks)
     launches = [0]
     attn_events = []
+    timed_flag = [False]
+    gather_on = [True]
+
+    def attn_chunk(a, b, dst):
+        if timed_flag[0]:
+            e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+            e0.record()
+        api.masked_mla_fp8_out(q8[a:b], kv8, u[a:b], sm, ks, cnt[a:b], msk[a:b], w.heads, dst, None, lse[a:b])
+        launches[0] += 1
+        if timed_flag[0]:
+            e1.record(); attn_events.append((e0, e1, b - a))
 
     def step(timed=False):
+        timed_flag[0] = timed
         api.union_qm_out(idx, u, cnt, msk, None, None, 1, w.s_kv)
         launches[0] += 1
-        for i in range(n_chunks):
-            a, b = bounds[i], bounds[i + 1]
-            if timed:
-                e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
-                e0.record()
-            api.masked_mla_fp8_out(q8[a:b], kv8, u[a:b], sm, ks, cnt[a:b], msk[a:b], w.heads, out[a:b],
-                                   None, lse[a:b])
-            launches[0] += 1
-            if timed:
-                e1.record(); attn_events.append((e0, e1, b - a))
-            if world > 1:
-                comm_stream.wait_stream(torch.cuda.current_stream())
-                with torch.cuda.stream(comm_stream):
-                    # gather this chunk of every rank's output: out_all[:, a:b]
-                    parts = [out_all[r, a:b] for r in range(world)]
-                    dist.all_gather(parts, out[a:b])
-        if world > 1:
-            torch.cuda.current_stream().wait_stream(comm_stream)
+        if world > 1 and gather_on[0]:
+            ldist.sharded_attention(attn_chunk, gatherer)
+        elif world > 1:
+            for i in range(gatherer.n_chunks):
+                attn_chunk(gatherer.bounds[i], gatherer.bounds[i + 1], gatherer.local(i))
+        else:
+            attn_chunk(0, ng, out)
 
     def barrier():
         if world > 1:
@@ -271,6 +318,20 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, attn_ms = float(t[0]), float(t[1])
     launches_per_step = launches[0] // args.steps
+    ms_compute_only = None
+    if world > 1:   # the same steps without the collective: what the all-gather costs
+        gather_on[0] = False
+        barrier()
+        c0 = torch.cuda.Event(enable_timing=True); c1 = torch.cuda.Event(enable_timing=True)
+        c0.record()
+        for _ in range(args.steps):
+            step()
+        c1.record()
+        barrier()
+        t = torch.tensor([c0.elapsed_time(c1) / args.steps], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_compute_only = float(t[0])
+        gather_on[0] = True
 
     # ---- end to end through the public API with host buffers (rank-local), copies inside the timing
     q_host = q.cpu().pin_memory(); idx_host = idx.cpu().pin_memory()
@@ -315,6 +376,10 @@ def main():
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "e4m3",
         "data": "synthetic", "config": config_dict(w, args),
         "effective_tflops": world * flop / (ms * 1e-3) / 1e12,
+        "compute_only": None if ms_compute_only is None else {
+            "ms_per_step": ms_compute_only, "value": world * w.tokens / (ms_compute_only * 1e-3),
+            "note": "same steps with the NCCL all-gather of the outputs switched off"},
+        "all_gather_bytes_per_rank_per_step": (world - 1) * ng * 128 * 512 * 2,
         "roofline": {"kernel": "masked_mla_fp8_kernel", "bound": "tensor", "achieved": achieved,
                      "peak": fp8_peak, "unit": "TFLOP/s", "frac": achieved / fp8_peak,
                      "traffic": ATTN_DRAM_TRAFFIC_BYTES,
