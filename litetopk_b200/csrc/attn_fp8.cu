@@ -378,18 +378,27 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
       // instruction issues the warp's ten gathers of a block
       const int quad = pw + 8 * (lane / 5), chunk = lane % 5;
       const bool active = lane < 10;
+      // lanes 16..23 gather the V tile: row quads pw + 8*t (t < 4) of all 128 keys, this CTA's
+      // two 128-byte value chunks
+      const int vl = lane - 16;
+      const bool v_active = vl >= 0 && vl < 8;
+      const int v_quad = pw + 8 * (vl >> 1), v_chunk = vl & 1;
+      const int32_t* v_idx_row = p.indices + (size_t)tile * p.idx_stride + 4 * (v_active ? v_quad : pw);
+      int4 vc0 = __ldg(reinterpret_cast<const int4*>(v_idx_row));
       const int32_t* idx_row = p.indices + (size_t)tile * p.idx_stride + 64 * cta + 4 * (active ? quad : pw);
       int4 c0 = __ldg(reinterpret_cast<const int4*>(idx_row));
       for (int k = 0; k < nb; ++k) {
         const int s = k & 1;
         const uint32_t ph = (k >> 1) & 1;
-        int4 n0 = c0;
-        if (k + 1 < nb) n0 = __ldg(reinterpret_cast<const int4*>(idx_row + (size_t)(k + 1) * kBlockKeys));
+        int4 n0 = c0, vn0 = vc0;
+        if (k + 1 < nb) {
+          n0 = __ldg(reinterpret_cast<const int4*>(idx_row + (size_t)(k + 1) * kBlockKeys));
+          vn0 = __ldg(reinterpret_cast<const int4*>(v_idx_row + (size_t)(k + 1) * kBlockKeys));
+        }
         if (pw == 0) LT_TS(1, k, 0);
         if (k >= 2) {
           // stage s held block k-2: QK(k-2) must have read it and its V copies must be out
           mbar_wait(&ms.qk_done[s], ph ^ 1, status, kSiteKFree, k);
-          mbar_wait(&ms.k_copied[s], ph ^ 1, status, kSiteKCopied, k);
         }
         __syncwarp();
         if (pw == 0) LT_TS(1, k, 1);
@@ -398,8 +407,16 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
           tma_gather4(sbase + kOffK + s * kKStage + (uint32_t)quad * 512 + chunk * kChunkBytes, &map_kv,
                       128 * chunk, c0, smem_u32(&ms.k_land[s]));
         __syncwarp();
+        // V stage s was last read by PV(k-2)
+        if (k >= 2) mbar_wait(&ms.pv_done[s], ph ^ 1, status, kSiteVFree, k);
+        __syncwarp();
+        if (pw == 0 && lane == 0) mbar_arrive_expect_tx(&ms.v_land[s], kVStage);
+        if (v_active)
+          tma_gather4(sbase + kOffV + s * kVStage + v_chunk * kVChunk + (uint32_t)v_quad * 512, &map_kv,
+                      256 * (int)cta + 128 * v_chunk, vc0, smem_u32(&ms.v_land[s]));
+        __syncwarp();
         if (pw == 0) LT_TS(1, k, 2);
-        c0 = n0;
+        c0 = n0; vc0 = vn0;
       }
     }
   } else {
@@ -497,19 +514,6 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         mbar_wait(&ms.k_land[s], ph, status, kSiteRelayK, k);
         LT_TS(3, k, 1);
         if (cta == 1) mbar_arrive_cluster(a_k_peer[s]);
-        if (k >= 2) mbar_wait(&ms.pv_done[s], ph ^ 1, status, kSiteVFree, k);   // V stage s free
-        LT_TS(3, k, 2);
-        mbar_arrive_expect_tx(&ms.v_land[s], kVStage);
-        const uint32_t src = sbase + kOffK + s * kKStage;
-        const uint32_t vdst = sbase + kOffV + s * kVStage + cta * (64 * 128);
-        const uint32_t vbar = smem_u32(&ms.v_land[s]);
-#pragma unroll
-        for (uint32_t d = 0; d < 2; ++d) {
-#pragma unroll
-          for (uint32_t nbk = 0; nbk < 2; ++nbk)
-            bulk_copy_s2s(mapa(vdst + nbk * kVChunk, d), src + (2 * d + nbk) * kChunkBytes,
-                          kChunkBytes, mapa(vbar, d));
-        }
         LT_TS(3, k, 3);
       }
     }
@@ -524,8 +528,6 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         LT_TS(4, k, 0);
         // all four copies INTO this CTA are done: tell both CTAs' producers (K stages are
         // sources of those copies) and, from the peer, the MMA thread
-        mbar_arrive_cluster(mapa(smem_u32(&ms.k_copied[s]), 0));
-        mbar_arrive_cluster(mapa(smem_u32(&ms.k_copied[s]), 1));
         if (cta == 1) mbar_arrive_cluster(a_v_peer[s]);
       }
     }
