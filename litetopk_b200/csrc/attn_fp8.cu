@@ -67,6 +67,8 @@ struct Misc {
   // in every CTA
   uint64_t k_land[2], v_land[2], k_copied[2], qk_done[2], pv_done[2], valid_ready[2], valid_free[2];
   uint64_t m_pub[2];                // running max of block k published by softmax group k%2
+  uint64_t q_free;                  // all QK^T of the current tile are complete (Q tile reusable)
+  uint64_t o_free;                  // leader CTA: the tile's O has been read out of TMEM
   uint32_t valid[2][4];             // 128 validity bits per stage
   uint32_t tmem_base;
   uint32_t pad;
@@ -92,7 +94,7 @@ struct AttnParams {
 // wait sites reported in the status word
 enum { kSiteQ = 1, kSiteKLand, kSiteKPeer, kSiteVLand, kSiteVPeer, kSiteQkDone, kSitePvDone,
        kSiteSFree, kSitePReady, kSiteValidReady, kSiteValidFree, kSiteKFree, kSiteKCopied,
-       kSiteVFree, kSitePFree, kSiteEpi, kSiteRelayK, kSiteRelayV, kSiteMPub, kSiteMmaIdle };
+       kSiteVFree, kSitePFree, kSiteEpi, kSiteRelayK, kSiteRelayV, kSiteMPub, kSiteMmaIdle, kSiteQFree, kSiteOFree };
 
 // status[0] first failing wait site, [1] block, [2] iteration, [3] launches completed
 __device__ int g_attn_status[4];
@@ -116,29 +118,34 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
   Misc& ms = *reinterpret_cast<Misc*>(sm + kOffMisc);
   int* status = g_attn_status;
 
+  // Persistent: each cluster walks tiles cid, cid + #clusters, ...  Every role runs the same
+  // tile loop; stages, buffers and barrier phases are indexed by the cluster-wide running
+  // block number kb, so the next tile's Q / K / V loads and first QK^T overlap the previous
+  // tile's last softmax blocks and its epilogue.
   const uint32_t cta = cluster_ctarank();
-  const int tile = blockIdx.x >> 1;
+  const int cid = blockIdx.x >> 1, ncl = gridDim.x >> 1;
   // broadcast so the compiler knows the role index is warp-uniform
   const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
-  int count = p.counts ? p.counts[tile] : p.cap;
-  count = min(max(count, 0), p.cap);
-  const int nb = max((count + kBlockKeys - 1) / kBlockKeys, 1);
+  auto tile_count = [&](int tile) -> int {
+    const int c = p.counts ? p.counts[tile] : p.cap;
+    return min(max(c, 0), p.cap);
+  };
+  auto blocks_of = [&](int count) -> int { return max((count + kBlockKeys - 1) / kBlockKeys, 1); };
   long long* ts = nullptr;
   bool ts_on = false;
-  if (kDebug && p.dbg) {
-    ts = reinterpret_cast<long long*>(p.dbg + (size_t)p.cap * 128 + 128 * 512 + 256);
-    ts_on = (tile == p.ng / 2) && lane == 0;
-  }
+  if (kDebug && p.dbg) ts = reinterpret_cast<long long*>(p.dbg + (size_t)p.cap * 128 + 128 * 512 + 256);
 
   if (threadIdx.x == 0) {
     mbar_init(&ms.q_full, 1);
+    mbar_init(&ms.q_free, 1);
+    mbar_init(&ms.o_free, 2 * kSoftmaxWarps);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&ms.k_peer[i], 1);
       mbar_init(&ms.v_peer[i], 1);
       mbar_init(&ms.s_free[i], 8);        // 4 warps of one softmax group x 2 CTAs
       mbar_init(&ms.p_ready[i], 8);
       mbar_init(&ms.k_land[i], 1);
-      mbar_init(&ms.v_land[i], 1);
+      mbar_init(&ms.v_land[i], 3);       // expect_tx arrival + the two copy warps
       mbar_init(&ms.k_copied[i], 2);
       mbar_init(&ms.qk_done[i], 1);
       mbar_init(&ms.pv_done[i], 1);
@@ -160,267 +167,287 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = ms.tmem_base;
-  const uint32_t peer = cta ^ 1u;
 
   if (warp < kSoftmaxWarps) {
     // ------------------------------------------------------------ softmax + epilogue
-    // Two groups of four warps work on alternate key blocks (group g: blocks g, g+2, ...), so
-    // two blocks are in flight and the latencies of one chain (TMEM load, exchanges, fences)
-    // hide behind the other.  Within a group, thread = TMEM lane tl: tile row r = tl % 64,
-    // key half h = tl / 64 (64 S columns each).  The only state that crosses groups is the
-    // running max m, handed over through shared memory right after each block's row maxima
-    // are known; the row sum l is kept per group relative to the m of the group's latest
-    // block and merged at the end.
-
+    // Two groups of four warps work on alternate key blocks (group g: blocks with kb % 2 == g),
+    // so two blocks are in flight and the latencies of one chain (TMEM load, exchanges,
+    // fences) hide behind the other.  Within a group, thread = TMEM lane tl: tile row
+    // r = tl % 64, key half h = tl / 64 (64 S columns each).  The only state that crosses
+    // groups is the running max m, handed over through shared memory right after each
+    // block's row maxima are known; the row sum l is kept per group relative to the m of the
+    // group's latest block and merged at the end of the tile.
     const int g = warp >> 2;                      // softmax group = block parity it serves
     const int tl = ((warp & 3) << 5) | lane;
     const int r = tl & 63, h = tl >> 6;
     const int row = (int)cta * 64 + r;            // row of the 128-row tile
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const int capw = p.cap >> 5;
-    const uint32_t* mrow = p.memb + ((size_t)tile * p.G + row / p.h_per_q) * capw + 2 * h;
     const float c = p.scale_log2;
-    float m_mine = kMInit;      // the running max my row sum is relative to
-    float li = 0.f, real_m = -INFINITY;
     const uint32_t a_s_free = mapa(smem_u32(&ms.s_free[g]), 0);
     const uint32_t a_p_ready = mapa(smem_u32(&ms.p_ready[g]), 0);
+    const uint32_t a_o_free = mapa(smem_u32(&ms.o_free), 0);
     const uint32_t scol = tmem + lane_base + (g ? kTmemS1 : kTmemS0);
-    uint2 mk = make_uint2(0u, 0u);
-    if (g < nb) mk = __ldg(reinterpret_cast<const uint2*>(mrow + (size_t)g * 4));
+    int kb0 = 0;
 
-    for (int k = g; k < nb; k += 2) {
-      const uint32_t ph = (k >> 1) & 1;
-      uint2 mk_next = mk;
-      if (k + 2 < nb) mk_next = __ldg(reinterpret_cast<const uint2*>(mrow + (size_t)(k + 2) * 4));
+    for (int tile = cid; tile < p.ng; tile += ncl) {
+      const int nb = blocks_of(tile_count(tile));
+      if (kDebug) ts_on = ts != nullptr && (tile == p.ng / 2) && lane == 0;
+      const uint32_t* mrow = p.memb + ((size_t)tile * p.G + row / p.h_per_q) * capw + 2 * h;
+      float m_mine = kMInit;      // the running max my row sum is relative to
+      float li = 0.f, real_m = -INFINITY;
+      const int k_first = (g - kb0) & 1;          // first local block with (kb0 + k) % 2 == g
+      uint2 mk = make_uint2(0u, 0u);
+      if (k_first < nb) mk = __ldg(reinterpret_cast<const uint2*>(mrow + (size_t)k_first * 4));
 
-      if ((warp & 3) == 0) LT_TS(0, k, 0);
-      mbar_wait(&ms.qk_done[g], ph, status, kSiteQkDone, k);
-      if ((warp & 3) == 0) LT_TS(0, k, 1);
+      for (int k = k_first; k < nb; k += 2) {
+        const int kb = kb0 + k;
+        const uint32_t ph = (kb >> 1) & 1;
+        uint2 mk_next = mk;
+        if (k + 2 < nb) mk_next = __ldg(reinterpret_cast<const uint2*>(mrow + (size_t)(k + 2) * 4));
+
+        if ((warp & 3) == 0) LT_TS(0, k, 0);
+        mbar_wait(&ms.qk_done[g], ph, status, kSiteQkDone, k);
+        if ((warp & 3) == 0) LT_TS(0, k, 1);
+        tc_fence_after();
+        float sv[64];
+        tmem_ld32(scol, sv);
+        tmem_ld32(scol + 32, sv + 32);
+        tmem_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(a_s_free);
+
+        if (kDebug && p.dbg && tile == 0) {
+          float* d = p.dbg + ((size_t)k * 128 + row) * 128 + 64 * h;
+#pragma unroll
+          for (int j = 0; j < 64; ++j) d[j] = sv[j];
+        }
+
+        mbar_wait(&ms.valid_ready[g], ph, status, kSiteValidReady, k);
+        const uint32_t v0 = ms.valid[g][2 * h] & mk.x, v1 = ms.valid[g][2 * h + 1] & mk.y;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ms.valid_free[g]);
+        mk = mk_next;
+        if ((warp & 3) == 0) LT_TS(0, k, 2);
+
+        float cur = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          sv[j] = ((v0 >> j) & 1u) ? sv[j] : -INFINITY;
+          sv[32 + j] = ((v1 >> j) & 1u) ? sv[32 + j] : -INFINITY;
+          cur = fmaxf(cur, fmaxf(sv[j], sv[32 + j]));
+        }
+        cur *= c;
+        float* xb = ms.xbuf[g][ph];
+        xb[tl] = cur;
+        if (g == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+        else asm volatile("bar.sync 2, 128;" ::: "memory");
+        cur = fmaxf(cur, xb[tl ^ 64]);
+        if ((warp & 3) == 0) LT_TS(0, k, 3);
+        real_m = fmaxf(real_m, cur);
+        // running max after block k-1 of this tile comes from the other group
+        float m_prev = kMInit;
+        if (k > 0) {
+          mbar_wait(&ms.m_pub[g ^ 1], ((kb - 1) >> 1) & 1, status, kSiteMPub, k);
+          m_prev = ms.mshare[g ^ 1][tl];
+        }
+        const bool rescale = __any_sync(0xffffffffu, cur - m_prev > kRescaleThreshold);
+        const float new_m = rescale ? fmaxf(cur, m_prev) : m_prev;
+        ms.mshare[g][tl] = new_m;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ms.m_pub[g]);
+        li *= fast_exp2(m_mine - new_m);
+        m_mine = new_m;
+        if ((warp & 3) == 0) LT_TS(0, k, 4);
+
+        const float nm = -new_m + kPScaleLog2;
+        uint32_t pk[16];
+#pragma unroll
+        for (int j = 0; j < 64; j += 4) {
+          float2 d0, d1;
+          d0.x = fast_exp2(fmaf(sv[j], c, nm));
+          d0.y = fast_exp2(fmaf(sv[j + 1], c, nm));
+          d1.x = fast_exp2(fmaf(sv[j + 2], c, nm));
+          d1.y = fast_exp2(fmaf(sv[j + 3], c, nm));
+          li += d0.x + d0.y;
+          li += d1.x + d1.y;
+          const uint32_t lo = __nv_cvt_float2_to_fp8x2(d0, __NV_SATFINITE, __NV_E4M3);
+          const uint32_t hi = __nv_cvt_float2_to_fp8x2(d1, __NV_SATFINITE, __NV_E4M3);
+          pk[j >> 2] = lo | (hi << 16);
+        }
+        if ((warp & 3) == 0) LT_TS(0, k, 5);
+        // P buffer g was last read by the PV of block kb-2
+        if (kb >= 2) mbar_wait(&ms.pv_done[g], ph ^ 1, status, kSitePFree, k);
+        uint8_t* pdst = sm + kOffP + g * kPBytes + (4 * h) * 1024 + r * 16;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          *reinterpret_cast<uint4*>(pdst + i * 1024) =
+              make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+
+        if (rescale && k > 0) {
+          // O holds blocks [0, k) relative to m_prev: bring it to new_m once PV(k-1) is complete
+          mbar_wait(&ms.pv_done[g ^ 1], ((kb - 1) >> 1) & 1, status, kSitePvDone, k);
+          tc_fence_after();
+          const float f = fast_exp2(m_prev - new_m);
+          float o[32];
+#pragma unroll 1
+          for (int cc = 0; cc < 8; ++cc) {
+            const uint32_t ocol = tmem + lane_base + kTmemO + cc * 32;
+            tmem_ld32(ocol, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) o[j] *= f;
+            tmem_st32(ocol, o);
+          }
+          tmem_wait_st();
+          tc_fence_before();
+        }
+        if ((warp & 3) == 0) LT_TS(0, k, 6);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(a_p_ready);
+        if ((warp & 3) == 0) LT_TS(0, k, 7);
+      }
+
+      // end of tile: merge the two groups' row sums (each relative to its own latest running max)
+      const int t = threadIdx.x;                    // 0..255 = g*128 + tl
+      ms.fin[0][t] = li;
+      ms.fin[1][t] = real_m;
+      ms.fin[2][t] = m_mine;
+      asm volatile("bar.sync 3, 256;" ::: "memory");
+      const int kbl = kb0 + nb - 1;                 // last block of the tile
+      const int last_g = kbl & 1;
+      float m = ms.fin[2][last_g * 128 + tl];       // running max after the last block
+      float lsum = 0.f;
+      real_m = -INFINITY;
+#pragma unroll
+      for (int gg = 0; gg < 2; ++gg) {
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const int o = gg * 128 + hh * 64 + r;
+          lsum += ms.fin[0][o] * fast_exp2(ms.fin[2][o] - m);
+          real_m = fmaxf(real_m, ms.fin[1][o]);
+        }
+      }
+      li = lsum;
+      if (real_m == -INFINITY) { li = 0.f; m = -INFINITY; }
+      const size_t grow = (size_t)tile * 128 + row;
+      if (g == 0 && h == 0) {
+        float l = __logf(li) - kPScaleLn + m * kLn2;
+        if (!(li > 0.f)) l = INFINITY;
+        p.lse[grow] = l;
+        if (p.max_logits) p.max_logits[grow] = real_m * kLn2;
+      }
+      mbar_wait(&ms.pv_done[kbl & 1], (kbl >> 1) & 1, status, kSiteEpi, nb);
       tc_fence_after();
-      float sv[64];
-      tmem_ld32(scol, sv);
-      tmem_ld32(scol + 32, sv + 32);
-      tmem_wait_ld();
+      const bool empty = !(li > 0.f);
+      const float oscale = empty ? 0.f : __fdividef(p.out_scale, li);
+      // group g writes dims [256h + 128g, +128) of its row
+      __nv_bfloat16* orow = p.out + grow * kDV + 256 * h + 128 * g;
+      float o[32];
+#pragma unroll 1
+      for (int cc = 0; cc < 4; ++cc) {
+        tmem_ld32(tmem + lane_base + kTmemO + g * 128 + cc * 32, o);
+        tmem_wait_ld();
+        if (kDebug && p.dbg && tile == 0) {
+          float* d = p.dbg + (size_t)p.cap * 128 + (size_t)row * 512 + 256 * h + 128 * g + cc * 32;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) d[j] = o[j];
+        }
+        uint32_t w[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float a = empty ? 0.f : o[2 * j] * oscale;
+          const float b = empty ? 0.f : o[2 * j + 1] * oscale;
+          __nv_bfloat162 v2 = __floats2bfloat162_rn(a, b);
+          w[j] = *reinterpret_cast<uint32_t*>(&v2);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(orow + cc * 32);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) dst[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+      }
+      if (kDebug && p.dbg && tile == 0 && g == 0 && h == 0) {
+        float* d = p.dbg + (size_t)p.cap * 128 + 128 * 512;
+        d[row] = m;
+        d[128 + row] = li;
+      }
+      // O has been read: the next tile's first PV may overwrite it
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(a_s_free);
-
-      if (kDebug && p.dbg && tile == 0) {
-        float* d = p.dbg + ((size_t)k * 128 + row) * 128 + 64 * h;
-#pragma unroll
-        for (int j = 0; j < 64; ++j) d[j] = sv[j];
-      }
-
-      mbar_wait(&ms.valid_ready[g], ph, status, kSiteValidReady, k);
-      const uint32_t v0 = ms.valid[g][2 * h] & mk.x, v1 = ms.valid[g][2 * h + 1] & mk.y;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ms.valid_free[g]);
-      mk = mk_next;
-      if ((warp & 3) == 0) LT_TS(0, k, 2);
-
-      float cur = -INFINITY;
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        sv[j] = ((v0 >> j) & 1u) ? sv[j] : -INFINITY;
-        sv[32 + j] = ((v1 >> j) & 1u) ? sv[32 + j] : -INFINITY;
-        cur = fmaxf(cur, fmaxf(sv[j], sv[32 + j]));
-      }
-      cur *= c;
-      float* xb = ms.xbuf[g][ph];
-      xb[tl] = cur;
-      if (g == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
-      else asm volatile("bar.sync 2, 128;" ::: "memory");
-      cur = fmaxf(cur, xb[tl ^ 64]);
-      if ((warp & 3) == 0) LT_TS(0, k, 3);
-      real_m = fmaxf(real_m, cur);
-      // running max after block k-1 comes from the other group
-      float m_prev = kMInit;
-      if (k > 0) {
-        mbar_wait(&ms.m_pub[g ^ 1], ((k - 1) >> 1) & 1, status, kSiteMPub, k);
-        m_prev = ms.mshare[g ^ 1][tl];
-      }
-      const bool rescale = __any_sync(0xffffffffu, cur - m_prev > kRescaleThreshold);
-      const float new_m = rescale ? fmaxf(cur, m_prev) : m_prev;
-      ms.mshare[g][tl] = new_m;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ms.m_pub[g]);
-      li *= fast_exp2(m_mine - new_m);
-      m_mine = new_m;
-      if ((warp & 3) == 0) LT_TS(0, k, 4);
-
-      const float nm = -new_m + kPScaleLog2;
-      uint32_t pk[16];
-#pragma unroll
-      for (int j = 0; j < 64; j += 4) {
-        float2 d0, d1;
-        d0.x = fast_exp2(fmaf(sv[j], c, nm));
-        d0.y = fast_exp2(fmaf(sv[j + 1], c, nm));
-        d1.x = fast_exp2(fmaf(sv[j + 2], c, nm));
-        d1.y = fast_exp2(fmaf(sv[j + 3], c, nm));
-        li += d0.x + d0.y;
-        li += d1.x + d1.y;
-        const uint32_t lo = __nv_cvt_float2_to_fp8x2(d0, __NV_SATFINITE, __NV_E4M3);
-        const uint32_t hi = __nv_cvt_float2_to_fp8x2(d1, __NV_SATFINITE, __NV_E4M3);
-        pk[j >> 2] = lo | (hi << 16);
-      }
-      if ((warp & 3) == 0) LT_TS(0, k, 5);
-      // P buffer g was last read by PV(k-2)
-      if (k >= 2) mbar_wait(&ms.pv_done[g], ph ^ 1, status, kSitePFree, k);
-      uint8_t* pdst = sm + kOffP + g * kPBytes + (4 * h) * 1024 + r * 16;
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-        *reinterpret_cast<uint4*>(pdst + i * 1024) =
-            make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
-
-      if (rescale && k > 0) {
-        // O holds blocks [0, k) relative to m_prev: bring it to new_m once PV(k-1) is complete
-        mbar_wait(&ms.pv_done[g ^ 1], ((k - 1) >> 1) & 1, status, kSitePvDone, k);
-        tc_fence_after();
-        const float f = fast_exp2(m_prev - new_m);
-        float o[32];
-#pragma unroll 1
-        for (int cc = 0; cc < 8; ++cc) {
-          const uint32_t ocol = tmem + lane_base + kTmemO + cc * 32;
-          tmem_ld32(ocol, o);
-          tmem_wait_ld();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) o[j] *= f;
-          tmem_st32(ocol, o);
-        }
-        tmem_wait_st();
-        tc_fence_before();
-      }
-      if ((warp & 3) == 0) LT_TS(0, k, 6);
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(a_p_ready);
-      if ((warp & 3) == 0) LT_TS(0, k, 7);
+      if (lane == 0) mbar_arrive_cluster(a_o_free);
+      kb0 += nb;
     }
-
-    // end of tile: merge the two groups' row sums (each relative to its own latest running max)
-    const int t = threadIdx.x;                    // 0..255 = g*128 + tl
-    ms.fin[0][t] = li;
-    ms.fin[1][t] = real_m;
-    ms.fin[2][t] = m_mine;
-    asm volatile("bar.sync 3, 256;" ::: "memory");
-    const int last_g = (nb - 1) & 1;
-    float m = ms.fin[2][last_g * 128 + tl];       // running max after the last block
-    float lsum = 0.f;
-    real_m = -INFINITY;
-#pragma unroll
-    for (int gg = 0; gg < 2; ++gg) {
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        const int o = gg * 128 + hh * 64 + r;
-        lsum += ms.fin[0][o] * fast_exp2(ms.fin[2][o] - m);
-        real_m = fmaxf(real_m, ms.fin[1][o]);
-      }
-    }
-    li = lsum;
-    if (real_m == -INFINITY) { li = 0.f; m = -INFINITY; }
-    const size_t grow = (size_t)tile * 128 + row;
-    if (g == 0 && h == 0) {
-      float l = __logf(li) - kPScaleLn + m * kLn2;
-      if (!(li > 0.f)) l = INFINITY;
-      p.lse[grow] = l;
-      if (p.max_logits) p.max_logits[grow] = real_m * kLn2;
-    }
-    mbar_wait(&ms.pv_done[(nb - 1) & 1], ((nb - 1) >> 1) & 1, status, kSiteEpi, nb);
-    tc_fence_after();
-    const bool empty = !(li > 0.f);
-    const float oscale = empty ? 0.f : __fdividef(p.out_scale, li);
-    // group g writes dims [256h + 128g, +128) of its row
-    __nv_bfloat16* orow = p.out + grow * kDV + 256 * h + 128 * g;
-    float o[32];
-#pragma unroll 1
-    for (int cc = 0; cc < 4; ++cc) {
-      tmem_ld32(tmem + lane_base + kTmemO + g * 128 + cc * 32, o);
-      tmem_wait_ld();
-      if (kDebug && p.dbg && tile == 0) {
-        float* d = p.dbg + (size_t)p.cap * 128 + (size_t)row * 512 + 256 * h + 128 * g + cc * 32;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) d[j] = o[j];
-      }
-      uint32_t w[16];
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const float a = empty ? 0.f : o[2 * j] * oscale;
-        const float b = empty ? 0.f : o[2 * j + 1] * oscale;
-        __nv_bfloat162 v2 = __floats2bfloat162_rn(a, b);
-        w[j] = *reinterpret_cast<uint32_t*>(&v2);
-      }
-      uint4* dst = reinterpret_cast<uint4*>(orow + cc * 32);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) dst[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
-    }
-    if (kDebug && p.dbg && tile == 0 && g == 0 && h == 0) {
-      float* d = p.dbg + (size_t)p.cap * 128 + 128 * 512;
-      d[row] = m;
-      d[128 + row] = li;
-    }
-    tc_fence_before();
   } else if (warp < kSoftmaxWarps + kProducerWarps) {
-    // ------------------------------------------------------------ TMA producers (K rows, Q tile)
-    // warp pw gathers row quads pw and pw+8 of this CTA's 64 keys, all five column chunks
-
-    // (the whole warp runs the loop with warp-uniform values; one elected lane issues)
+    // ------------------------------------------------------------ TMA producers (K rows, V rows of the peer's keys, Q tile)
     {
       const int pw = warp - kSoftmaxWarps;
-      if (pw == 0 && lane == 0) {
-        if (cta == 0) mbar_arrive_expect_tx(&ms.q_full, 2 * kQBytes);
-        const uint32_t a_q_full = mapa(smem_u32(&ms.q_full), 0);
-        for (int j = 0; j < kChunks; ++j)
-          tma_load_2d_pair(sbase + kOffQ + j * kChunkBytes, &map_q, 128 * j,
-                           tile * 128 + (int)cta * 64, a_q_full);
-      }
-      __syncwarp();
-      // lane l < 10 of warp pw owns row quad pw + 8*(l/5) and column chunk l%5: one warp-wide
-      // instruction issues the warp's ten gathers of a block
+      // lane l < 10 of warp pw owns row quad pw + 8*(l/5) and column chunk l%5 of this CTA's 64
+      // keys: one warp-wide instruction issues the warp's ten K gathers of a block
       const int quad = pw + 8 * (lane / 5), chunk = lane % 5;
       const bool active = lane < 10;
-      // lanes 16..23 gather the V tile: row quads pw + 8*t (t < 4) of all 128 keys, this CTA's
-      // two 128-byte value chunks
+      // lanes 16..19 gather the PEER's 64 keys of the V tile (row quads pw + 8*t, t < 2, this
+      // CTA's two 128-byte value chunks); the own keys' value bytes are copied from the K tile
       const int vl = lane - 16;
-      const bool v_active = vl >= 0 && vl < 8;
-      const int v_quad = pw + 8 * (vl >> 1), v_chunk = vl & 1;
-      const int32_t* v_idx_row = p.indices + (size_t)tile * p.idx_stride + 4 * (v_active ? v_quad : pw);
-      int4 vc0 = __ldg(reinterpret_cast<const int4*>(v_idx_row));
-      const int32_t* idx_row = p.indices + (size_t)tile * p.idx_stride + 64 * cta + 4 * (active ? quad : pw);
-      int4 c0 = __ldg(reinterpret_cast<const int4*>(idx_row));
-      for (int k = 0; k < nb; ++k) {
-        const int s = k & 1;
-        const uint32_t ph = (k >> 1) & 1;
-        int4 n0 = c0, vn0 = vc0;
-        if (k + 1 < nb) {
-          n0 = __ldg(reinterpret_cast<const int4*>(idx_row + (size_t)(k + 1) * kBlockKeys));
-          vn0 = __ldg(reinterpret_cast<const int4*>(v_idx_row + (size_t)(k + 1) * kBlockKeys));
+      const bool v_active = vl >= 0 && vl < 4;
+      const int v_quad = 16 * (int)(cta ^ 1u) + pw + 8 * (vl >> 1), v_chunk = vl & 1;
+      const uint32_t a_q_full = mapa(smem_u32(&ms.q_full), 0);
+      int kb0 = 0, it = 0;
+      for (int tile = cid; tile < p.ng; tile += ncl, ++it) {
+        const int nb = blocks_of(tile_count(tile));
+        if (kDebug) ts_on = ts != nullptr && (tile == p.ng / 2) && lane == 0;
+        if (pw == 0) {
+          // the Q tile of the previous tile must have been consumed by its last QK^T
+          if (it >= 1) mbar_wait(&ms.q_free, (it - 1) & 1, status, kSiteQFree, it);
+          if (lane == 0) {
+            if (cta == 0) mbar_arrive_expect_tx(&ms.q_full, 2 * kQBytes);
+            for (int j = 0; j < kChunks; ++j)
+              tma_load_2d_pair(sbase + kOffQ + j * kChunkBytes, &map_q, 128 * j,
+                               tile * 128 + (int)cta * 64, a_q_full);
+          }
+          __syncwarp();
         }
-        if (pw == 0) LT_TS(1, k, 0);
-        if (k >= 2) {
-          // stage s held block k-2: QK(k-2) must have read it and its V copies must be out
-          mbar_wait(&ms.qk_done[s], ph ^ 1, status, kSiteKFree, k);
+        const int32_t* idx_row = p.indices + (size_t)tile * p.idx_stride + 64 * cta + 4 * (active ? quad : pw);
+        const int32_t* v_idx_row = p.indices + (size_t)tile * p.idx_stride + 4 * (v_active ? v_quad : pw);
+        int4 c0 = __ldg(reinterpret_cast<const int4*>(idx_row));
+        int4 vc0 = __ldg(reinterpret_cast<const int4*>(v_idx_row));
+        for (int k = 0; k < nb; ++k) {
+          const int kb = kb0 + k;
+          const int s = kb & 1;
+          const uint32_t ph = (kb >> 1) & 1;
+          int4 n0 = c0, vn0 = vc0;
+          if (k + 1 < nb) {
+            n0 = __ldg(reinterpret_cast<const int4*>(idx_row + (size_t)(k + 1) * kBlockKeys));
+            vn0 = __ldg(reinterpret_cast<const int4*>(v_idx_row + (size_t)(k + 1) * kBlockKeys));
+          }
+          if (pw == 0) LT_TS(1, k, 0);
+          if (kb >= 2) {
+            // stage s held block kb-2: its QK^T must have read it and its value copies must be out
+            mbar_wait(&ms.qk_done[s], ph ^ 1, status, kSiteKFree, k);
+            mbar_wait(&ms.k_copied[s], ph ^ 1, status, kSiteKCopied, k);
+          }
+          __syncwarp();
+          if (pw == 0) LT_TS(1, k, 1);
+          if (pw == 0 && lane == 0) mbar_arrive_expect_tx(&ms.k_land[s], kKStage);
+          if (active)
+            tma_gather4(sbase + kOffK + s * kKStage + (uint32_t)quad * 512 + chunk * kChunkBytes, &map_kv,
+                        128 * chunk, c0, smem_u32(&ms.k_land[s]));
+          __syncwarp();
+          // V stage s was last read by the PV of block kb-2
+          if (kb >= 2) mbar_wait(&ms.pv_done[s], ph ^ 1, status, kSiteVFree, k);
+          __syncwarp();
+          if (pw == 0 && lane == 0) mbar_arrive_expect_tx(&ms.v_land[s], kVStage / 2);
+          if (v_active)
+            tma_gather4(sbase + kOffV + s * kVStage + v_chunk * kVChunk + (uint32_t)v_quad * 512, &map_kv,
+                        256 * (int)cta + 128 * v_chunk, vc0, smem_u32(&ms.v_land[s]));
+          __syncwarp();
+          if (pw == 0) LT_TS(1, k, 2);
+          c0 = n0; vc0 = vn0;
         }
-        __syncwarp();
-        if (pw == 0) LT_TS(1, k, 1);
-        if (pw == 0 && lane == 0) mbar_arrive_expect_tx(&ms.k_land[s], kKStage);
-        if (active)
-          tma_gather4(sbase + kOffK + s * kKStage + (uint32_t)quad * 512 + chunk * kChunkBytes, &map_kv,
-                      128 * chunk, c0, smem_u32(&ms.k_land[s]));
-        __syncwarp();
-        // V stage s was last read by PV(k-2)
-        if (k >= 2) mbar_wait(&ms.pv_done[s], ph ^ 1, status, kSiteVFree, k);
-        __syncwarp();
-        if (pw == 0 && lane == 0) mbar_arrive_expect_tx(&ms.v_land[s], kVStage);
-        if (v_active)
-          tma_gather4(sbase + kOffV + s * kVStage + v_chunk * kVChunk + (uint32_t)v_quad * 512, &map_kv,
-                      256 * (int)cta + 128 * v_chunk, vc0, smem_u32(&ms.v_land[s]));
-        __syncwarp();
-        if (pw == 0) LT_TS(1, k, 2);
-        c0 = n0; vc0 = vn0;
+        kb0 += nb;
       }
     }
   } else {
-
    if (warp == kWarpMma) {
     // ------------------------------------------------------------ MMA issue (leader CTA only)
     if (cta == 0) {   // the whole warp runs this loop; one elected lane issues
@@ -428,11 +455,10 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
       constexpr uint32_t idesc_pv = umma_idesc(0, 0, false, true, 128, 256);
       const uint32_t a_qk_done_peer[2] = {mapa(smem_u32(&ms.qk_done[0]), 1), mapa(smem_u32(&ms.qk_done[1]), 1)};
       const uint32_t a_pv_done_peer[2] = {mapa(smem_u32(&ms.pv_done[0]), 1), mapa(smem_u32(&ms.pv_done[1]), 1)};
-      mbar_wait(&ms.q_full, 0, status, kSiteQ, 0);
-      __syncwarp();
-      // S = Q K^T of block k into S buffer k%2 (needs K stage k%2 on both CTAs, buffer drained)
-      auto issue_qk = [&](int k) {
-        const int s = k & 1;
+      const uint32_t a_q_free_peer = mapa(smem_u32(&ms.q_free), 1);
+      // S = Q K^T of block kb into S buffer kb%2
+      auto issue_qk = [&](int k, int kb) {
+        const int s = kb & 1;
         LT_TS(2, k, 2);
         tc_fence_after();
         const uint32_t d = tmem + (s ? kTmemS1 : kTmemS0);
@@ -444,119 +470,155 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         mma_commit_pair_elect(a_qk_done_peer[s]);
         LT_TS(2, k, 3);
       };
-      auto issue_pv = [&](int kb_) {
-        const int s = kb_ & 1;
-        LT_TS(2, kb_, 6);
+      auto issue_pv = [&](int k, int kb) {
+        const int s = kb & 1;
+        LT_TS(2, k, 6);
         tc_fence_after();
         const uint64_t ad = umma_desc(sbase + kOffP + s * kPBytes, 1024, 128, kSwzNone);
         const uint64_t bd = umma_desc(sbase + kOffV + s * kVStage, kVChunk, 1024, kSwz128);
         mma_f8_pair_pv8(tmem + kTmemO, idesc_pv, (uint32_t)ad, (uint32_t)bd, (uint32_t)(ad >> 32),
-                        (uint32_t)(bd >> 32), kb_ ? 1u : 0u);
+                        (uint32_t)(bd >> 32), k ? 1u : 0u);
         mma_commit_pair_elect(smem_u32(&ms.pv_done[s]));
         mma_commit_pair_elect(a_pv_done_peer[s]);
-        LT_TS(2, kb_, 7);
+        LT_TS(2, k, 7);
       };
-      // Ready-driven issue: whichever of "next QK" (its K stage landed on both CTAs and its S
-      // buffer drained) and "next PV" (its P written, its V stage landed on both CTAs) is
-      // ready goes first; PV wins ties because it releases stages.  QK can run up to two
-      // blocks ahead of the softmax warps.  Bounded like every other wait.
-      int qk_i = 0, pv_i = 0;
-      unsigned long long idle_since = 0;
+      int kb0 = 0, it = 0;
       bool aborted = false;
-      while (pv_i < nb && !aborted) {
-        bool did = false;
-        {
-          const int s = pv_i & 1;
-          const uint32_t ph = (pv_i >> 1) & 1;
-          // lanes poll independently: act only on what every lane has seen (keeps the warp converged)
-          const bool ok = pv_i < qk_i && mbar_test(&ms.p_ready[s], ph) &&
-                          mbar_test(&ms.v_land[s], ph) && mbar_test(&ms.v_peer[s], ph);
-          if (__all_sync(0xffffffffu, ok)) {
-            issue_pv(pv_i++);
-            did = true;
+      for (int tile = cid; tile < p.ng && !aborted; tile += ncl, ++it) {
+        const int nb = blocks_of(tile_count(tile));
+        if (kDebug) ts_on = ts != nullptr && (tile == p.ng / 2) && lane == 0;
+        mbar_wait(&ms.q_full, it & 1, status, kSiteQ, it);
+        __syncwarp();
+        // Ready-driven issue: whichever of "next QK" (its K stage landed on both CTAs and its S
+        // buffer drained) and "next PV" (its P written, its V stage landed on both CTAs, and for
+        // the tile's first PV the previous tile's O read out) is ready goes first.
+        int qk_i = 0, pv_i = 0;
+        unsigned long long idle_since = 0;
+        while (pv_i < nb && !aborted) {
+          bool did = false;
+          {
+            const int kb = kb0 + pv_i;
+            const int s = kb & 1;
+            const uint32_t ph = (kb >> 1) & 1;
+            // lanes poll independently: act only on what every lane has seen (keeps the warp converged)
+            const bool ok = pv_i < qk_i && mbar_test(&ms.p_ready[s], ph) && mbar_test(&ms.v_land[s], ph) &&
+                            mbar_test(&ms.v_peer[s], ph) &&
+                            (pv_i > 0 || it == 0 || mbar_test(&ms.o_free, (it - 1) & 1));
+            if (__all_sync(0xffffffffu, ok)) {
+              issue_pv(pv_i, kb);
+              ++pv_i;
+              did = true;
+            }
+          }
+          if (qk_i < nb) {
+            const int kb = kb0 + qk_i;
+            const int s = kb & 1;
+            const uint32_t ph = (kb >> 1) & 1;
+            const bool ok = mbar_test(&ms.k_land[s], ph) && mbar_test(&ms.k_peer[s], ph) &&
+                            (kb < 2 || mbar_test(&ms.s_free[s], ph ^ 1));
+            if (__all_sync(0xffffffffu, ok)) {
+              issue_qk(qk_i, kb);
+              ++qk_i;
+              if (qk_i == nb) {      // the Q tile is no longer needed once these MMAs complete
+                mma_commit_pair_elect(smem_u32(&ms.q_free));
+                mma_commit_pair_elect(a_q_free_peer);
+              }
+              did = true;
+            }
+          }
+          if (did) {
+            idle_since = 0;
+          } else {
+            const unsigned long long now = globaltimer_ns();
+            if (idle_since == 0) idle_since = now;
+            bool stop = *reinterpret_cast<volatile int*>(status) != 0;
+            if (now - idle_since > kWaitLimitNs) {
+              if (lane == 0 && atomicCAS(status, 0, (int)kSiteMmaIdle) == 0) { status[1] = (int)blockIdx.x; status[2] = pv_i; }
+              stop = true;
+            }
+            aborted = __any_sync(0xffffffffu, stop);
           }
         }
-        if (qk_i < nb) {
-          const int s = qk_i & 1;
-          const uint32_t ph = (qk_i >> 1) & 1;
-          const bool ok = mbar_test(&ms.k_land[s], ph) && mbar_test(&ms.k_peer[s], ph) &&
-                          (qk_i < 2 || mbar_test(&ms.s_free[s], ph ^ 1));
-          if (__all_sync(0xffffffffu, ok)) {
-            issue_qk(qk_i++);
-            did = true;
-          }
-        }
-        if (did) {
-          idle_since = 0;
-        } else {
-          const unsigned long long now = globaltimer_ns();
-          if (idle_since == 0) idle_since = now;
-          bool stop = *reinterpret_cast<volatile int*>(status) != 0;
-          if (now - idle_since > kWaitLimitNs) {
-            if (lane == 0 && atomicCAS(status, 0, (int)kSiteMmaIdle) == 0) { status[1] = (int)blockIdx.x; status[2] = pv_i; }
-            stop = true;
-          }
-          aborted = __any_sync(0xffffffffu, stop);
-        }
+        kb0 += nb;
       }
     }
-  } else if (warp == kWarpCopy) {
-    // ------------------------------------------------------------ V operand = copies of K chunks
-    // The value dims of a key are the first 512 bytes of the row the K gather already
-    // fetched.  Chunk pair {2d, 2d+1} of this CTA's 64 keys goes to rows [64*cta, +64) of
-    // CTA d's V stage: two copies stay local, two cross to the peer over DSMEM.
-    if (lane == 0) {
-      const uint32_t a_k_peer[2] = {mapa(smem_u32(&ms.k_peer[0]), 0), mapa(smem_u32(&ms.k_peer[1]), 0)};
+  } else if (warp == kWarpCopy || warp == kWarpRelay) {
+    // ------------------------------------------------------------ own keys' V bytes + relays
+    // The value dims of a key are the first 512 bytes of the row the K gather fetched.  Each
+    // of these two warps copies one 8 KB chunk (64 own keys x 128 bytes of this CTA's dims)
+    // from the K tile into rows [64*cta, +64) of the V tile -- both tiles use the same
+    // 128-byte swizzle, so the copy is linear -- and tells the leader CTA what has landed.
+    const int half = warp - kWarpCopy;            // value chunk nbk this warp copies
+    const uint32_t a_k_peer[2] = {mapa(smem_u32(&ms.k_peer[0]), 0), mapa(smem_u32(&ms.k_peer[1]), 0)};
+    const uint32_t a_v_peer[2] = {mapa(smem_u32(&ms.v_peer[0]), 0), mapa(smem_u32(&ms.v_peer[1]), 0)};
+    int kb0 = 0;
+    for (int tile = cid; tile < p.ng; tile += ncl) {
+      const int nb = blocks_of(tile_count(tile));
+      if (kDebug) ts_on = ts != nullptr && (tile == p.ng / 2) && lane == 0;
       for (int k = 0; k < nb; ++k) {
-        const int s = k & 1;
-        const uint32_t ph = (k >> 1) & 1;
-        LT_TS(3, k, 0);
+        const int kb = kb0 + k;
+        const int s = kb & 1;
+        const uint32_t ph = (kb >> 1) & 1;
+        if (half == 0) LT_TS(3, k, 0);
         mbar_wait(&ms.k_land[s], ph, status, kSiteRelayK, k);
-        LT_TS(3, k, 1);
-        if (cta == 1) mbar_arrive_cluster(a_k_peer[s]);
-        LT_TS(3, k, 3);
+        if (half == 0) LT_TS(3, k, 1);
+        if (half == 0 && cta == 1 && lane == 0) mbar_arrive_cluster(a_k_peer[s]);
+        if (kb >= 2) mbar_wait(&ms.pv_done[s], ph ^ 1, status, kSiteVFree, k);   // V stage s free
+        __syncwarp();
+        const uint4* src = reinterpret_cast<const uint4*>(sm + kOffK + s * kKStage + (2 * cta + half) * kChunkBytes);
+        uint4* dst = reinterpret_cast<uint4*>(sm + kOffV + s * kVStage + half * kVChunk + cta * kChunkBytes);
+        uint4 t[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) t[i] = src[i * 32 + lane];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) dst[i * 32 + lane] = t[i];
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&ms.k_copied[s]);
+          mbar_arrive(&ms.v_land[s]);
+        }
+        if (half == 0) LT_TS(3, k, 3);
+        if (half == 1) {
+          mbar_wait(&ms.v_land[s], ph, status, kSiteRelayV, k);
+          LT_TS(4, k, 0);
+          if (cta == 1 && lane == 0) mbar_arrive_cluster(a_v_peer[s]);
+        }
       }
-    }
-  } else if (warp == kWarpRelay) {
-    // ------------------------------------------------------------ "V landed" relay
-    if (lane == 0) {
-      const uint32_t a_v_peer[2] = {mapa(smem_u32(&ms.v_peer[0]), 0), mapa(smem_u32(&ms.v_peer[1]), 0)};
-      for (int k = 0; k < nb; ++k) {
-        const int s = k & 1;
-        const uint32_t ph = (k >> 1) & 1;
-        mbar_wait(&ms.v_land[s], ph, status, kSiteRelayV, k);
-        LT_TS(4, k, 0);
-        // all four copies INTO this CTA are done: tell both CTAs' producers (K stages are
-        // sources of those copies) and, from the peer, the MMA thread
-        if (cta == 1) mbar_arrive_cluster(a_v_peer[s]);
-      }
+      kb0 += nb;
     }
   } else {
     // ------------------------------------------------------------ index-validity bits
-    const int32_t* idx_row = p.indices + (size_t)tile * p.idx_stride;
-    int4 cur = __ldg(reinterpret_cast<const int4*>(idx_row) + lane);
-    for (int k = 0; k < nb; ++k) {
-      const int s = k & 1;
-      const uint32_t ph = (k >> 1) & 1;
-      int4 nxt = cur;
-      if (k + 1 < nb) nxt = __ldg(reinterpret_cast<const int4*>(idx_row + (size_t)(k + 1) * kBlockKeys) + lane);
-      const int rank0 = k * kBlockKeys + lane * 4;
-      auto ok = [&](int idx, int rk) -> uint32_t {
-        return (idx >= 0 && idx < p.s_kv && rk < count) ? 1u : 0u;
-      };
-      const uint32_t nib = ok(cur.x, rank0) | (ok(cur.y, rank0 + 1) << 1) |
-                           (ok(cur.z, rank0 + 2) << 2) | (ok(cur.w, rank0 + 3) << 3);
-      if (k >= 2) mbar_wait(&ms.valid_free[s], ph ^ 1, status, kSiteValidFree, k);
-      const uint32_t nib_hi = __shfl_down_sync(0xffffffffu, nib, 1);
-      if ((lane & 1) == 0)
-        reinterpret_cast<uint8_t*>(&ms.valid[s][0])[lane >> 1] = (uint8_t)(nib | (nib_hi << 4));
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ms.valid_ready[s]);
-      cur = nxt;
+    int kb0 = 0;
+    for (int tile = cid; tile < p.ng; tile += ncl) {
+      const int count = tile_count(tile);
+      const int nb = blocks_of(count);
+      const int32_t* idx_row = p.indices + (size_t)tile * p.idx_stride;
+      int4 cur = __ldg(reinterpret_cast<const int4*>(idx_row) + lane);
+      for (int k = 0; k < nb; ++k) {
+        const int kb = kb0 + k;
+        const int s = kb & 1;
+        const uint32_t ph = (kb >> 1) & 1;
+        int4 nxt = cur;
+        if (k + 1 < nb) nxt = __ldg(reinterpret_cast<const int4*>(idx_row + (size_t)(k + 1) * kBlockKeys) + lane);
+        const int rank0 = k * kBlockKeys + lane * 4;
+        auto ok = [&](int idx, int rk) -> uint32_t {
+          return (idx >= 0 && idx < p.s_kv && rk < count) ? 1u : 0u;
+        };
+        const uint32_t nib = ok(cur.x, rank0) | (ok(cur.y, rank0 + 1) << 1) |
+                             (ok(cur.z, rank0 + 2) << 2) | (ok(cur.w, rank0 + 3) << 3);
+        if (kb >= 2) mbar_wait(&ms.valid_free[s], ph ^ 1, status, kSiteValidFree, k);
+        const uint32_t nib_hi = __shfl_down_sync(0xffffffffu, nib, 1);
+        if ((lane & 1) == 0)
+          reinterpret_cast<uint8_t*>(&ms.valid[s][0])[lane >> 1] = (uint8_t)(nib | (nib_hi << 4));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ms.valid_ready[s]);
+        cur = nxt;
+      }
+      kb0 += nb;
     }
   }
   }
-  (void)peer;
 
   // tear-down: nobody may still be reading TMEM of either CTA when it is released
   __syncthreads();
@@ -564,6 +626,28 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
   cluster_sync_all();
   if (warp == kWarpMma) tmem_dealloc_pair(tmem, kTmemCols);
   if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&status[3], 1);
+}
+
+// how many 2-CTA clusters of this kernel the current device can hold at once
+static int max_clusters() {
+  static thread_local int cached_dev = -1, cached = 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev == cached_dev) return cached;
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int n = sms / 2;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(sms, 1, 1); cfg.blockDim = dim3(kAttnThreads, 1, 1); cfg.dynamicSmemBytes = kAttnSmem;
+  cudaLaunchAttribute at; at.id = cudaLaunchAttributeClusterDimension; at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+  cfg.attrs = &at; cfg.numAttrs = 1;
+  int q = 0;
+  if (cudaFuncSetAttribute(masked_mla_fp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem) == cudaSuccess &&
+      cudaOccupancyMaxActiveClusters(&q, masked_mla_fp8_kernel<false>, &cfg) == cudaSuccess && q > 0)
+    n = q;
+  cudaGetLastError();
+  cached_dev = dev; cached = n;
+  return n;
 }
 
 static int launch_fp8(const void* q8, const void* kv8, const int32_t* indices, float sm_scale,
@@ -589,7 +673,7 @@ static int launch_fp8(const void* q8, const void* kv8, const int32_t* indices, f
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem) !=
       cudaSuccess)
     return LITEDSA_ERR_CUDA;
-  kern<<<2 * ng, kAttnThreads, kAttnSmem, stream>>>(map_q, map_kv, p);
+  kern<<<2 * min(ng, max_clusters()), kAttnThreads, kAttnSmem, stream>>>(map_q, map_kv, p);
   return cudaGetLastError() == cudaSuccess ? LITEDSA_OK : LITEDSA_ERR_CUDA;
 }
 
