@@ -380,17 +380,15 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
     }
   } else if (warp < kSoftmaxWarps + kProducerWarps) {
     // ------------------------------------------------------------ TMA producers (K rows, V rows of the peer's keys, Q tile)
-    {
-      const int pw = warp - kSoftmaxWarps;
-      // lane l < 10 of warp pw owns row quad pw + 8*(l/5) and column chunk l%5 of this CTA's 64
-      // keys: one warp-wide instruction issues the warp's ten K gathers of a block
-      const int quad = pw + 8 * (lane / 5), chunk = lane % 5;
-      const bool active = lane < 10;
-      // lanes 16..19 gather the PEER's 64 keys of the V tile (row quads pw + 8*t, t < 2, this
-      // CTA's two 128-byte value chunks); the own keys' value bytes are copied from the K tile
-      const int vl = lane - 16;
-      const bool v_active = vl >= 0 && vl < 4;
-      const int v_quad = 16 * (int)(cta ^ 1u) + pw + 8 * (vl >> 1), v_chunk = vl & 1;
+    // Producer warps 0-3 gather K (and load the Q tile), warps 4-7 gather the peer keys' V
+    // rows: the two have different stage-free conditions (QK^T done vs PV done) and must not
+    // wait for each other.
+    const int pw = warp - kSoftmaxWarps;
+    if (pw < 4) {
+      // lane l < 20 owns row quad pw + 4*(l/5) and column chunk l%5 of this CTA's 64 keys: one
+      // warp-wide instruction issues the warp's twenty K gathers of a block
+      const int quad = pw + 4 * (lane / 5), chunk = lane % 5;
+      const bool active = lane < 20;
       const uint32_t a_q_full = mapa(smem_u32(&ms.q_full), 0);
       int kb0 = 0, it = 0;
       for (int tile = cid; tile < p.ng; tile += ncl, ++it) {
@@ -408,18 +406,13 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
           __syncwarp();
         }
         const int32_t* idx_row = p.indices + (size_t)tile * p.idx_stride + 64 * cta + 4 * (active ? quad : pw);
-        const int32_t* v_idx_row = p.indices + (size_t)tile * p.idx_stride + 4 * (v_active ? v_quad : pw);
         int4 c0 = __ldg(reinterpret_cast<const int4*>(idx_row));
-        int4 vc0 = __ldg(reinterpret_cast<const int4*>(v_idx_row));
         for (int k = 0; k < nb; ++k) {
           const int kb = kb0 + k;
           const int s = kb & 1;
           const uint32_t ph = (kb >> 1) & 1;
-          int4 n0 = c0, vn0 = vc0;
-          if (k + 1 < nb) {
-            n0 = __ldg(reinterpret_cast<const int4*>(idx_row + (size_t)(k + 1) * kBlockKeys));
-            vn0 = __ldg(reinterpret_cast<const int4*>(v_idx_row + (size_t)(k + 1) * kBlockKeys));
-          }
+          int4 n0 = c0;
+          if (k + 1 < nb) n0 = __ldg(reinterpret_cast<const int4*>(idx_row + (size_t)(k + 1) * kBlockKeys));
           if (pw == 0) LT_TS(1, k, 0);
           if (kb >= 2) {
             // stage s held block kb-2: its QK^T must have read it and its value copies must be out
@@ -433,16 +426,38 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
             tma_gather4(sbase + kOffK + s * kKStage + (uint32_t)quad * 512 + chunk * kChunkBytes, &map_kv,
                         128 * chunk, c0, smem_u32(&ms.k_land[s]));
           __syncwarp();
+          if (pw == 0) LT_TS(1, k, 2);
+          c0 = n0;
+        }
+        kb0 += nb;
+      }
+    } else {
+      // lane l < 8 of V warp vw gathers the PEER's 64 keys of the V tile: row quad vw + 4*(l/2)
+      // of those keys, value chunk l%2 of this CTA's dims (the own keys' value bytes are copied
+      // from the K tile by the copy warps)
+      const int vw = pw - 4;
+      const bool v_active = lane < 8;
+      const int v_quad = 16 * (int)(cta ^ 1u) + vw + 4 * (lane >> 1), v_chunk = lane & 1;
+      int kb0 = 0;
+      for (int tile = cid; tile < p.ng; tile += ncl) {
+        const int nb = blocks_of(tile_count(tile));
+        const int32_t* v_idx_row = p.indices + (size_t)tile * p.idx_stride + 4 * (v_active ? v_quad : vw);
+        int4 vc0 = __ldg(reinterpret_cast<const int4*>(v_idx_row));
+        for (int k = 0; k < nb; ++k) {
+          const int kb = kb0 + k;
+          const int s = kb & 1;
+          const uint32_t ph = (kb >> 1) & 1;
+          int4 vn0 = vc0;
+          if (k + 1 < nb) vn0 = __ldg(reinterpret_cast<const int4*>(v_idx_row + (size_t)(k + 1) * kBlockKeys));
           // V stage s was last read by the PV of block kb-2
           if (kb >= 2) mbar_wait(&ms.pv_done[s], ph ^ 1, status, kSiteVFree, k);
           __syncwarp();
-          if (pw == 0 && lane == 0) mbar_arrive_expect_tx(&ms.v_land[s], kVStage / 2);
+          if (vw == 0 && lane == 0) mbar_arrive_expect_tx(&ms.v_land[s], kVStage / 2);
           if (v_active)
             tma_gather4(sbase + kOffV + s * kVStage + v_chunk * kVChunk + (uint32_t)v_quad * 512, &map_kv,
                         256 * (int)cta + 128 * v_chunk, vc0, smem_u32(&ms.v_land[s]));
           __syncwarp();
-          if (pw == 0) LT_TS(1, k, 2);
-          c0 = n0; vc0 = vn0;
+          vc0 = vn0;
         }
         kb0 += nb;
       }
