@@ -380,86 +380,112 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
     }
   } else if (warp < kSoftmaxWarps + kProducerWarps) {
     // ------------------------------------------------------------ TMA producers (K rows, V rows of the peer's keys, Q tile)
-    // Producer warps 0-3 gather K (and load the Q tile), warps 4-7 gather the peer keys' V
-    // rows: the two have different stage-free conditions (QK^T done vs PV done) and must not
-    // wait for each other.
+    // All eight warps issue gathers (the TMA unit takes more in flight from more warps).  Per
+    // block a warp owns ten K gathers (lanes 0-9: row quad pw + 8*(l/5), chunk l%5 of this CTA's
+    // 64 keys) and four V gathers (lanes 16-19: the PEER's keys, row quad pw + 8*((l-16)/2),
+    // value chunk (l-16)%2 of this CTA's dims; the own keys' value bytes are copied from the K
+    // tile by the copy warps).  K and V streams have different stage-free conditions (QK^T done
+    // vs PV done), so each warp advances two independent cursors and issues whichever is ready.
     const int pw = warp - kSoftmaxWarps;
-    if (pw < 4) {
-      // lane l < 20 owns row quad pw + 4*(l/5) and column chunk l%5 of this CTA's 64 keys: one
-      // warp-wide instruction issues the warp's twenty K gathers of a block
-      const int quad = pw + 4 * (lane / 5), chunk = lane % 5;
-      const bool active = lane < 20;
-      const uint32_t a_q_full = mapa(smem_u32(&ms.q_full), 0);
-      int kb0 = 0, it = 0;
-      for (int tile = cid; tile < p.ng; tile += ncl, ++it) {
-        const int nb = blocks_of(tile_count(tile));
-        if (kDebug) ts_on = ts != nullptr && (tile == p.ng / 2) && lane == 0;
-        if (pw == 0) {
-          // the Q tile of the previous tile must have been consumed by its last QK^T
-          if (it >= 1) mbar_wait(&ms.q_free, (it - 1) & 1, status, kSiteQFree, it);
+    const int quad = pw + 8 * (lane / 5), chunk = lane % 5;
+    const bool k_active = lane < 10;
+    const int vl = lane - 16;
+    const bool v_active = vl >= 0 && vl < 4;
+    const int v_quad = 16 * (int)(cta ^ 1u) + pw + 8 * (vl >> 1), v_chunk = vl & 1;
+    const uint32_t a_q_full = mapa(smem_u32(&ms.q_full), 0);
+    struct Cursor { int tile, it, k, nb, kb0; };
+    auto cur_init = [&](Cursor& c) {
+      c.tile = cid; c.it = 0; c.k = 0; c.kb0 = 0;
+      c.nb = c.tile < p.ng ? blocks_of(tile_count(c.tile)) : 0;
+    };
+    auto cur_next = [&](Cursor& c) {
+      if (++c.k == c.nb) {
+        c.kb0 += c.nb; c.k = 0; c.tile += ncl; ++c.it;
+        c.nb = c.tile < p.ng ? blocks_of(tile_count(c.tile)) : 0;
+      }
+    };
+    Cursor ck, cv;
+    cur_init(ck);
+    cur_init(cv);
+    auto k_idx = [&](const Cursor& c) {
+      return __ldg(reinterpret_cast<const int4*>(p.indices + (size_t)c.tile * p.idx_stride +
+                                                 (size_t)c.k * kBlockKeys + 64 * cta + 4 * (k_active ? quad : pw)));
+    };
+    auto v_idx = [&](const Cursor& c) {
+      return __ldg(reinterpret_cast<const int4*>(p.indices + (size_t)c.tile * p.idx_stride +
+                                                 (size_t)c.k * kBlockKeys + 4 * (v_active ? v_quad : pw)));
+    };
+    int4 kc = make_int4(0, 0, 0, 0), vc = make_int4(0, 0, 0, 0);
+    if (ck.tile < p.ng) { kc = k_idx(ck); vc = v_idx(cv); }
+    int q_tile = cid, q_it = 0;           // next Q tile to request (warp 0 only)
+    unsigned long long idle_since = 0;
+    bool aborted = false;
+    while ((ck.tile < p.ng || cv.tile < p.ng || (pw == 0 && q_tile < p.ng)) && !aborted) {
+      bool did = false;
+      if (pw == 0 && q_tile < p.ng) {
+        // the previous tile's Q must have been consumed by its last QK^T
+        const bool okq = q_it == 0 || mbar_test(&ms.q_free, (q_it - 1) & 1);
+        if (__all_sync(0xffffffffu, okq)) {
           if (lane == 0) {
             if (cta == 0) mbar_arrive_expect_tx(&ms.q_full, 2 * kQBytes);
             for (int j = 0; j < kChunks; ++j)
               tma_load_2d_pair(sbase + kOffQ + j * kChunkBytes, &map_q, 128 * j,
-                               tile * 128 + (int)cta * 64, a_q_full);
+                               q_tile * 128 + (int)cta * 64, a_q_full);
           }
           __syncwarp();
+          q_tile += ncl;
+          ++q_it;
+          did = true;
         }
-        const int32_t* idx_row = p.indices + (size_t)tile * p.idx_stride + 64 * cta + 4 * (active ? quad : pw);
-        int4 c0 = __ldg(reinterpret_cast<const int4*>(idx_row));
-        for (int k = 0; k < nb; ++k) {
-          const int kb = kb0 + k;
-          const int s = kb & 1;
-          const uint32_t ph = (kb >> 1) & 1;
-          int4 n0 = c0;
-          if (k + 1 < nb) n0 = __ldg(reinterpret_cast<const int4*>(idx_row + (size_t)(k + 1) * kBlockKeys));
-          if (pw == 0) LT_TS(1, k, 0);
-          if (kb >= 2) {
-            // stage s held block kb-2: its QK^T must have read it and its value copies must be out
-            mbar_wait(&ms.qk_done[s], ph ^ 1, status, kSiteKFree, k);
-            mbar_wait(&ms.k_copied[s], ph ^ 1, status, kSiteKCopied, k);
-          }
-          __syncwarp();
-          if (pw == 0) LT_TS(1, k, 1);
-          if (pw == 0 && lane == 0) mbar_arrive_expect_tx(&ms.k_land[s], kKStage);
-          if (active)
-            tma_gather4(sbase + kOffK + s * kKStage + (uint32_t)quad * 512 + chunk * kChunkBytes, &map_kv,
-                        128 * chunk, c0, smem_u32(&ms.k_land[s]));
-          __syncwarp();
-          if (pw == 0) LT_TS(1, k, 2);
-          c0 = n0;
-        }
-        kb0 += nb;
       }
-    } else {
-      // lane l < 8 of V warp vw gathers the PEER's 64 keys of the V tile: row quad vw + 4*(l/2)
-      // of those keys, value chunk l%2 of this CTA's dims (the own keys' value bytes are copied
-      // from the K tile by the copy warps)
-      const int vw = pw - 4;
-      const bool v_active = lane < 8;
-      const int v_quad = 16 * (int)(cta ^ 1u) + vw + 4 * (lane >> 1), v_chunk = lane & 1;
-      int kb0 = 0;
-      for (int tile = cid; tile < p.ng; tile += ncl) {
-        const int nb = blocks_of(tile_count(tile));
-        const int32_t* v_idx_row = p.indices + (size_t)tile * p.idx_stride + 4 * (v_active ? v_quad : vw);
-        int4 vc0 = __ldg(reinterpret_cast<const int4*>(v_idx_row));
-        for (int k = 0; k < nb; ++k) {
-          const int kb = kb0 + k;
-          const int s = kb & 1;
-          const uint32_t ph = (kb >> 1) & 1;
-          int4 vn0 = vc0;
-          if (k + 1 < nb) vn0 = __ldg(reinterpret_cast<const int4*>(v_idx_row + (size_t)(k + 1) * kBlockKeys));
-          // V stage s was last read by the PV of block kb-2
-          if (kb >= 2) mbar_wait(&ms.pv_done[s], ph ^ 1, status, kSiteVFree, k);
+      if (ck.tile < p.ng) {
+        if (kDebug) ts_on = ts != nullptr && (ck.tile == p.ng / 2) && lane == 0;
+        const int kb = ck.kb0 + ck.k;
+        const int s = kb & 1;
+        const uint32_t ph = (kb >> 1) & 1;
+        // stage s held block kb-2: its QK^T must have read it and its value copies must be out
+        const bool ok = kb < 2 || (mbar_test(&ms.qk_done[s], ph ^ 1) && mbar_test(&ms.k_copied[s], ph ^ 1));
+        if (__all_sync(0xffffffffu, ok)) {
+          if (pw == 0) LT_TS(1, ck.k, 1);
+          if (pw == 0 && lane == 0) mbar_arrive_expect_tx(&ms.k_land[s], kKStage);
+          if (k_active)
+            tma_gather4(sbase + kOffK + s * kKStage + (uint32_t)quad * 512 + chunk * kChunkBytes, &map_kv,
+                        128 * chunk, kc, smem_u32(&ms.k_land[s]));
           __syncwarp();
-          if (vw == 0 && lane == 0) mbar_arrive_expect_tx(&ms.v_land[s], kVStage / 2);
+          if (pw == 0) LT_TS(1, ck.k, 2);
+          cur_next(ck);
+          if (ck.tile < p.ng) kc = k_idx(ck);
+          did = true;
+        }
+      }
+      if (cv.tile < p.ng) {
+        const int kb = cv.kb0 + cv.k;
+        const int s = kb & 1;
+        const uint32_t ph = (kb >> 1) & 1;
+        // V stage s was last read by the PV of block kb-2
+        const bool ok = kb < 2 || mbar_test(&ms.pv_done[s], ph ^ 1);
+        if (__all_sync(0xffffffffu, ok)) {
+          if (pw == 0 && lane == 0) mbar_arrive_expect_tx(&ms.v_land[s], kVStage / 2);
           if (v_active)
             tma_gather4(sbase + kOffV + s * kVStage + v_chunk * kVChunk + (uint32_t)v_quad * 512, &map_kv,
-                        256 * (int)cta + 128 * v_chunk, vc0, smem_u32(&ms.v_land[s]));
+                        256 * (int)cta + 128 * v_chunk, vc, smem_u32(&ms.v_land[s]));
           __syncwarp();
-          vc0 = vn0;
+          cur_next(cv);
+          if (cv.tile < p.ng) vc = v_idx(cv);
+          did = true;
         }
-        kb0 += nb;
+      }
+      if (did) {
+        idle_since = 0;
+      } else {
+        const unsigned long long now = globaltimer_ns();
+        if (idle_since == 0) idle_since = now;
+        bool stop = *reinterpret_cast<volatile int*>(status) != 0;
+        if (now - idle_since > kWaitLimitNs) {
+          if (lane == 0 && atomicCAS(status, 0, (int)kSiteKFree) == 0) { status[1] = (int)blockIdx.x; status[2] = ck.k; }
+          stop = true;
+        }
+        aborted = __any_sync(0xffffffffu, stop);
       }
     }
   } else {
