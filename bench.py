@@ -39,8 +39,8 @@ from litetopk_b200 import synth  # noqa: E402
 
 METRIC = "sparse_mla_prefill_query_tokens_per_s"
 # DRAM bytes per launch of masked_mla_fp8_kernel on the benchmark workload, from the ncu
-# capture summarised in profiles/ (None until captured)
-ATTN_DRAM_TRAFFIC_BYTES = None
+# capture summarised in profiles/masked_mla_fp8_kernel_c1_2048tok.md (scaled to 8192 tokens)
+ATTN_DRAM_TRAFFIC_BYTES = 729_000_000  # 196.4 MB captured on 2048 tokens, q/out/index part scaled x4
 
 
 def load_peaks():
@@ -382,7 +382,7 @@ def main():
         "all_gather_bytes_per_rank_per_step": (world - 1) * ng * 128 * 512 * 2,
         "roofline": {"kernel": "masked_mla_fp8_kernel", "bound": "tensor", "achieved": achieved,
                      "peak": fp8_peak, "unit": "TFLOP/s", "frac": achieved / fp8_peak,
-                     "traffic": ATTN_DRAM_TRAFFIC_BYTES,
+                     "traffic": ATTN_DRAM_TRAFFIC_BYTES if (w.name == "c1" and not args.tokens) else None,
                      "peak_source": f"2 x bf16 dense {peaks['bf16_tflops']} TFLOP/s of {peaks['source']} "
                                     "(FP8 dense is not in MEASURED_PEAKS.json); nominal FP8 dense 4500",
                      "kernel_ms_per_launch": attn_ms / n_chunks,
