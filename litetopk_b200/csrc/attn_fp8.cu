@@ -80,6 +80,8 @@ static_assert(sizeof(Misc) <= kMiscBytes, "Misc too large");
 
 struct AttnParams {
   const uint32_t* memb;      // [ng, G, cap/32]
+  const uint8_t* kv;         // [s_kv, kv_pitch] e4m3 rows (576 bytes used)
+  long long kv_pitch;        // bytes between KV rows
   const int32_t* indices;    // [ng, idx_stride]
   const int32_t* counts;     // [ng] or null
   __nv_bfloat16* out;        // [ng, 128, 512]
@@ -144,8 +146,8 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
       mbar_init(&ms.v_peer[i], 1);
       mbar_init(&ms.s_free[i], 8);        // 4 warps of one softmax group x 2 CTAs
       mbar_init(&ms.p_ready[i], 8);
-      mbar_init(&ms.k_land[i], 1);
-      mbar_init(&ms.v_land[i], 3);       // expect_tx arrival + the two copy warps
+      mbar_init(&ms.k_land[i], kProducerWarps * 32);        // one async arrival per gather thread
+      mbar_init(&ms.v_land[i], kProducerWarps * 32);        // one async arrival per gather thread
       mbar_init(&ms.k_copied[i], 2);
       mbar_init(&ms.qk_done[i], 1);
       mbar_init(&ms.pv_done[i], 1);
@@ -379,20 +381,27 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
       kb0 += nb;
     }
   } else if (warp < kSoftmaxWarps + kProducerWarps) {
-    // ------------------------------------------------------------ TMA producers (K rows, V rows of the peer's keys, Q tile)
-    // All eight warps issue gathers (the TMA unit takes more in flight from more warps).  Per
-    // block a warp owns ten K gathers (lanes 0-9: row quad pw + 8*(l/5), chunk l%5 of this CTA's
-    // 64 keys) and four V gathers (lanes 16-19: the PEER's keys, row quad pw + 8*((l-16)/2),
-    // value chunk (l-16)%2 of this CTA's dims; the own keys' value bytes are copied from the K
-    // tile by the copy warps).  K and V streams have different stage-free conditions (QK^T done
-    // vs PV done), so each warp advances two independent cursors and issues whichever is ready.
+    // ------------------------------------------------------------ KV row gather (cp.async) and the Q tile (TMA)
+    // The union rows are fetched with 16-byte cp.async copies issued by all 256 threads of
+    // these eight warps: fire-and-forget, any number of blocks in flight, destination written
+    // directly in the 128-byte-swizzled tile layout, completion reported to an mbarrier by an
+    // asynchronous arrival.  (TMA gather4 was measured at one instruction per ~8.5 ns per SM,
+    // i.e. ~1 us per block for this tile shape: it, not the tensor pipe, set the pace.)
+    // Warp pw owns rows [8pw, 8pw+8) of this CTA's 64 keys (K tile: all 576 bytes, nine copies
+    // per lane) and rows [16pw, 16pw+16) of the block's 128 keys (V tile: this CTA's 256 value
+    // bytes, eight copies per lane).  K and V streams have different stage-free conditions
+    // (QK^T done vs PV done), so each warp advances two independent cursors and issues
+    // whichever is ready; neither tile is derived from the other, so no stage waits on a copy.
     const int pw = warp - kSoftmaxWarps;
-    const int quad = pw + 8 * (lane / 5), chunk = lane % 5;
-    const bool k_active = lane < 10;
-    const int vl = lane - 16;
-    const bool v_active = vl >= 0 && vl < 4;
-    const int v_quad = 16 * (int)(cta ^ 1u) + pw + 8 * (vl >> 1), v_chunk = vl & 1;
     const uint32_t a_q_full = mapa(smem_u32(&ms.q_full), 0);
+    // the unused half of the fifth (rope) chunk of both K stages must read as zero
+    for (int i = pw * 32 + lane; i < 2 * 64 * 8; i += kProducerWarps * 32) {
+      const int st = i >> 9, rowp = (i >> 3) & 63, c8 = i & 7;
+      *reinterpret_cast<uint4*>(sm + kOffK + st * kKStage + 4 * kChunkBytes + rowp * 128 + c8 * 16) =
+          make_uint4(0u, 0u, 0u, 0u);
+    }
+    fence_proxy_async_smem();
+    asm volatile("bar.sync 4, 256;" ::: "memory");   // zeros are in place before any copy lands
     struct Cursor { int tile, it, k, nb, kb0; };
     auto cur_init = [&](Cursor& c) {
       c.tile = cid; c.it = 0; c.k = 0; c.kb0 = 0;
@@ -407,17 +416,19 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
     Cursor ck, cv;
     cur_init(ck);
     cur_init(cv);
-    auto k_idx = [&](const Cursor& c) {
-      return __ldg(reinterpret_cast<const int4*>(p.indices + (size_t)c.tile * p.idx_stride +
-                                                 (size_t)c.k * kBlockKeys + 64 * cta + 4 * (k_active ? quad : pw)));
+    // lane l < 16 holds the index of own key 8pw + l%8 (K tile rows), lane l >= 16 of key
+    // 16pw + l - 16 of the block's 128 keys (V tile rows)
+    const int my_key = lane < 16 ? 64 * (int)cta + 8 * pw + (lane & 7) : 16 * pw + (lane - 16);
+    auto load_idx = [&](const Cursor& c) -> int {
+      const int v = __ldg(p.indices + (size_t)c.tile * p.idx_stride + (size_t)c.k * kBlockKeys + my_key);
+      return ((unsigned)v < (unsigned)p.s_kv) ? v : 0;     // out-of-range rows are masked later
     };
-    auto v_idx = [&](const Cursor& c) {
-      return __ldg(reinterpret_cast<const int4*>(p.indices + (size_t)c.tile * p.idx_stride +
-                                                 (size_t)c.k * kBlockKeys + 4 * (v_active ? v_quad : pw)));
-    };
-    int4 kc = make_int4(0, 0, 0, 0), vc = make_int4(0, 0, 0, 0);
-    if (ck.tile < p.ng) { kc = k_idx(ck); vc = v_idx(cv); }
-    int q_tile = cid, q_it = 0;           // next Q tile to request (warp 0 only)
+    int kidx = 0, vidx = 0;
+    if (ck.tile < p.ng) { kidx = load_idx(ck); vidx = load_idx(cv); }
+    const uint8_t* kvb = p.kv;
+    const long long pitch = p.kv_pitch;
+    const int cj = lane >> 3, cc = lane & 7;       // latent piece `lane`: chunk cj, 16-byte slot cc
+    int q_tile = cid, q_it = 0;                    // next Q tile to request (warp 0 only)
     unsigned long long idle_since = 0;
     bool aborted = false;
     while ((ck.tile < p.ng || cv.tile < p.ng || (pw == 0 && q_tile < p.ng)) && !aborted) {
@@ -443,18 +454,28 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         const int kb = ck.kb0 + ck.k;
         const int s = kb & 1;
         const uint32_t ph = (kb >> 1) & 1;
-        // stage s held block kb-2: its QK^T must have read it and its value copies must be out
-        const bool ok = kb < 2 || (mbar_test(&ms.qk_done[s], ph ^ 1) && mbar_test(&ms.k_copied[s], ph ^ 1));
+        // stage s held block kb-2: its QK^T must have read it
+        const bool ok = kb < 2 || mbar_test(&ms.qk_done[s], ph ^ 1);
         if (__all_sync(0xffffffffu, ok)) {
           if (pw == 0) LT_TS(1, ck.k, 1);
-          if (pw == 0 && lane == 0) mbar_arrive_expect_tx(&ms.k_land[s], kKStage);
-          if (k_active)
-            tma_gather4(sbase + kOffK + s * kKStage + (uint32_t)quad * 512 + chunk * kChunkBytes, &map_kv,
-                        128 * chunk, kc, smem_u32(&ms.k_land[s]));
-          __syncwarp();
+          const uint32_t kst = sbase + kOffK + s * kKStage;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int ri = __shfl_sync(0xffffffffu, kidx, i);
+            const int row = 8 * pw + i;
+            cp_async16(kst + cj * kChunkBytes + row * 128 + ((cc ^ (row & 7)) << 4),
+                       kvb + (size_t)ri * pitch + 16 * lane);
+          }
+          {
+            const int ri = __shfl_sync(0xffffffffu, kidx, lane >> 2);
+            const int row = 8 * pw + (lane >> 2);
+            cp_async16(kst + 4 * kChunkBytes + row * 128 + (((lane & 3) ^ (row & 7)) << 4),
+                       kvb + (size_t)ri * pitch + 512 + 16 * (lane & 3));
+          }
+          cp_async_mbar_arrive_noinc(&ms.k_land[s]);
           if (pw == 0) LT_TS(1, ck.k, 2);
           cur_next(ck);
-          if (ck.tile < p.ng) kc = k_idx(ck);
+          if (ck.tile < p.ng) kidx = load_idx(ck);
           did = true;
         }
       }
@@ -465,13 +486,21 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         // V stage s was last read by the PV of block kb-2
         const bool ok = kb < 2 || mbar_test(&ms.pv_done[s], ph ^ 1);
         if (__all_sync(0xffffffffu, ok)) {
-          if (pw == 0 && lane == 0) mbar_arrive_expect_tx(&ms.v_land[s], kVStage / 2);
-          if (v_active)
-            tma_gather4(sbase + kOffV + s * kVStage + v_chunk * kVChunk + (uint32_t)v_quad * 512, &map_kv,
-                        256 * (int)cta + 128 * v_chunk, vc, smem_u32(&ms.v_land[s]));
-          __syncwarp();
+          const uint32_t vst = sbase + kOffV + s * kVStage;
+          // lane: row 16pw + 2i + lane/16 of the block's 128 keys, 16-byte piece lane%16 of this
+          // CTA's 256 value bytes
+          const int pc = lane & 15, nbk = pc >> 3, c8 = pc & 7;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rloc = 2 * i + (lane >> 4);
+            const int ri = __shfl_sync(0xffffffffu, vidx, 16 + rloc);
+            const int row = 16 * pw + rloc;
+            cp_async16(vst + nbk * kVChunk + row * 128 + ((c8 ^ (row & 7)) << 4),
+                       kvb + (size_t)ri * pitch + 256 * cta + 16 * pc);
+          }
+          cp_async_mbar_arrive_noinc(&ms.v_land[s]);
           cur_next(cv);
-          if (cv.tile < p.ng) vc = v_idx(cv);
+          if (cv.tile < p.ng) vidx = load_idx(cv);
           did = true;
         }
       }
@@ -584,49 +613,25 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
       }
     }
   } else if (warp == kWarpCopy || warp == kWarpRelay) {
-    // ------------------------------------------------------------ own keys' V bytes + relays
-    // The value dims of a key are the first 512 bytes of the row the K gather fetched.  Each
-    // of these two warps copies one 8 KB chunk (64 own keys x 128 bytes of this CTA's dims)
-    // from the K tile into rows [64*cta, +64) of the V tile -- both tiles use the same
-    // 128-byte swizzle, so the copy is linear -- and tells the leader CTA what has landed.
-    const int half = warp - kWarpCopy;            // value chunk nbk this warp copies
-    const uint32_t a_k_peer[2] = {mapa(smem_u32(&ms.k_peer[0]), 0), mapa(smem_u32(&ms.k_peer[1]), 0)};
-    const uint32_t a_v_peer[2] = {mapa(smem_u32(&ms.v_peer[0]), 0), mapa(smem_u32(&ms.v_peer[1]), 0)};
-    int kb0 = 0;
-    for (int tile = cid; tile < p.ng; tile += ncl) {
-      const int nb = blocks_of(tile_count(tile));
-      if (kDebug) ts_on = ts != nullptr && (tile == p.ng / 2) && lane == 0;
-      for (int k = 0; k < nb; ++k) {
-        const int kb = kb0 + k;
-        const int s = kb & 1;
-        const uint32_t ph = (kb >> 1) & 1;
-        if (half == 0) LT_TS(3, k, 0);
-        mbar_wait(&ms.k_land[s], ph, status, kSiteRelayK, k);
-        if (half == 0) LT_TS(3, k, 1);
-        if (half == 0 && cta == 1 && lane == 0) mbar_arrive_cluster(a_k_peer[s]);
-        if (kb >= 2) mbar_wait(&ms.pv_done[s], ph ^ 1, status, kSiteVFree, k);   // V stage s free
-        __syncwarp();
-        const uint4* src = reinterpret_cast<const uint4*>(sm + kOffK + s * kKStage + (2 * cta + half) * kChunkBytes);
-        uint4* dst = reinterpret_cast<uint4*>(sm + kOffV + s * kVStage + half * kVChunk + cta * kChunkBytes);
-        uint4 t[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) t[i] = src[i * 32 + lane];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) dst[i * 32 + lane] = t[i];
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(&ms.k_copied[s]);
-          mbar_arrive(&ms.v_land[s]);
+    // ------------------------------------------------------------ "landed" relays to the leader CTA
+    // The MMA thread lives in the leader CTA and can only wait on its own barriers: in the
+    // peer CTA warp 17 forwards "K tile landed" and warp 18 "V tile landed".
+    if (cta == 1) {
+      const bool is_k = warp == kWarpCopy;
+      const uint32_t a_peer[2] = {mapa(smem_u32(is_k ? &ms.k_peer[0] : &ms.v_peer[0]), 0),
+                                  mapa(smem_u32(is_k ? &ms.k_peer[1] : &ms.v_peer[1]), 0)};
+      int kb0 = 0;
+      for (int tile = cid; tile < p.ng; tile += ncl) {
+        const int nb = blocks_of(tile_count(tile));
+        for (int k = 0; k < nb; ++k) {
+          const int kb = kb0 + k;
+          const int s = kb & 1;
+          const uint32_t ph = (kb >> 1) & 1;
+          mbar_wait(is_k ? &ms.k_land[s] : &ms.v_land[s], ph, status, is_k ? kSiteRelayK : kSiteRelayV, k);
+          if (lane == 0) mbar_arrive_cluster_release(a_peer[s]);
         }
-        if (half == 0) LT_TS(3, k, 3);
-        if (half == 1) {
-          mbar_wait(&ms.v_land[s], ph, status, kSiteRelayV, k);
-          LT_TS(4, k, 0);
-          if (cta == 1 && lane == 0) mbar_arrive_cluster(a_v_peer[s]);
-        }
+        kb0 += nb;
       }
-      kb0 += nb;
     }
   } else {
     // ------------------------------------------------------------ index-validity bits
@@ -705,6 +710,7 @@ static int launch_fp8(const void* q8, const void* kv8, const int32_t* indices, f
     return LITEDSA_ERR_CUDA;
   AttnParams p;
   p.memb = memb; p.indices = indices; p.counts = counts;
+  p.kv = reinterpret_cast<const uint8_t*>(kv8); p.kv_pitch = kv_row_stride;
   p.out = reinterpret_cast<__nv_bfloat16*>(out); p.lse = lse; p.max_logits = max_logits;
   p.dbg = dbg;
   p.ng = ng; p.s_kv = s_kv; p.cap = topk; p.h_per_q = h_per_q; p.G = 128 / h_per_q;

@@ -218,6 +218,16 @@ __device__ __forceinline__ void bulk_copy_s2s(uint32_t dst_cluster, uint32_t src
       : "memory");
 }
 
+// 16-byte asynchronous global -> shared copy (LSU path, any shared destination) and the
+// asynchronous arrival that fires when all earlier cp.async of the thread have landed
+// (.noinc: the arrival counts against the barrier's expected count)
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 // ---------------------------------------------------------------- TMEM / tcgen05
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst_smem, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
