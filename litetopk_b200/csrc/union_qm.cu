@@ -30,6 +30,9 @@ struct UnionParams {
   const int32_t* req_pg;    // [ng] or null (identity table)
   const int32_t* btab;      // [nreq, bt_stride] or null
   int bt_stride, bt_blocks, bsz;
+  uint32_t bsz_mul;         // ceil(2^32 / bsz), or 0: divide
+  int kq;                   // k / 4: 16-byte loads per token row
+  uint32_t kq_mul;          // ceil(2^32 / kq), or 0: divide
   int k, G, cap, s_words;   // s_words = seq_space / 32
   int rank_shift;           // rank table holds one entry per (1 << rank_shift) bitmap words
   int stage_list;           // 1: sorted list staged in smem
@@ -46,11 +49,20 @@ __host__ __device__ inline size_t union_smem_bytes(int s_words, int rank_shift, 
   return b;
 }
 
+// n / d through a multiply-high when the host proved it exact (n * d < 2^32, d > 1)
+__device__ __forceinline__ int fast_div(int n, int d, uint32_t mul) {
+  return mul ? (int)__umulhi((uint32_t)n, mul) : n / d;
+}
+inline uint32_t fast_div_mul(int64_t n_max, int d) {
+  if (d <= 1 || n_max * d >= (int64_t(1) << 32)) return 0;
+  return (uint32_t)(((int64_t(1) << 32) + d - 1) / d);
+}
+
 template <int VPT>  // int4 loads cached per thread (0: nothing cached, second pass re-reads)
 __global__ void __launch_bounds__(kUnionThreads)
 union_qm_kernel(const UnionParams p) {
   extern __shared__ __align__(16) uint32_t smem[];
-  __shared__ int warp_tot[kUnionThreads / 32 + 1];
+  __shared__ int warp_tot[kUnionThreads / 32];
 
   const int g = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
   const int s_words = p.s_words, cap = p.cap, capw = cap >> 5, total = p.G * p.k;
@@ -95,7 +107,8 @@ union_qm_kernel(const UnionParams p) {
   }
   __syncthreads();
 
-  // phase 2: per-thread popcount of a contiguous run of words, block-wide exclusive scan
+  // phase 2: per-thread popcount of a contiguous run of words; warp scan, then every
+  // thread adds the totals of the warps before its own
   const int wpt = (s_words + kUnionThreads - 1) / kUnionThreads;   // words per thread
   const int w0 = min(tid * wpt, s_words), w1 = min(w0 + wpt, s_words);
   int mine = 0;
@@ -106,46 +119,25 @@ union_qm_kernel(const UnionParams p) {
     const int t = __shfl_up_sync(0xffffffffu, incl, off);
     if (lane >= off) incl += t;
   }
-  if (lane == 31) warp_tot[wid + 1] = incl;
-  if (tid == 0) warp_tot[0] = 0;
+  if (lane == 31) warp_tot[wid] = incl;
   __syncthreads();
-  if (wid == 0) {
-    int t = lane < kUnionThreads / 32 ? warp_tot[lane + 1] : 0;
+  int before = 0, count = 0;
 #pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-      const int u = __shfl_up_sync(0xffffffffu, t, off);
-      if (lane >= off) t += u;
-    }
-    if (lane < kUnionThreads / 32) warp_tot[lane + 1] = t;
+  for (int i = 0; i < kUnionThreads / 32; ++i) {
+    const int t = warp_tot[i];
+    before += i < wid ? t : 0;
+    count += t;
   }
-  __syncthreads();
-  const int count = warp_tot[kUnionThreads / 32];
   const int live = min(count, cap);
   if (tid == 0) p.counts[g] = count;
 
-  // phase 3: rank table + ascending emit (logical -> physical through the block table)
-  const int32_t* bt_row = p.btab ? p.btab + (size_t)p.req_pg[g] * p.bt_stride : nullptr;
-  int32_t* out_row = p.u_phys + (size_t)g * cap;
+  // phase 3: exclusive rank of every bitmap word (or every 2^rank_shift-th word)
   {
-    int r = warp_tot[wid] + incl - mine;
+    int r = before + incl - mine;
     const int rmask = (1 << p.rank_shift) - 1;
     for (int w = w0; w < w1; ++w) {
       if ((w & rmask) == 0) rtab[w >> p.rank_shift] = (uint16_t)r;
-      uint32_t m = bm[w];
-      while (m) {
-        const int b = __ffs(m) - 1;
-        m &= m - 1;
-        if (r < cap) {
-          const int pos = (w << 5) | b;
-          int phys = pos;
-          if (bt_row) {
-            const int blk = pos / p.bsz;
-            phys = blk < p.bt_blocks ? bt_row[blk] * p.bsz + (pos - blk * p.bsz) : -1;
-          }
-          if (p.stage_list) list_s[r] = phys; else out_row[r] = phys;
-        }
-        ++r;
-      }
+      r += __popc(bm[w]);
     }
   }
   // live mask words per query row: max(4, roundup4(ceil(live / 32)))
@@ -153,28 +145,43 @@ union_qm_kernel(const UnionParams p) {
   for (int i = tid; i < p.G * active; i += kUnionThreads) qm_s[i] = 0u;
   __syncthreads();
 
-  // phase 4: membership bits (rank of every candidate of every token)
-  auto mark = [&](int pos, int e) {
+  // phase 4: every candidate looks up its rank, sets its token's membership bit and
+  // writes its own slot of the sorted list (duplicates write the same value)
+  const int32_t* bt_row = p.btab ? p.btab + (size_t)p.req_pg[g] * p.bt_stride : nullptr;
+  int32_t* out_row = p.u_phys + (size_t)g * cap;
+  int32_t* list_dst = p.stage_list ? list_s : out_row;
+  auto mark = [&](int pos, int qrow) {
     if ((unsigned)pos >= (unsigned)S) return;
     const int w = pos >> 5;
     int r = rtab[w >> p.rank_shift];
-    for (int x = (w >> p.rank_shift) << p.rank_shift; x < w; ++x) r += __popc(bm[x]);
+    if (p.rank_shift)
+      for (int x = (w >> p.rank_shift) << p.rank_shift; x < w; ++x) r += __popc(bm[x]);
     r += __popc(bm[w] & ((1u << (pos & 31)) - 1u));
-    if (r < cap) atomicOr(&qm_s[(e / p.k) * active + (r >> 5)], 1u << (r & 31));
+    if (r >= cap) return;
+    atomicOr(&qm_s[qrow + (r >> 5)], 1u << (r & 31));
+    int phys = pos;
+    if (bt_row) {
+      const int blk = fast_div(pos, p.bsz, p.bsz_mul);
+      phys = blk < p.bt_blocks ? bt_row[blk] * p.bsz + (pos - blk * p.bsz) : -1;
+    }
+    list_dst[r] = phys;
   };
   if (VPT > 0) {
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      const int e = (i * kUnionThreads + tid) << 2;
-      mark(v[i].x, e); mark(v[i].y, e + 1); mark(v[i].z, e + 2); mark(v[i].w, e + 3);
+      // k % 4 == 0: the four candidates of one 16-byte load belong to one token
+      const int qrow = fast_div(i * kUnionThreads + tid, p.kq, p.kq_mul) * active;
+      mark(v[i].x, qrow); mark(v[i].y, qrow); mark(v[i].z, qrow); mark(v[i].w, qrow);
     }
   } else {
     for (int qd = tid; qd < nquad; qd += kUnionThreads) {
       const int4 t = __ldg(src + qd);
-      const int e = qd << 2;
-      mark(t.x, e); mark(t.y, e + 1); mark(t.z, e + 2); mark(t.w, e + 3);
+      const int qrow = fast_div(qd, p.kq, p.kq_mul) * active;
+      mark(t.x, qrow); mark(t.y, qrow); mark(t.z, qrow); mark(t.w, qrow);
     }
   }
+  __syncthreads();
+
   // sorted list -> global, 16-byte stores (the last quad is padded with -1)
   if (p.stage_list) {
     const int q_live = (live + 3) >> 2;
@@ -192,7 +199,6 @@ union_qm_kernel(const UnionParams p) {
   } else if (p.fill_tail) {
     for (int i = live + tid; i < cap; i += kUnionThreads) out_row[i] = -1;
   }
-  __syncthreads();
 
   // phase 5: dump the live mask words (whole rows when fill_tail)
   {
@@ -238,11 +244,14 @@ extern "C" int litedsa_union_qm(const int32_t* topk_indices, int32_t* u_phys, in
   if ((block_table != nullptr) != (req_pg != nullptr)) return LITEDSA_ERR_ARG;
   if (block_table && (block_size <= 0 || bt_blocks <= 0 || bt_rows <= 0)) return LITEDSA_ERR_SHAPE;
   if (k % 4 != 0) return LITEDSA_ERR_UNSUPPORTED;    // 16-byte row loads
+  if (cap > 65536) return LITEDSA_ERR_UNSUPPORTED;   // 16-bit rank table
 
   UnionParams p;
   p.idx = topk_indices; p.u_phys = u_phys; p.counts = counts; p.memb = memb_qm;
   p.req_pg = req_pg; p.btab = block_table;
   p.bt_stride = bt_blocks; p.bt_blocks = bt_blocks; p.bsz = block_table ? block_size : 1;
+  p.bsz_mul = fast_div_mul(int64_t(s_words) * 32, p.bsz);
+  p.kq = k / 4; p.kq_mul = fast_div_mul(int64_t(G) * (k / 4), k / 4);
   p.k = k; p.G = G; p.cap = cap; p.s_words = s_words; p.fill_tail = fill_tail ? 1 : 0;
   // pick the richest shared-memory plan that fits (227 KB per CTA on sm_100)
   const size_t limit = 220 * 1024;
