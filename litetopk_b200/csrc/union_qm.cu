@@ -20,7 +20,6 @@
 
 namespace lt {
 
-constexpr int kUnionThreads = 256;
 
 struct UnionParams {
   const int32_t* idx;       // [T, k]
@@ -58,9 +57,12 @@ inline uint32_t fast_div_mul(int64_t n_max, int d) {
   return (uint32_t)(((int64_t(1) << 32) + d - 1) / d);
 }
 
-template <int VPT>  // int4 loads cached per thread (0: nothing cached, second pass re-reads)
-__global__ void __launch_bounds__(kUnionThreads)
+// NT threads per tile; VPT int4 loads cached per thread (0: nothing cached, the second
+// pass re-reads the tile)
+template <int NT, int VPT>
+__global__ void __launch_bounds__(NT)
 union_qm_kernel(const UnionParams p) {
+  constexpr int kUnionThreads = NT;
   extern __shared__ __align__(16) uint32_t smem[];
   __shared__ int warp_tot[kUnionThreads / 32];
 
@@ -213,9 +215,10 @@ union_qm_kernel(const UnionParams p) {
   }
 }
 
-template <int VPT>
+template <int NT, int VPT>
 static int launch_union(const UnionParams& p, int ng, size_t smem, cudaStream_t stream) {
-  auto kern = union_qm_kernel<VPT>;
+  constexpr int kUnionThreads = NT;
+  auto kern = union_qm_kernel<NT, VPT>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return LITEDSA_ERR_CUDA;
   kern<<<ng, kUnionThreads, smem, stream>>>(p);
@@ -262,9 +265,19 @@ extern "C" int litedsa_union_qm(const int32_t* topk_indices, int32_t* u_phys, in
   if (smem > limit) return LITEDSA_ERR_UNSUPPORTED;
 
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const int quads_per_thread = (G * k / 4 + kUnionThreads - 1) / kUnionThreads;
-  if (quads_per_thread <= 1) return launch_union<1>(p, ng, smem, st);
-  if (quads_per_thread <= 4) return launch_union<4>(p, ng, smem, st);
-  if (quads_per_thread <= 16) return launch_union<16>(p, ng, smem, st);
-  return launch_union<0>(p, ng, smem, st);
+  const int quads = G * k / 4;
+  // small tiles: 256-thread CTAs, several per SM; tiles whose shared memory leaves room for
+  // only a few CTAs per SM get 1024 threads each to keep the SM's warp slots filled
+  if (smem <= 48 * 1024) {
+    const int qpt = (quads + 255) / 256;
+    if (qpt <= 1) return launch_union<256, 1>(p, ng, smem, st);
+    if (qpt <= 4) return launch_union<256, 4>(p, ng, smem, st);
+    if (qpt <= 16) return launch_union<256, 16>(p, ng, smem, st);
+    return launch_union<256, 0>(p, ng, smem, st);
+  }
+  const int qpt = (quads + 1023) / 1024;
+  if (qpt <= 2) return launch_union<1024, 2>(p, ng, smem, st);
+  if (qpt <= 4) return launch_union<1024, 4>(p, ng, smem, st);
+  if (qpt <= 8) return launch_union<1024, 8>(p, ng, smem, st);
+  return launch_union<1024, 0>(p, ng, smem, st);
 }
