@@ -27,6 +27,9 @@
 #include "tensor_map.cuh"
 
 namespace lt {
+constexpr unsigned kIdleCheckEvery = 64;   // idle polls between two time-limit checks (power of two)
+constexpr unsigned kIdleSleepNs = 8;       // back-off of an idle poll
+
 
 constexpr int kSoftmaxWarps = 8, kProducerWarps = 8;
 constexpr int kWarpMma = 16, kWarpCopy = 17, kWarpRelay = 18, kWarpValid = 19;
@@ -430,6 +433,7 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
     const int cj = lane >> 3, cc = lane & 7;       // latent piece `lane`: chunk cj, 16-byte slot cc
     int q_tile = cid, q_it = 0;                    // next Q tile to request (warp 0 only)
     unsigned long long idle_since = 0;
+    unsigned idle_iters = 0;
     bool aborted = false;
     while ((ck.tile < p.ng || cv.tile < p.ng || (pw == 0 && q_tile < p.ng)) && !aborted) {
       bool did = false;
@@ -506,7 +510,11 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
       }
       if (did) {
         idle_since = 0;
+        idle_iters = 0;
+      } else if ((++idle_iters & (kIdleCheckEvery - 1)) != 0) {
+        __nanosleep(kIdleSleepNs);
       } else {
+        // the (slow) time-limit and abort check runs once per kIdleCheckEvery idle polls
         const unsigned long long now = globaltimer_ns();
         if (idle_since == 0) idle_since = now;
         bool stop = *reinterpret_cast<volatile int*>(status) != 0;
@@ -564,6 +572,7 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         // the tile's first PV the previous tile's O read out) is ready goes first.
         int qk_i = 0, pv_i = 0;
         unsigned long long idle_since = 0;
+        unsigned idle_iters = 0;
         while (pv_i < nb && !aborted) {
           bool did = false;
           {
@@ -598,6 +607,9 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
           }
           if (did) {
             idle_since = 0;
+            idle_iters = 0;
+          } else if ((++idle_iters & (kIdleCheckEvery - 1)) != 0) {
+            __nanosleep(kIdleSleepNs);
           } else {
             const unsigned long long now = globaltimer_ns();
             if (idle_since == 0) idle_since = now;
