@@ -115,7 +115,8 @@ __device__ int g_attn_status[4];
 template <bool kDebug>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kAttnThreads, 1)
 masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
-                      const __grid_constant__ CUtensorMap map_kv, const AttnParams p) {
+                      const __grid_constant__ CUtensorMap map_kv,
+                      const __grid_constant__ CUtensorMap map_out, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t sbase = (raw + 1023u) & ~1023u;       // 128B-swizzle tiles need 1024-byte alignment
@@ -161,6 +162,7 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
     fence_mbar_init();
     tma_prefetch_desc(&map_q);
     tma_prefetch_desc(&map_kv);
+    tma_prefetch_desc(&map_out);
   }
   __syncthreads();
   cluster_sync_all();
@@ -317,6 +319,7 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
 
       // end of tile: merge the two groups' row sums (each relative to its own latest running max)
       const int t = threadIdx.x;                    // 0..255 = g*128 + tl
+      if (warp == 0) LT_TS(3, 0, 0);
       ms.fin[0][t] = li;
       ms.fin[1][t] = real_m;
       ms.fin[2][t] = m_mine;
@@ -344,17 +347,40 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         p.lse[grow] = l;
         if (p.max_logits) p.max_logits[grow] = real_m * kLn2;
       }
+      if (warp == 0) LT_TS(3, 0, 1);
       mbar_wait(&ms.pv_done[kbl & 1], (kbl >> 1) & 1, status, kSiteEpi, nb);
+      if (warp == 0) LT_TS(3, 0, 2);
       tc_fence_after();
       const bool empty = !(li > 0.f);
       const float oscale = empty ? 0.f : __fdividef(p.out_scale, li);
-      // group g writes dims [256h + 128g, +128) of its row
-      __nv_bfloat16* orow = p.out + grow * kDV + 256 * h + 128 * g;
-      float o[32];
-#pragma unroll 1
+      // Each thread owns dims [256h + 128g, +128) of its row, 32 dims (64 bytes) per round.  A
+      // warp stages its round (32 rows x 64 bytes, 64-byte swizzle: the 16-byte stores of eight
+      // consecutive rows hit distinct banks) in its own 2 KB slice of the group's P buffer
+      // (free: every PV of the tile has completed) and one lane hands the box to TMA:
+      // full-sector asynchronous writes instead of 32 scattered 16-byte stores per warp
+      // instruction, and no barrier wider than the warp.
+      const int rhalf = (warp & 1);                                  // rows [32 rhalf, +32) of the CTA
+      const uint32_t stage_off = kOffP + g * kPBytes + h * 4096 + rhalf * 2048;
+      uint8_t* st_row = sm + stage_off + (r & 31) * 64;
+      const int sw = (r >> 1) & 3;
+      const int out_x = 256 * h + 128 * g;
+      const int out_y = tile * 128 + (int)cta * 64 + 32 * rhalf;
+      const uint32_t emask = empty ? 0u : 0xffffffffu;
+      const uint32_t ocol = tmem + lane_base + kTmemO + g * 128;
+      float ob[2][32];
+      tmem_ld32(ocol, ob[0]);
+#pragma unroll
       for (int cc = 0; cc < 4; ++cc) {
-        tmem_ld32(tmem + lane_base + kTmemO + g * 128 + cc * 32, o);
+        float* o = ob[cc & 1];
         tmem_wait_ld();
+        if (cc < 3) {
+          tmem_ld32(ocol + (cc + 1) * 32, ob[(cc + 1) & 1]);
+        } else {
+          // O has been read: the next tile's first PV may overwrite it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(a_o_free);
+        }
         if (kDebug && p.dbg && tile == 0) {
           float* d = p.dbg + (size_t)p.cap * 128 + (size_t)row * 512 + 256 * h + 128 * g + cc * 32;
 #pragma unroll
@@ -363,26 +389,37 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         uint32_t w[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          const float a = empty ? 0.f : o[2 * j] * oscale;
-          const float b = empty ? 0.f : o[2 * j + 1] * oscale;
-          __nv_bfloat162 v2 = __floats2bfloat162_rn(a, b);
-          w[j] = *reinterpret_cast<uint32_t*>(&v2);
+          __nv_bfloat162 v2 = __floats2bfloat162_rn(o[2 * j] * oscale, o[2 * j + 1] * oscale);
+          w[j] = *reinterpret_cast<uint32_t*>(&v2) & emask;    // rows without a valid key: zeros
         }
-        uint4* dst = reinterpret_cast<uint4*>(orow + cc * 32);
+        if (cc > 0) {   // the previous round's box must have been read out of the slice
+          if (lane == 0) bulk_wait_read_all();
+          __syncwarp();
+        }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) dst[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+        for (int j = 0; j < 4; ++j)
+          *reinterpret_cast<uint4*>(st_row + ((j ^ sw) << 4)) =
+              make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&map_out, sbase + stage_off, out_x + 32 * cc, out_y);
+          bulk_commit_group();
+        }
       }
+      // The slices are P again in the next tile: the issuing lane waits for its last box to be
+      // read, and every P store of the next tile comes after a group barrier (the row-max
+      // exchange) that each issuing lane only reaches after this wait.
+      if (lane == 0) bulk_wait_read_all();
       if (kDebug && p.dbg && tile == 0 && g == 0 && h == 0) {
         float* d = p.dbg + (size_t)p.cap * 128 + 128 * 512;
         d[row] = m;
         d[128 + row] = li;
       }
-      // O has been read: the next tile's first PV may overwrite it
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(a_o_free);
+      if (warp == 0) LT_TS(3, 0, 3);
       kb0 += nb;
     }
+    if (lane == 0) bulk_wait_all();   // output boxes written before the CTA retires
   } else if (warp < kSoftmaxWarps + kProducerWarps) {
     // ------------------------------------------------------------ KV row gather (cp.async) and the Q tile (TMA)
     // The union rows are fetched with 16-byte cp.async copies issued by all 256 threads of
@@ -713,7 +750,11 @@ static int launch_fp8(const void* q8, const void* kv8, const int32_t* indices, f
                       void* out, float* max_logits, float* lse, int ng, int s_kv, int topk,
                       long long q_row_stride, long long kv_row_stride, long long idx_row_stride,
                       float* dbg, cudaStream_t stream) {
-  CUtensorMap map_q, map_kv;
+  CUtensorMap map_q, map_kv, map_out;
+  // out is stored as boxes of 32 rows x 32 dims (64 bytes wide, 64-byte swizzle)
+  if (!make_map_2d(&map_out, out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, kDV, (uint64_t)ng * 128,
+                   (uint64_t)kDV * 2, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B))
+    return LITEDSA_ERR_CUDA;
   if (!make_map_2d(&map_q, q8, CU_TENSOR_MAP_DATA_TYPE_UINT8, kDQK, (uint64_t)ng * 128,
                    (uint64_t)q_row_stride, 128, 64))
     return LITEDSA_ERR_CUDA;
@@ -732,7 +773,7 @@ static int launch_fp8(const void* q8, const void* kv8, const int32_t* indices, f
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem) !=
       cudaSuccess)
     return LITEDSA_ERR_CUDA;
-  kern<<<2 * min(ng, max_clusters()), kAttnThreads, kAttnSmem, stream>>>(map_q, map_kv, p);
+  kern<<<2 * min(ng, max_clusters()), kAttnThreads, kAttnSmem, stream>>>(map_q, map_kv, map_out, p);
   return cudaGetLastError() == cudaSuccess ? LITEDSA_OK : LITEDSA_ERR_CUDA;
 }
 

@@ -221,6 +221,23 @@ __device__ __forceinline__ void bulk_copy_s2s(uint32_t dst_cluster, uint32_t src
 // 16-byte asynchronous global -> shared copy (LSU path, any shared destination) and the
 // asynchronous arrival that fires when all earlier cp.async of the thread have landed
 // (.noinc: the arrival counts against the barrier's expected count)
+// TMA tile store shared -> global (bulk async-group completion)
+__device__ __forceinline__ void tma_store_2d(const void* map, uint32_t src_smem, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               :: "l"(map), "r"(src_smem), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// all committed bulk groups of this thread have finished READING their shared-memory source
+__device__ __forceinline__ void bulk_wait_read_all() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+// all committed bulk groups of this thread are complete (writes performed)
+__device__ __forceinline__ void bulk_wait_all() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
 __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
 }

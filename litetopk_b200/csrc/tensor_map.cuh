@@ -27,10 +27,12 @@ inline EncodeTiledFn encode_tiled_fn() {
 }
 
 // 2-D row-major tensor [rows, cols] of `elem_bytes`-wide elements, row pitch in bytes,
-// box = box_cols x box_rows, 128-byte swizzle, out-of-bounds elements read as zero.
+// box = box_cols x box_rows, 128-byte swizzle unless told otherwise, out-of-bounds elements
+// read as zero (and are not written by stores).
 inline bool make_map_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dtype,
                         uint64_t cols, uint64_t rows, uint64_t pitch_bytes, uint32_t box_cols,
-                        uint32_t box_rows) {
+                        uint32_t box_rows,
+                        CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return false;
   cuuint64_t size[2] = {cols, rows};
@@ -38,7 +40,7 @@ inline bool make_map_2d(CUtensorMap* map, const void* base, CUtensorMapDataType 
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
   return fn(map, dtype, 2, const_cast<void*>(base), size, stride, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
