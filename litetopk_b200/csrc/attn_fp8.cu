@@ -49,7 +49,9 @@ constexpr uint32_t kOffV = kOffK + 2 * kKStage;
 constexpr uint32_t kOffP = kOffV + 2 * kVStage;
 constexpr uint32_t kOffMisc = kOffP + 2 * kPBytes;   // 204800
 constexpr uint32_t kMiscBytes = 7168;
-constexpr uint32_t kAttnSmem = kOffMisc + kMiscBytes + 1024;  // + alignment slack
+constexpr uint32_t kOffStage = kOffMisc + kMiscBytes;  // 8 x 2 KB output staging slices
+constexpr uint32_t kStageBytes = 8 * 2048;
+constexpr uint32_t kAttnSmem = kOffStage + kStageBytes + 1024;  // + alignment slack
 static_assert(kAttnSmem <= 232448, "shared-memory plan exceeds the 227 KB per-CTA limit");
 
 constexpr uint32_t kTmemCols = 512;
@@ -72,12 +74,14 @@ struct Misc {
   uint64_t m_pub[2];                // running max of block k published by softmax group k%2
   uint64_t q_free;                  // all QK^T of the current tile are complete (Q tile reusable)
   uint64_t o_free;                  // leader CTA: the tile's O has been read out of TMEM
+  uint64_t epi_ready;               // the tile's row scales are published (softmax warps)
   uint32_t valid[2][4];             // 128 validity bits per stage
   uint32_t tmem_base;
   uint32_t pad;
   float xbuf[2][2][128];            // [group][parity][lane]: row-max exchange between key halves
   float mshare[2][128];             // [group][lane]: running max after the group's latest block
   float fin[3][256];                // end of tile: row sums, true maxima, last running max
+  float oscale[2][64];              // [tile parity][row]: out_scale / l, 0 for rows without a key
 };
 static_assert(sizeof(Misc) <= kMiscBytes, "Misc too large");
 
@@ -144,7 +148,8 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
   if (threadIdx.x == 0) {
     mbar_init(&ms.q_full, 1);
     mbar_init(&ms.q_free, 1);
-    mbar_init(&ms.o_free, 2 * kSoftmaxWarps);
+    mbar_init(&ms.o_free, 2 * kProducerWarps);
+    mbar_init(&ms.epi_ready, kSoftmaxWarps);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&ms.k_peer[i], 1);
       mbar_init(&ms.v_peer[i], 1);
@@ -193,9 +198,8 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
     const float c = p.scale_log2;
     const uint32_t a_s_free = mapa(smem_u32(&ms.s_free[g]), 0);
     const uint32_t a_p_ready = mapa(smem_u32(&ms.p_ready[g]), 0);
-    const uint32_t a_o_free = mapa(smem_u32(&ms.o_free), 0);
     const uint32_t scol = tmem + lane_base + (g ? kTmemS1 : kTmemS0);
-    int kb0 = 0;
+    int kb0 = 0, it = 0;
 
     for (int tile = cid; tile < p.ng; tile += ncl) {
       const int nb = blocks_of(tile_count(tile));
@@ -347,79 +351,20 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         p.lse[grow] = l;
         if (p.max_logits) p.max_logits[grow] = real_m * kLn2;
       }
+      // Hand the tile over to the gather warps, which read O out of TMEM, scale it and store
+      // it while these warps already work on the next tile: all they need is 1 / l per row.
+      if (g == 0 && h == 0) ms.oscale[it & 1][r] = (li > 0.f) ? __fdividef(p.out_scale, li) : 0.f;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ms.epi_ready);
       if (warp == 0) LT_TS(3, 0, 1);
-      mbar_wait(&ms.pv_done[kbl & 1], (kbl >> 1) & 1, status, kSiteEpi, nb);
-      if (warp == 0) LT_TS(3, 0, 2);
-      tc_fence_after();
-      const bool empty = !(li > 0.f);
-      const float oscale = empty ? 0.f : __fdividef(p.out_scale, li);
-      // Each thread owns dims [256h + 128g, +128) of its row, 32 dims (64 bytes) per round.  A
-      // warp stages its round (32 rows x 64 bytes, 64-byte swizzle: the 16-byte stores of eight
-      // consecutive rows hit distinct banks) in its own 2 KB slice of the group's P buffer
-      // (free: every PV of the tile has completed) and one lane hands the box to TMA:
-      // full-sector asynchronous writes instead of 32 scattered 16-byte stores per warp
-      // instruction, and no barrier wider than the warp.
-      const int rhalf = (warp & 1);                                  // rows [32 rhalf, +32) of the CTA
-      const uint32_t stage_off = kOffP + g * kPBytes + h * 4096 + rhalf * 2048;
-      uint8_t* st_row = sm + stage_off + (r & 31) * 64;
-      const int sw = (r >> 1) & 3;
-      const int out_x = 256 * h + 128 * g;
-      const int out_y = tile * 128 + (int)cta * 64 + 32 * rhalf;
-      const uint32_t emask = empty ? 0u : 0xffffffffu;
-      const uint32_t ocol = tmem + lane_base + kTmemO + g * 128;
-      float ob[2][32];
-      tmem_ld32(ocol, ob[0]);
-#pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
-        float* o = ob[cc & 1];
-        tmem_wait_ld();
-        if (cc < 3) {
-          tmem_ld32(ocol + (cc + 1) * 32, ob[(cc + 1) & 1]);
-        } else {
-          // O has been read: the next tile's first PV may overwrite it
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(a_o_free);
-        }
-        if (kDebug && p.dbg && tile == 0) {
-          float* d = p.dbg + (size_t)p.cap * 128 + (size_t)row * 512 + 256 * h + 128 * g + cc * 32;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) d[j] = o[j];
-        }
-        uint32_t w[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          __nv_bfloat162 v2 = __floats2bfloat162_rn(o[2 * j] * oscale, o[2 * j + 1] * oscale);
-          w[j] = *reinterpret_cast<uint32_t*>(&v2) & emask;    // rows without a valid key: zeros
-        }
-        if (cc > 0) {   // the previous round's box must have been read out of the slice
-          if (lane == 0) bulk_wait_read_all();
-          __syncwarp();
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          *reinterpret_cast<uint4*>(st_row + ((j ^ sw) << 4)) =
-              make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          tma_store_2d(&map_out, sbase + stage_off, out_x + 32 * cc, out_y);
-          bulk_commit_group();
-        }
-      }
-      // The slices are P again in the next tile: the issuing lane waits for its last box to be
-      // read, and every P store of the next tile comes after a group barrier (the row-max
-      // exchange) that each issuing lane only reaches after this wait.
-      if (lane == 0) bulk_wait_read_all();
       if (kDebug && p.dbg && tile == 0 && g == 0 && h == 0) {
         float* d = p.dbg + (size_t)p.cap * 128 + 128 * 512;
         d[row] = m;
         d[128 + row] = li;
       }
-      if (warp == 0) LT_TS(3, 0, 3);
       kb0 += nb;
+      ++it;
     }
-    if (lane == 0) bulk_wait_all();   // output boxes written before the CTA retires
   } else if (warp < kSoftmaxWarps + kProducerWarps) {
     // ------------------------------------------------------------ KV row gather (cp.async) and the Q tile (TMA)
     // The union rows are fetched with 16-byte cp.async copies issued by all 256 threads of
@@ -453,9 +398,22 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         c.nb = c.tile < p.ng ? blocks_of(tile_count(c.tile)) : 0;
       }
     };
-    Cursor ck, cv;
+    Cursor ck, cv, ce;   // K gather, V gather, epilogue
     cur_init(ck);
     cur_init(cv);
+    cur_init(ce);
+    // Epilogue duty: gather warp pw reads the TMEM lanes of its quarter (warp % 4), i.e. rows
+    // r of key half h, dims [256h + 128(pw / 4), +128), 32 dims (64 bytes) per round.  A round
+    // is staged in the warp's own 2 KB slice (32 rows x 64 bytes, 64-byte swizzle: the 16-byte
+    // stores of eight consecutive rows hit distinct banks) and one lane hands the box to TMA:
+    // full-sector asynchronous writes, no barrier wider than the warp.
+    const int e_tl = ((warp & 3) << 5) | lane, e_r = e_tl & 63, e_h = e_tl >> 6, e_g = pw >> 2;
+    const uint32_t e_stage = kOffStage + pw * 2048;
+    uint8_t* e_st_row = sm + e_stage + (e_r & 31) * 64;
+    const int e_sw = (e_r >> 1) & 3;
+    const uint32_t e_ocol = tmem + ((uint32_t)((warp & 3) * 32) << 16) + kTmemO + e_g * 128;
+    const uint32_t a_o_free = mapa(smem_u32(&ms.o_free), 0);
+    int e_round = 0;
     // lane l < 16 holds the index of own key 8pw + l%8 (K tile rows), lane l >= 16 of key
     // 16pw + l - 16 of the block's 128 keys (V tile rows)
     const int my_key = lane < 16 ? 64 * (int)cta + 8 * pw + (lane & 7) : 16 * pw + (lane - 16);
@@ -472,8 +430,63 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
     unsigned long long idle_since = 0;
     unsigned idle_iters = 0;
     bool aborted = false;
-    while ((ck.tile < p.ng || cv.tile < p.ng || (pw == 0 && q_tile < p.ng)) && !aborted) {
+    while ((ck.tile < p.ng || cv.tile < p.ng || ce.tile < p.ng || (pw == 0 && q_tile < p.ng)) && !aborted) {
       bool did = false;
+      if (ce.tile < p.ng) {
+        const int kbl = ce.kb0 + ce.nb - 1;          // last block of the tile
+        // the row scales are published and the tile's last PV has completed
+        const bool ok = e_round > 0 || (mbar_test(&ms.epi_ready, ce.it & 1) &&
+                                        mbar_test(&ms.pv_done[kbl & 1], (kbl >> 1) & 1));
+        if (__all_sync(0xffffffffu, ok)) {
+          if (kDebug) ts_on = ts != nullptr && (ce.tile == p.ng / 2) && lane == 0;
+          if (pw == 0) LT_TS(3, 1 + e_round, 0);
+          const float oscale = ms.oscale[ce.it & 1][e_r];
+          const uint32_t emask = oscale != 0.f ? 0xffffffffu : 0u;
+          float o[32];
+          tc_fence_after();
+          tmem_ld32(e_ocol + e_round * 32, o);
+          tmem_wait_ld();
+          if (e_round == 3) {
+            // O has been read: the next tile's first PV may overwrite it
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(a_o_free);
+          }
+          if (kDebug && p.dbg && ce.tile == 0) {
+            float* d = p.dbg + (size_t)p.cap * 128 + (size_t)((int)cta * 64 + e_r) * 512 + 256 * e_h +
+                       128 * e_g + e_round * 32;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) d[j] = o[j];
+          }
+          uint32_t w[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            __nv_bfloat162 v2 = __floats2bfloat162_rn(o[2 * j] * oscale, o[2 * j + 1] * oscale);
+            w[j] = *reinterpret_cast<uint32_t*>(&v2) & emask;    // rows without a valid key: zeros
+          }
+          // the previous round's box must have been read out of the slice
+          if (lane == 0) bulk_wait_read_all();
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(e_st_row + ((j ^ e_sw) << 4)) =
+                make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&map_out, sbase + e_stage, 256 * e_h + 128 * e_g + 32 * e_round,
+                         ce.tile * 128 + (int)cta * 64 + 32 * (warp & 1));
+            bulk_commit_group();
+          }
+          if (pw == 0) LT_TS(3, 1 + e_round, 1);
+          if (++e_round == 4) {
+            e_round = 0;
+            ce.k = ce.nb - 1;
+            cur_next(ce);
+          }
+          did = true;
+        }
+      }
       if (pw == 0 && q_tile < p.ng) {
         // the previous tile's Q must have been consumed by its last QK^T
         const bool okq = q_it == 0 || mbar_test(&ms.q_free, (q_it - 1) & 1);
@@ -562,6 +575,7 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         aborted = __any_sync(0xffffffffu, stop);
       }
     }
+    if (lane == 0) bulk_wait_all();   // output boxes written before the CTA retires
   } else {
    if (warp == kWarpMma) {
     // ------------------------------------------------------------ MMA issue (leader CTA only)
