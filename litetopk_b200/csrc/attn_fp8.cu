@@ -11,17 +11,25 @@
 // Those numerics are reproduced exactly so the two implementations agree to rounding.
 //
 // How it is organised here (written from scratch, raw PTX, no CuTe):
-//   * one cluster of 2 CTAs per tile; each CTA owns 64 query rows.  Both GEMMs are
-//     single tcgen05 cta_group::2 instructions spanning the pair: QK^T splits the 128
-//     keys of a block across the CTAs (N split), PV splits the 512 value dims (N split).
-//   * 6 warps per CTA: warps 0-3 softmax + epilogue (one TMEM lane per thread),
-//     warp 4 = TMA producer (Q tile, row gathers for K and V, index-validity bits),
-//     warp 5 = MMA issue (one thread of the leader CTA) and TMEM allocation.
-//   * every tile of the 576-byte rows is stored as five 128-byte-swizzled column
-//     chunks (the fifth is half zero-filled by TMA bounds handling), so Q, K and V all
-//     share one shared-memory geometry and one tensor-map shape.
-//   * completion is tracked with mbarriers only; every wait is bounded (common.cuh)
-//     and reports through a status word instead of trapping.
+//   * persistent: one cluster of 2 CTAs per SM pair walks tiles cid, cid + #clusters, ...;
+//     each CTA owns 64 query rows.  Both GEMMs are single tcgen05 cta_group::2 instructions
+//     spanning the pair: QK^T splits the 128 keys of a block across the CTAs (N split), PV
+//     splits the 512 value dims (N split).
+//   * 20 warps per CTA:
+//       warps 0-7   softmax, two groups of four warps on alternate key blocks (one TMEM lane
+//                   per thread, 64 S columns each);
+//       warps 8-15  KV row gather with 16-byte cp.async copies written straight into the
+//                   128-byte-swizzled tile layout (K: own 64 keys x 576 bytes; V: all 128 keys
+//                   x this CTA's 256 value bytes), the Q tile (TMA), and the tile epilogue:
+//                   O out of TMEM, x out_scale / l, bf16, staged per warp and written with
+//                   TMA tile stores while the softmax warps already work on the next tile;
+//       warp 16     MMA issue (leader CTA; whole warp polls, one elected lane issues);
+//       warps 17-18 relay "K / V landed" from the peer CTA to the leader's barriers;
+//       warp 19     index-validity bits.
+//   * K tiles are five 128-byte-swizzled column chunks per 64 keys (the fifth holds the 64
+//     rope bytes, its other half kept zero), V tiles two MN-major chunks per 128 keys.
+//   * completion is tracked with mbarriers only; every wait is bounded (common.cuh) and
+//     reports through a status word instead of trapping.
 //   * no TMA multicast of any kind; the pair is signalled with two plain commits.
 #include "common.cuh"
 #include "tensor_map.cuh"
@@ -70,7 +78,7 @@ struct Misc {
   // s_free / p_ready (softmax warps of both CTAs)
   uint64_t q_full, k_peer[2], v_peer[2], s_free[2], p_ready[2];
   // in every CTA
-  uint64_t k_land[2], v_land[2], k_copied[2], qk_done[2], pv_done[2], valid_ready[2], valid_free[2];
+  uint64_t k_land[2], v_land[2], qk_done[2], pv_done[2], valid_ready[2], valid_free[2];
   uint64_t m_pub[2];                // running max of block k published by softmax group k%2
   uint64_t q_free;                  // all QK^T of the current tile are complete (Q tile reusable)
   uint64_t o_free;                  // leader CTA: the tile's O has been read out of TMEM
@@ -108,8 +116,8 @@ enum { kSiteQ = 1, kSiteKLand, kSiteKPeer, kSiteVLand, kSiteVPeer, kSiteQkDone, 
 // status[0] first failing wait site, [1] block, [2] iteration, [3] launches completed
 __device__ int g_attn_status[4];
 
-// bring-up aid: cycle stamps of one tile's roles (role 0 softmax thread 0, 1 producer warp 0,
-// 2 MMA thread, 3 copy thread, 4 relay thread), 8 slots per block, written after the S/O dump
+// bring-up aid: time stamps of one tile's roles (role 0 softmax thread 0, 1 gather warp 0,
+// 2 MMA warp, 3 tile hand-over and epilogue rounds), 8 slots per block, written after the S/O dump
 #define LT_TS(role, k, slot)                                                              \
   do {                                                                                    \
     if (kDebug && ts_on && (k) < 64)                                                      \
@@ -119,7 +127,6 @@ __device__ int g_attn_status[4];
 template <bool kDebug>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kAttnThreads, 1)
 masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
-                      const __grid_constant__ CUtensorMap map_kv,
                       const __grid_constant__ CUtensorMap map_out, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -157,7 +164,6 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
       mbar_init(&ms.p_ready[i], 8);
       mbar_init(&ms.k_land[i], kProducerWarps * 32);        // one async arrival per gather thread
       mbar_init(&ms.v_land[i], kProducerWarps * 32);        // one async arrival per gather thread
-      mbar_init(&ms.k_copied[i], 2);
       mbar_init(&ms.qk_done[i], 1);
       mbar_init(&ms.pv_done[i], 1);
       mbar_init(&ms.valid_ready[i], 1);
@@ -166,7 +172,6 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
     }
     fence_mbar_init();
     tma_prefetch_desc(&map_q);
-    tma_prefetch_desc(&map_kv);
     tma_prefetch_desc(&map_out);
   }
   __syncthreads();
@@ -764,16 +769,13 @@ static int launch_fp8(const void* q8, const void* kv8, const int32_t* indices, f
                       void* out, float* max_logits, float* lse, int ng, int s_kv, int topk,
                       long long q_row_stride, long long kv_row_stride, long long idx_row_stride,
                       float* dbg, cudaStream_t stream) {
-  CUtensorMap map_q, map_kv, map_out;
+  CUtensorMap map_q, map_out;
   // out is stored as boxes of 32 rows x 32 dims (64 bytes wide, 64-byte swizzle)
   if (!make_map_2d(&map_out, out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, kDV, (uint64_t)ng * 128,
                    (uint64_t)kDV * 2, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B))
     return LITEDSA_ERR_CUDA;
   if (!make_map_2d(&map_q, q8, CU_TENSOR_MAP_DATA_TYPE_UINT8, kDQK, (uint64_t)ng * 128,
                    (uint64_t)q_row_stride, 128, 64))
-    return LITEDSA_ERR_CUDA;
-  if (!make_map_2d(&map_kv, kv8, CU_TENSOR_MAP_DATA_TYPE_UINT8, kDQK, (uint64_t)s_kv,
-                   (uint64_t)kv_row_stride, 128, 1))
     return LITEDSA_ERR_CUDA;
   AttnParams p;
   p.memb = memb; p.indices = indices; p.counts = counts;
@@ -787,7 +789,7 @@ static int launch_fp8(const void* q8, const void* kv8, const int32_t* indices, f
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem) !=
       cudaSuccess)
     return LITEDSA_ERR_CUDA;
-  kern<<<2 * min(ng, max_clusters()), kAttnThreads, kAttnSmem, stream>>>(map_q, map_kv, map_out, p);
+  kern<<<2 * min(ng, max_clusters()), kAttnThreads, kAttnSmem, stream>>>(map_q, map_out, p);
   return cudaGetLastError() == cudaSuccess ? LITEDSA_OK : LITEDSA_ERR_CUDA;
 }
 
