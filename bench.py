@@ -339,11 +339,9 @@ def main():
     lse_host = torch.empty((w.tokens, w.heads), dtype=torch.float32).pin_memory()
 
     def e2e_step():
-        qd = q_host.to(dev, non_blocking=True)
-        idd = idx_host.to(dev, non_blocking=True)
-        o, l = api.sparse_prefill(qd, kv8, idd, synth.SM_SCALE, kv_scale=ks, q_scale=qs, seq_space=w.s_kv)
-        out_host.copy_(o, non_blocking=True)
-        lse_host.copy_(l, non_blocking=True)
+        # chunks of 512 tokens: upload, kernels and download of neighbouring chunks overlap
+        api.sparse_prefill_host(q_host, kv8, idx_host, synth.SM_SCALE, out_host=out_host,
+                                lse_host=lse_host, kv_scale=ks, q_scale=qs, seq_space=w.s_kv)
 
     for _ in range(min(2, args.e2e_steps)):
         e2e_step()

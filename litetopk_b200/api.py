@@ -232,8 +232,10 @@ def repack_kv656(kv_rows: torch.Tensor, scale: float, out: Optional[torch.Tensor
 def masked_mla_fp8(q: torch.Tensor, kv_cache_fp8: torch.Tensor, union_idx: torch.Tensor,
                    mask: torch.Tensor, sm_scale: float, *, counts: Optional[torch.Tensor] = None,
                    kv_scale: float = 1.0, q_scale: Optional[float] = None,
-                   return_max_logits: bool = False):
-    """Masked FP8 MLA prefill over the per-tile union; returns ``(out [T,h,512] bf16, lse [T,h] f32)``.
+                   return_max_logits: bool = False, out: Optional[torch.Tensor] = None,
+                   lse: Optional[torch.Tensor] = None):
+    """Masked FP8 MLA prefill over the per-tile union; returns ``(out [T,h,512] bf16, lse [T,h] f32)``
+    (written into ``out`` / ``lse`` when given: contiguous, same shapes and dtypes).
 
     q            [T, h, 576]; bf16 (quantised here to e4m3 with the power-of-two ``q_scale``,
                  default: the smallest one that avoids saturation) or e4m3/uint8 codes
@@ -266,8 +268,20 @@ def masked_mla_fp8(q: torch.Tensor, kv_cache_fp8: torch.Tensor, union_idx: torch
         kv = repack_kv656(kv, kv_scale)
     if counts is None:
         counts = (union_idx >= 0).sum(dim=1, dtype=torch.int32)
-    out = torch.empty((ng, 128, 512), dtype=torch.bfloat16, device=q.device)
-    lse = torch.empty((ng, 128), dtype=torch.float32, device=q.device)
+    if out is None:
+        out = torch.empty((ng, 128, 512), dtype=torch.bfloat16, device=q.device)
+    else:
+        _need(out, "out", torch.bfloat16)
+        if out.numel() != T * h * 512 or not out.is_contiguous():
+            raise ValueError("out must be a contiguous [T,h,512] bf16 tensor")
+        out = out.view(ng, 128, 512)
+    if lse is None:
+        lse = torch.empty((ng, 128), dtype=torch.float32, device=q.device)
+    else:
+        _need(lse, "lse", torch.float32)
+        if lse.numel() != T * h or not lse.is_contiguous():
+            raise ValueError("lse must be a contiguous [T,h] f32 tensor")
+        lse = lse.view(ng, 128)
     ml = torch.empty((ng, 128), dtype=torch.float32, device=q.device) if return_max_logits else None
     masked_mla_fp8_out(q8.view(ng, 128, 576), kv, union_idx, float(sm_scale) * q_scale * kv_scale,
                        kv_scale, counts, mask, h, out, ml, lse)
@@ -277,18 +291,116 @@ def masked_mla_fp8(q: torch.Tensor, kv_cache_fp8: torch.Tensor, union_idx: torch
 
 def sparse_prefill(q: torch.Tensor, kv_cache_fp8: torch.Tensor, topk_idx: torch.Tensor,
                    sm_scale: float, *, kv_scale: float = 1.0, q_scale: Optional[float] = None,
-                   seq_space: Optional[int] = None):
+                   seq_space: Optional[int] = None, out: Optional[torch.Tensor] = None,
+                   lse: Optional[torch.Tensor] = None):
     """The whole hot path for one chunk of query tokens: union_qm + masked_mla_fp8.
 
     q [T,h,576], topk_idx [T,k] int32, kv_cache_fp8 as in :func:`masked_mla_fp8` (already
-    resident on the device).  Returns ``(out [T,h,512] bf16, lse [T,h] f32)``.
+    resident on the device).  Returns ``(out [T,h,512] bf16, lse [T,h] f32)``, written into
+    ``out`` / ``lse`` when given.
     """
     h = q.shape[1]
     u, m, c = union_qm(topk_idx, 128 // h,
                        seq_space=seq_space if seq_space is not None else kv_cache_fp8.shape[0],
                        return_counts=True)
     return masked_mla_fp8(q, kv_cache_fp8, u, m, sm_scale, counts=c, kv_scale=kv_scale,
-                          q_scale=q_scale)
+                          q_scale=q_scale, out=out, lse=lse)
+
+
+_SIDE_STREAMS = {}
+_HOST_WORKSPACE = {}
+
+
+def _side_streams(device: torch.device):
+    """One (upload, download) stream pair per device, created on first use."""
+    key = torch.device(device).index if torch.device(device).index is not None \
+        else torch.cuda.current_device()
+    if key not in _SIDE_STREAMS:
+        _SIDE_STREAMS[key] = (torch.cuda.Stream(device=key), torch.cuda.Stream(device=key))
+    return _SIDE_STREAMS[key]
+
+
+def _host_workspace(device, T: int, h: int, k: int, q_dtype, idx_dtype):
+    """Device staging buffers of :func:`sparse_prefill_host`, kept per (device, shape) so that
+    steady-state calls allocate nothing (one q + top-k + out + lse image of the step)."""
+    key = (str(device), T, h, k, q_dtype, idx_dtype)
+    ws = _HOST_WORKSPACE.get(key)
+    if ws is None:
+        _HOST_WORKSPACE.clear()            # one live shape per process is enough
+        ws = (torch.empty((T, h, 576), dtype=q_dtype, device=device),
+              torch.empty((T, k), dtype=idx_dtype, device=device),
+              torch.empty((T, h, 512), dtype=torch.bfloat16, device=device),
+              torch.empty((T, h), dtype=torch.float32, device=device))
+        _HOST_WORKSPACE[key] = ws
+    return ws
+
+
+def sparse_prefill_host(q_host: torch.Tensor, kv_cache_fp8: torch.Tensor, topk_host: torch.Tensor,
+                        sm_scale: float, *, out_host: Optional[torch.Tensor] = None,
+                        lse_host: Optional[torch.Tensor] = None, kv_scale: float = 1.0,
+                        q_scale: Optional[float] = None, seq_space: Optional[int] = None,
+                        chunk_tokens: int = 512):
+    """:func:`sparse_prefill` for callers whose queries and results live in host memory.
+
+    ``q_host`` [T,h,576] and ``topk_host`` [T,k] are host tensors (pinned for full speed),
+    ``kv_cache_fp8`` is resident on the device.  The tokens are cut into tile-aligned chunks
+    and pipelined over three streams: the upload of chunk i+1, the kernels of chunk i (on
+    the caller's current stream) and the download of chunk i-1 run concurrently, so a step
+    costs about max(upload, download) instead of their sum plus the kernels.  Results are
+    written to ``out_host`` [T,h,512] bf16 and ``lse_host`` [T,h] f32 (allocated pinned when
+    not given); they are complete once the caller's current stream has been synchronised.
+    The device staging buffers are cached per shape (see :func:`_host_workspace`); calls on
+    one device must not overlap each other.
+    """
+    if q_host.is_cuda or topk_host.is_cuda:
+        raise ValueError("q_host and topk_host must be host tensors (use sparse_prefill)")
+    if not kv_cache_fp8.is_cuda:
+        raise ValueError("kv_cache_fp8 must be resident on a CUDA device (there is no CPU path)")
+    if q_host.dim() != 3 or q_host.shape[2] != 576 or topk_host.dim() != 2 \
+            or topk_host.shape[0] != q_host.shape[0]:
+        raise ValueError("q_host must be [T,h,576] and topk_host [T,k]")
+    T, h, _ = q_host.shape
+    if 128 % h or 128 // h > 16 or T % (128 // h):
+        raise ValueError("heads must divide 128 (128/h <= 16) and T be a multiple of 128 // heads")
+    G = 128 // h
+    dev = kv_cache_fp8.device
+    chunk = max(G, int(chunk_tokens) // G * G)
+    if out_host is None:
+        out_host = torch.empty((T, h, 512), dtype=torch.bfloat16).pin_memory()
+    if lse_host is None:
+        lse_host = torch.empty((T, h), dtype=torch.float32).pin_memory()
+    if tuple(out_host.shape) != (T, h, 512) or out_host.dtype != torch.bfloat16 or \
+            tuple(lse_host.shape) != (T, h) or lse_host.dtype != torch.float32:
+        raise ValueError("out_host must be [T,h,512] bf16 and lse_host [T,h] f32")
+    space = seq_space if seq_space is not None else kv_cache_fp8.shape[0]
+    with torch.cuda.device(dev):
+        kv = kv_cache_fp8
+        if kv.dim() == 2 and kv.shape[1] == 656:
+            kv = repack_kv656(kv, kv_scale)
+        qd, idd, od, ld = _host_workspace(dev, T, h, topk_host.shape[1], q_host.dtype,
+                                          topk_host.dtype)
+        cur = torch.cuda.current_stream(dev)
+        s_in, s_out = _side_streams(dev)
+        s_in.wait_stream(cur)      # earlier kernels may still read the staging buffers
+        s_out.wait_stream(cur)
+        for t0 in range(0, T, chunk):
+            t1 = min(T, t0 + chunk)
+            with torch.cuda.stream(s_in):
+                qd[t0:t1].copy_(q_host[t0:t1], non_blocking=True)
+                idd[t0:t1].copy_(topk_host[t0:t1], non_blocking=True)
+                ev_in = torch.cuda.Event()
+                ev_in.record(s_in)
+            cur.wait_event(ev_in)
+            sparse_prefill(qd[t0:t1], kv, idd[t0:t1], sm_scale, kv_scale=kv_scale, q_scale=q_scale,
+                           seq_space=space, out=od[t0:t1], lse=ld[t0:t1])
+            ev_c = torch.cuda.Event()
+            ev_c.record(cur)
+            s_out.wait_event(ev_c)
+            with torch.cuda.stream(s_out):
+                out_host[t0:t1].copy_(od[t0:t1], non_blocking=True)
+                lse_host[t0:t1].copy_(ld[t0:t1], non_blocking=True)
+        cur.wait_stream(s_out)
+    return out_host, lse_host
 
 
 # --------------------------------------------------------------------------- DSv4 BF16 two-range attention

@@ -338,8 +338,12 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
       float m = ms.fin[2][last_g * 128 + tl];       // running max after the last block
       float lsum = 0.f;
       real_m = -INFINITY;
+      // fixed summation order (even local blocks first, whichever group served them), so a
+      // tile's result does not depend on the blocks its cluster processed before
+      const int g_even = kb0 & 1;
 #pragma unroll
-      for (int gg = 0; gg < 2; ++gg) {
+      for (int gi = 0; gi < 2; ++gi) {
+        const int gg = gi ^ g_even;
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
           const int o = gg * 128 + hh * 64 + r;

@@ -92,6 +92,25 @@ def test_end_to_end_api_from_bf16_q_and_packed_cache():
     assert cos >= 0.9995 and float((lse.cpu() - lse_e.float()).abs().max()) <= TOL_LSE
 
 
+def test_host_buffer_pipeline_matches_device_call():
+    # chunked upload / kernels / download over three streams == one device-resident call
+    w, idx, kv, q = _case(256, 64, 512, 4096, (0.8, 0.8), seed=6)
+    _, _, (q8, kv8, qs, ks) = _oracle(w, idx, kv, q)
+    want_o, want_l = api.sparse_prefill(q.to(DEV), kv.to(DEV), idx.to(DEV), synth.SM_SCALE,
+                                        kv_scale=ks, q_scale=qs)
+    qh, ih = q.pin_memory(), idx.pin_memory()
+    for chunk in (64, 100, 4096):        # several chunks, a ragged last chunk, one chunk
+        out_h, lse_h = api.sparse_prefill_host(qh, kv.to(DEV), ih, synth.SM_SCALE, kv_scale=ks,
+                                               q_scale=qs, chunk_tokens=chunk)
+        torch.cuda.synchronize()
+        assert torch.equal(out_h, want_o.cpu()) and torch.equal(lse_h, want_l.cpu()), chunk
+    assert api.attn_status()[0] == 0
+    with pytest.raises(ValueError):
+        api.sparse_prefill_host(qh.to(DEV), kv.to(DEV), ih, synth.SM_SCALE)
+    with pytest.raises(ValueError):
+        api.sparse_prefill_host(qh, kv, ih, synth.SM_SCALE)          # cache not on the device
+
+
 def test_padding_empty_tokens_stale_tails_and_bad_indices():
     def mutate(idx):
         idx = idx.clone()
