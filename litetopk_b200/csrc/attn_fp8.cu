@@ -423,6 +423,8 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
     const uint32_t e_ocol = tmem + ((uint32_t)((warp & 3) * 32) << 16) + kTmemO + e_g * 128;
     const uint32_t a_o_free = mapa(smem_u32(&ms.o_free), 0);
     int e_round = 0;
+    // the KV cache is re-read by every tile (keep it in L2); q and out stream through once
+    const uint64_t pol_keep = l2_policy_evict_last(), pol_stream = l2_policy_evict_first();
     // lane l < 16 holds the index of own key 8pw + l%8 (K tile rows), lane l >= 16 of key
     // 16pw + l - 16 of the block's 128 keys (V tile rows)
     const int my_key = lane < 16 ? 64 * (int)cta + 8 * pw + (lane & 7) : 16 * pw + (lane - 16);
@@ -483,8 +485,8 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(&map_out, sbase + e_stage, 256 * e_h + 128 * e_g + 32 * e_round,
-                         ce.tile * 128 + (int)cta * 64 + 32 * (warp & 1));
+            tma_store_2d_hint(&map_out, sbase + e_stage, 256 * e_h + 128 * e_g + 32 * e_round,
+                              ce.tile * 128 + (int)cta * 64 + 32 * (warp & 1), pol_stream);
             bulk_commit_group();
           }
           if (pw == 0) LT_TS(3, 1 + e_round, 1);
@@ -503,8 +505,8 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
           if (lane == 0) {
             if (cta == 0) mbar_arrive_expect_tx(&ms.q_full, 2 * kQBytes);
             for (int j = 0; j < kChunks; ++j)
-              tma_load_2d_pair(sbase + kOffQ + j * kChunkBytes, &map_q, 128 * j,
-                               q_tile * 128 + (int)cta * 64, a_q_full);
+              tma_load_2d_pair_hint(sbase + kOffQ + j * kChunkBytes, &map_q, 128 * j,
+                                    q_tile * 128 + (int)cta * 64, a_q_full, pol_stream);
           }
           __syncwarp();
           q_tile += ncl;
@@ -526,14 +528,14 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
           for (int i = 0; i < 8; ++i) {
             const int ri = __shfl_sync(0xffffffffu, kidx, i);
             const int row = 8 * pw + i;
-            cp_async16(kst + cj * kChunkBytes + row * 128 + ((cc ^ (row & 7)) << 4),
-                       kvb + (size_t)ri * pitch + 16 * lane);
+            cp_async16_hint(kst + cj * kChunkBytes + row * 128 + ((cc ^ (row & 7)) << 4),
+                       kvb + (size_t)ri * pitch + 16 * lane, pol_keep);
           }
           {
             const int ri = __shfl_sync(0xffffffffu, kidx, lane >> 2);
             const int row = 8 * pw + (lane >> 2);
-            cp_async16(kst + 4 * kChunkBytes + row * 128 + (((lane & 3) ^ (row & 7)) << 4),
-                       kvb + (size_t)ri * pitch + 512 + 16 * (lane & 3));
+            cp_async16_hint(kst + 4 * kChunkBytes + row * 128 + (((lane & 3) ^ (row & 7)) << 4),
+                       kvb + (size_t)ri * pitch + 512 + 16 * (lane & 3), pol_keep);
           }
           cp_async_mbar_arrive_noinc(&ms.k_land[s]);
           if (pw == 0) LT_TS(1, ck.k, 2);
@@ -558,8 +560,8 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
             const int rloc = 2 * i + (lane >> 4);
             const int ri = __shfl_sync(0xffffffffu, vidx, 16 + rloc);
             const int row = 16 * pw + rloc;
-            cp_async16(vst + nbk * kVChunk + row * 128 + ((c8 ^ (row & 7)) << 4),
-                       kvb + (size_t)ri * pitch + 256 * cta + 16 * pc);
+            cp_async16_hint(vst + nbk * kVChunk + row * 128 + ((c8 ^ (row & 7)) << 4),
+                       kvb + (size_t)ri * pitch + 256 * cta + 16 * pc, pol_keep);
           }
           cp_async_mbar_arrive_noinc(&ms.v_land[s]);
           cur_next(cv);

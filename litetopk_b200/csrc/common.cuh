@@ -238,6 +238,36 @@ __device__ __forceinline__ void bulk_wait_all() {
   asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
 
+// L2 eviction-priority policies for streaming (read or written once) and resident data
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ void cp_async16_hint(uint32_t dst_smem, const void* src, uint64_t pol) {
+  asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;"
+               ::"r"(dst_smem), "l"(src), "l"(pol) : "memory");
+}
+__device__ __forceinline__ void tma_store_2d_hint(const void* map, uint32_t src_smem, int x, int y,
+                                                  uint64_t pol) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint"
+               " [%0, {%2, %3}], [%1], %4;"
+               :: "l"(map), "r"(src_smem), "r"(x), "r"(y), "l"(pol) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair_hint(uint32_t dst_smem, const CUtensorMap* map,
+                                                      int x, int y, uint32_t mbar_cluster_addr,
+                                                      uint64_t pol) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes.cta_group::2"
+      ".L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
+      ::"r"(dst_smem), "l"(map), "r"(x), "r"(y), "r"(mbar_cluster_addr), "l"(pol)
+      : "memory");
+}
 __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
 }
