@@ -159,7 +159,7 @@ def config_dict(w, args):
             "tokens_per_gpu": w.tokens, "tokens_per_tile": w.group, "seed": 1,
             "l2_policy": "inputs+outputs per step (~0.9 GB) exceed the 126 MB L2; the 19 MB KV cache stays "
                          "resident by design",
-            "parallelism": f"dp{args.gpus} (query-token blocks; KV replicated; NCCL all-gather of out)"}
+            "parallelism": f"dp{args.gpus} (query-token blocks; KV replicated; all-gather of out)"}
 
 
 def run_dsv4(args, w):
@@ -216,6 +216,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-tiles", type=int, default=32)
     ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--gather", choices=("fused", "nccl"), default="fused",
+                    help="N > 1: how the ranks' outputs are gathered")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tokens", type=int, default=0,
                     help="shrink the workload to this many query tokens per GPU (profiling aid; "
@@ -261,19 +263,37 @@ def main():
     sm = synth.SM_SCALE * qs * ks
     n_chunks = 4 if world > 1 else 1
     gatherer = None
+    peer_out = None
+    gather_kind = "none"
     if world > 1:
         from litetopk_b200 import dist as ldist
-        gatherer = ldist.ChunkedAllGather(ng, (128, 512), torch.bfloat16, dev, n_chunks=n_chunks)
+        if args.gather == "fused":
+            try:   # the kernel's epilogue writes every rank's copy through peer-mapped memory
+                peer_out = ldist.PeerGatheredOutput(ng, (128, 512), torch.bfloat16, dev)
+                gather_kind = "fused: TMA tile stores of the attention epilogue into every rank's buffer (symmetric memory) + barrier"
+            except Exception as e:     # symmetric memory not available on this box
+                gather_kind = f"nccl (symmetric memory unavailable: {type(e).__name__})"
+        flags = torch.tensor([1 if peer_out is not None else 0], dtype=torch.int32, device=dev)
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+        if int(flags.item()) == 0:
+            peer_out = None
+            if gather_kind.startswith("fused"):
+                gather_kind = "nccl (symmetric memory unavailable on a peer)"
+        if peer_out is None:
+            if args.gather != "fused":
+                gather_kind = "nccl: chunked all_gather_into_tensor on a side stream"
+            gatherer = ldist.ChunkedAllGather(ng, (128, 512), torch.bfloat16, dev, n_chunks=n_chunks)
     launches = [0]
     attn_events = []
     timed_flag = [False]
     gather_on = [True]
 
-    def attn_chunk(a, b, dst):
+    def attn_chunk(a, b, dst, peers=None):
         if timed_flag[0]:
             e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
             e0.record()
-        api.masked_mla_fp8_out(q8[a:b], kv8, u[a:b], sm, ks, cnt[a:b], msk[a:b], w.heads, dst, None, lse[a:b])
+        api.masked_mla_fp8_out(q8[a:b], kv8, u[a:b], sm, ks, cnt[a:b], msk[a:b], w.heads, dst, None,
+                               lse[a:b], peer_outs=peers)
         launches[0] += 1
         if timed_flag[0]:
             e1.record(); attn_events.append((e0, e1, b - a))
@@ -282,7 +302,11 @@ def main():
         timed_flag[0] = timed
         api.union_qm_out(idx, u, cnt, msk, None, None, 1, w.s_kv)
         launches[0] += 1
-        if world > 1 and gather_on[0]:
+        if peer_out is not None and gather_on[0]:
+            ldist.fused_sharded_attention(lambda dst, peers: attn_chunk(0, ng, dst, peers), peer_out)
+        elif peer_out is not None:
+            attn_chunk(0, ng, peer_out.local())
+        elif world > 1 and gather_on[0]:
             ldist.sharded_attention(attn_chunk, gatherer)
         elif world > 1:
             for i in range(gatherer.n_chunks):
@@ -376,14 +400,15 @@ def main():
         "effective_tflops": world * flop / (ms * 1e-3) / 1e12,
         "compute_only": None if ms_compute_only is None else {
             "ms_per_step": ms_compute_only, "value": world * w.tokens / (ms_compute_only * 1e-3),
-            "note": "same steps with the NCCL all-gather of the outputs switched off"},
+            "note": "same steps with the all-gather of the outputs switched off"},
+        "gather": gather_kind,
         "all_gather_bytes_per_rank_per_step": (world - 1) * ng * 128 * 512 * 2,
         "roofline": {"kernel": "masked_mla_fp8_kernel", "bound": "tensor", "achieved": achieved,
                      "peak": fp8_peak, "unit": "TFLOP/s", "frac": achieved / fp8_peak,
                      "traffic": ATTN_DRAM_TRAFFIC_BYTES if (w.name == "c1" and not args.tokens) else None,
                      "peak_source": f"2 x bf16 dense {peaks['bf16_tflops']} TFLOP/s of {peaks['source']} "
                                     "(FP8 dense is not in MEASURED_PEAKS.json); nominal FP8 dense 4500",
-                     "kernel_ms_per_launch": attn_ms / n_chunks,
+                     "kernel_ms_per_launch": attn_ms / (1 if peer_out is not None else n_chunks),
                      "algorithmic_flop_per_step": flop,
                      "executed_flop_per_step": union_rows * 128 * synth.FLOP_PER_PAIR,
                      "gather_bytes_per_step": union_rows * 576,

@@ -88,6 +88,23 @@ int litedsa_masked_mla_fp8(const void* q8, const void* kv8, const int32_t* indic
                            float* debug_dump, void* stream);
 
 /*
+ * litedsa_masked_mla_fp8 with the all-gather of a query-sharded multi-GPU run folded into
+ * the kernel's epilogue.  Every output box is written to n_outs (1..8) destinations with
+ * TMA tile stores: outs[0] is this GPU's [ng, 128, 512] bf16 buffer, outs[1..] are
+ * peer-mapped device addresses of the slot this rank owns in each peer's gathered buffer
+ * (same shape).  The writes to a peer are complete when this kernel has completed; the
+ * caller orders the peers' reads after it (a barrier among the ranks).  No counterpart
+ * in the reference, which has no multi-GPU code (its tiles are independent units,
+ * kernels/b200/dsa/litedsa_attention_sm100.cuh:1839-1840).
+ */
+int litedsa_masked_mla_fp8_multi(const void* q8, const void* kv8, const int32_t* indices,
+                                 float sm_scale, float out_scale, const int32_t* topk_length,
+                                 const uint32_t* memb_qm, int h_per_q, void* const* outs,
+                                 int n_outs, float* max_logits, float* lse, int ng, int s_kv,
+                                 int topk, int64_t q_row_stride, int64_t kv_row_stride,
+                                 int64_t indices_row_stride, void* stream);
+
+/*
  * Synchronous read (and optional reset) of the attention kernels' device status word on
  * the current device.  out4_host[0] = first bounded wait that expired (0 = none),
  * [1] = block, [2] = loop iteration, [3] = launches completed since the last reset.

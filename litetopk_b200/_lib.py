@@ -25,6 +25,10 @@ SIGNATURES = {
                                        c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                        c_int, c_int, c_int64, c_int64, c_int64, c_void_p,
                                        c_void_p]),
+    "litedsa_masked_mla_fp8_multi": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_float,
+                                             c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
+                                             c_void_p, c_int, c_int, c_int, c_int64, c_int64,
+                                             c_int64, c_void_p]),
     "litedsa_attn_status": (c_int, [c_void_p, c_int]),
     "litedsa_quantize_e4m3": (c_int, [c_void_p, c_void_p, c_int64, c_float, c_void_p]),
     "litedsa_repack_kv656": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_float, c_void_p,

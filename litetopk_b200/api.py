@@ -121,8 +121,12 @@ def masked_mla_fp8_out(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor,
                        out_scale: float, topk_length: Optional[torch.Tensor],
                        memb_qm: torch.Tensor, h_per_q: int, out: torch.Tensor,
                        max_logits: Optional[torch.Tensor], lse: torch.Tensor,
-                       *, _debug_dump: Optional[torch.Tensor] = None) -> None:
+                       *, peer_outs=None, _debug_dump: Optional[torch.Tensor] = None) -> None:
     """Reference argument order (kernels/b200/dsa/litedsa.cu:77-80).
+
+    ``peer_outs`` (sharded multi-GPU runs): up to seven peer-mapped device addresses (ints)
+    of [ng,128,512] bf16 buffers on other GPUs that receive a copy of every output box from
+    the kernel's epilogue (see :mod:`litetopk_b200.dist`).
 
     q [ng,128,576] e4m3 (uint8 storage accepted); kv [s_kv,1,576] or [s_kv,576] e4m3, row
     pitch = kv.stride(0); indices [ng,1,topk] or [ng,topk] i32 physical slots; topk_length
@@ -169,11 +173,23 @@ def masked_mla_fp8_out(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor,
         if max_logits.numel() != ng * 128 or not max_logits.is_contiguous():
             raise ValueError("max_logits must be a contiguous [ng,128]")
     with torch.cuda.device(q.device):
-        rc = _lib.lib().litedsa_masked_mla_fp8(
-            _ptr(q), _ptr(kv), _ptr(indices), float(sm_scale), float(out_scale),
-            _ptr(topk_length), _ptr(memb_qm), int(h_per_q), _ptr(out), _ptr(max_logits),
-            _ptr(lse), ng, kv.shape[0], topk, q.stride(1), kv.stride(0), indices.stride(0),
-            _ptr(_debug_dump), _stream(q))
+        if peer_outs:
+            import ctypes
+            ptrs = [_ptr(out)] + [int(a) for a in peer_outs]
+            if len(ptrs) > 8:
+                raise ValueError("at most 7 peer destinations")
+            arr = (ctypes.c_void_p * len(ptrs))(*ptrs)
+            rc = _lib.lib().litedsa_masked_mla_fp8_multi(
+                _ptr(q), _ptr(kv), _ptr(indices), float(sm_scale), float(out_scale),
+                _ptr(topk_length), _ptr(memb_qm), int(h_per_q), arr, len(ptrs), _ptr(max_logits),
+                _ptr(lse), ng, kv.shape[0], topk, q.stride(1), kv.stride(0), indices.stride(0),
+                _stream(q))
+        else:
+            rc = _lib.lib().litedsa_masked_mla_fp8(
+                _ptr(q), _ptr(kv), _ptr(indices), float(sm_scale), float(out_scale),
+                _ptr(topk_length), _ptr(memb_qm), int(h_per_q), _ptr(out), _ptr(max_logits),
+                _ptr(lse), ng, kv.shape[0], topk, q.stride(1), kv.stride(0), indices.stride(0),
+                _ptr(_debug_dump), _stream(q))
     check(rc, "masked_mla_fp8")
 
 

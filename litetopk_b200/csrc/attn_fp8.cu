@@ -93,6 +93,11 @@ struct Misc {
 };
 static_assert(sizeof(Misc) <= kMiscBytes, "Misc too large");
 
+constexpr int kMaxOutputs = 8;
+// tensor maps of the output destinations: this GPU's buffer and, in a sharded run, the
+// peers' gathered buffers (peer-mapped addresses written with plain TMA tile stores)
+struct OutMaps { CUtensorMap m[kMaxOutputs]; };
+
 struct AttnParams {
   const uint32_t* memb;      // [ng, G, cap/32]
   const uint8_t* kv;         // [s_kv, kv_pitch] e4m3 rows (576 bytes used)
@@ -104,6 +109,7 @@ struct AttnParams {
   float* max_logits;         // [ng, 128] or null
   float* dbg;                // debug dump or null
   int ng, s_kv, cap, h_per_q, G;
+  int n_out;                 // destinations of every output box (1 + peers that hold a copy)
   long long idx_stride;
   float scale_log2, out_scale;
 };
@@ -127,7 +133,7 @@ __device__ int g_attn_status[4];
 template <bool kDebug>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kAttnThreads, 1)
 masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
-                      const __grid_constant__ CUtensorMap map_out, const AttnParams p) {
+                      const __grid_constant__ OutMaps omaps, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t sbase = (raw + 1023u) & ~1023u;       // 128B-swizzle tiles need 1024-byte alignment
@@ -172,7 +178,7 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
     }
     fence_mbar_init();
     tma_prefetch_desc(&map_q);
-    tma_prefetch_desc(&map_out);
+    for (int d = 0; d < p.n_out; ++d) tma_prefetch_desc(&omaps.m[d]);
   }
   __syncthreads();
   cluster_sync_all();
@@ -485,8 +491,9 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d_hint(&map_out, sbase + e_stage, 256 * e_h + 128 * e_g + 32 * e_round,
-                              ce.tile * 128 + (int)cta * 64 + 32 * (warp & 1), pol_stream);
+            for (int d = 0; d < p.n_out; ++d)
+              tma_store_2d_hint(&omaps.m[d], sbase + e_stage, 256 * e_h + 128 * e_g + 32 * e_round,
+                                ce.tile * 128 + (int)cta * 64 + 32 * (warp & 1), pol_stream);
             bulk_commit_group();
           }
           if (pw == 0) LT_TS(3, 1 + e_round, 1);
@@ -772,21 +779,23 @@ static int max_clusters() {
 
 static int launch_fp8(const void* q8, const void* kv8, const int32_t* indices, float sm_scale,
                       float out_scale, const int32_t* counts, const uint32_t* memb, int h_per_q,
-                      void* out, float* max_logits, float* lse, int ng, int s_kv, int topk,
+                      void* const* outs, int n_out, float* max_logits, float* lse, int ng, int s_kv, int topk,
                       long long q_row_stride, long long kv_row_stride, long long idx_row_stride,
                       float* dbg, cudaStream_t stream) {
-  CUtensorMap map_q, map_out;
+  CUtensorMap map_q;
+  OutMaps omaps;
   // out is stored as boxes of 32 rows x 32 dims (64 bytes wide, 64-byte swizzle)
-  if (!make_map_2d(&map_out, out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, kDV, (uint64_t)ng * 128,
-                   (uint64_t)kDV * 2, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B))
-    return LITEDSA_ERR_CUDA;
+  for (int d = 0; d < kMaxOutputs; ++d)
+    if (!make_map_2d(&omaps.m[d], outs[d < n_out ? d : 0], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, kDV,
+                     (uint64_t)ng * 128, (uint64_t)kDV * 2, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B))
+      return LITEDSA_ERR_CUDA;
   if (!make_map_2d(&map_q, q8, CU_TENSOR_MAP_DATA_TYPE_UINT8, kDQK, (uint64_t)ng * 128,
                    (uint64_t)q_row_stride, 128, 64))
     return LITEDSA_ERR_CUDA;
   AttnParams p;
   p.memb = memb; p.indices = indices; p.counts = counts;
   p.kv = reinterpret_cast<const uint8_t*>(kv8); p.kv_pitch = kv_row_stride;
-  p.out = reinterpret_cast<__nv_bfloat16*>(out); p.lse = lse; p.max_logits = max_logits;
+  p.out = reinterpret_cast<__nv_bfloat16*>(outs[0]); p.n_out = n_out; p.lse = lse; p.max_logits = max_logits;
   p.dbg = dbg;
   p.ng = ng; p.s_kv = s_kv; p.cap = topk; p.h_per_q = h_per_q; p.G = 128 / h_per_q;
   p.idx_stride = idx_row_stride;
@@ -795,7 +804,7 @@ static int launch_fp8(const void* q8, const void* kv8, const int32_t* indices, f
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem) !=
       cudaSuccess)
     return LITEDSA_ERR_CUDA;
-  kern<<<2 * min(ng, max_clusters()), kAttnThreads, kAttnSmem, stream>>>(map_q, map_out, p);
+  kern<<<2 * min(ng, max_clusters()), kAttnThreads, kAttnSmem, stream>>>(map_q, omaps, p);
   return cudaGetLastError() == cudaSuccess ? LITEDSA_OK : LITEDSA_ERR_CUDA;
 }
 
@@ -823,9 +832,40 @@ extern "C" int litedsa_masked_mla_fp8(const void* q8, const void* kv8, const int
   if (((uintptr_t)q8 | (uintptr_t)kv8 | (uintptr_t)indices | (uintptr_t)out) & 15)
     return LITEDSA_ERR_UNSUPPORTED;
   if (indices_row_stride < topk || indices_row_stride % 4) return LITEDSA_ERR_UNSUPPORTED;
-  return launch_fp8(q8, kv8, indices, sm_scale, out_scale, topk_length, memb_qm, h_per_q, out,
+  void* outs[1] = {out};
+  return launch_fp8(q8, kv8, indices, sm_scale, out_scale, topk_length, memb_qm, h_per_q, outs, 1,
                     max_logits, lse, ng, s_kv, topk, q_row_stride, kv_row_stride,
                     indices_row_stride, debug_dump, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// The same operator with the all-gather of a sharded run folded into its epilogue: every
+// output box is written to n_outs destinations with plain TMA tile stores -- outs[0] is
+// this GPU's buffer, outs[1..] are the peers' copies (peer-mapped device addresses of the
+// slot this rank owns in each peer's gathered buffer).  The reference has no multi-GPU path.
+extern "C" int litedsa_masked_mla_fp8_multi(const void* q8, const void* kv8, const int32_t* indices,
+                                            float sm_scale, float out_scale,
+                                            const int32_t* topk_length, const uint32_t* memb_qm,
+                                            int h_per_q, void* const* outs, int n_outs,
+                                            float* max_logits, float* lse, int ng, int s_kv,
+                                            int topk, int64_t q_row_stride, int64_t kv_row_stride,
+                                            int64_t indices_row_stride, void* stream) {
+  using namespace lt;
+  if (!q8 || !kv8 || !indices || !memb_qm || !outs || !lse) return LITEDSA_ERR_ARG;
+  if (n_outs < 1 || n_outs > kMaxOutputs) return LITEDSA_ERR_SHAPE;
+  if (ng <= 0 || s_kv <= 0 || topk <= 0 || topk % 128 != 0) return LITEDSA_ERR_SHAPE;
+  if (h_per_q <= 0 || 128 % h_per_q != 0 || 128 / h_per_q > 16) return LITEDSA_ERR_SHAPE;
+  if (q_row_stride < kDQK || kv_row_stride < kDQK || q_row_stride % 16 || kv_row_stride % 16)
+    return LITEDSA_ERR_UNSUPPORTED;
+  uintptr_t bits = (uintptr_t)q8 | (uintptr_t)kv8 | (uintptr_t)indices;
+  for (int d = 0; d < n_outs; ++d) {
+    if (!outs[d]) return LITEDSA_ERR_ARG;
+    bits |= (uintptr_t)outs[d];
+  }
+  if (bits & 15) return LITEDSA_ERR_UNSUPPORTED;
+  if (indices_row_stride < topk || indices_row_stride % 4) return LITEDSA_ERR_UNSUPPORTED;
+  return launch_fp8(q8, kv8, indices, sm_scale, out_scale, topk_length, memb_qm, h_per_q, outs,
+                    n_outs, max_logits, lse, ng, s_kv, topk, q_row_stride, kv_row_stride,
+                    indices_row_stride, nullptr, reinterpret_cast<cudaStream_t>(stream));
 }
 
 // Synchronous read (and optional reset) of the device status word of the attention

@@ -1,5 +1,8 @@
 """Multi-GPU prefill: tile-aligned query blocks per rank, KV cache replicated, one
-collective -- the all-gather of the bf16 outputs (NCCL over NVLink on GPUs).
+collective -- the all-gather of the bf16 outputs.  Two forms: `ChunkedAllGather` (NCCL
+over NVLink, chunk by chunk on a side stream) and `PeerGatheredOutput` (the attention
+kernel's epilogue writes every output box into all ranks' buffers through peer-mapped
+symmetric memory, so the gather costs no extra pass and no SMs).
 
 Tiles are independent units of the hot path (one CTA pair per tile, no cross-tile state;
 the reference launches them the same way, kernels/b200/dsa/litedsa_attention_sm100.cuh:
@@ -85,3 +88,71 @@ def sharded_attention(compute_chunk: Callable[[int, int, torch.Tensor], None], a
             ag.gather(i)
     ag.finish()
     return ag
+
+
+def peer_slot_addresses(base_ptrs: List[int], rank: int, slot_bytes: int, offset: int = 0) -> List[int]:
+    """Addresses, as mapped on this rank, of slot `rank` in every OTHER rank's gathered buffer.
+
+    ``base_ptrs[r]`` is the base of rank r's buffer in this rank's address space; every buffer
+    is ``[world, slot]`` so slot `rank` starts ``rank * slot_bytes`` bytes in (plus the
+    tensor's offset inside the symmetric allocation)."""
+    if not (0 <= rank < len(base_ptrs)):
+        raise ValueError("rank out of range")
+    return [int(base_ptrs[r]) + offset + rank * slot_bytes for r in range(len(base_ptrs)) if r != rank]
+
+
+class PeerGatheredOutput:
+    """``[world, rows, ...]`` output buffer that exists on every rank; rank r's kernel writes
+    slot r of ALL ranks' buffers (its own through a normal pointer, the others through
+    peer-mapped addresses), so when every rank's kernel has completed every rank holds the
+    gathered result.
+
+    On CUDA the buffers live in symmetric memory (``torch.distributed._symmetric_memory``) and
+    ``finish()`` is a barrier among the ranks on the current stream; a consumer must not
+    start the next step (which overwrites the slots) before it has read the previous result
+    on every rank -- call ``finish()`` again after consuming, or order it by other means.
+    On CPU ranks (gloo; used by the host-logic tests) the buffer is a plain tensor and
+    ``finish()`` falls back to an all-gather, so both forms have the same result.
+    """
+
+    def __init__(self, rows: int, row_shape, dtype, device, group=None):
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.device = torch.device(device)
+        shape = (self.world, rows, *row_shape)
+        self.handle = None
+        if self.device.type == "cuda":
+            import torch.distributed._symmetric_memory as symm_mem
+            self.buf = symm_mem.empty(shape, dtype=dtype, device=self.device)
+            self.handle = symm_mem.rendezvous(self.buf, self.group)
+            slot_bytes = self.buf[0].numel() * self.buf.element_size()
+            ptrs = [int(x) for x in self.handle.buffer_ptrs]
+            offset = self.buf.data_ptr() - ptrs[self.rank]
+            self.peer_ptrs = peer_slot_addresses(ptrs, self.rank, slot_bytes, offset)
+        else:
+            self.buf = torch.empty(shape, dtype=dtype, device=self.device)
+            self.peer_ptrs = []
+
+    def local(self) -> torch.Tensor:
+        return self.buf[self.rank]
+
+    def gathered(self) -> torch.Tensor:
+        return self.buf
+
+    def finish(self) -> None:
+        if self.handle is not None:
+            self.handle.barrier()
+        else:
+            dist.all_gather([self.buf[r] for r in range(self.world)], self.buf[self.rank].clone(),
+                            group=self.group)
+
+
+def fused_sharded_attention(launch: Callable[[torch.Tensor, List[int]], None],
+                            pg: PeerGatheredOutput) -> PeerGatheredOutput:
+    """One launch for this rank's rows: ``launch(out_rows, peer_addresses)`` runs the attention
+    whose epilogue writes ``out_rows`` (slot `rank` of this rank's buffer) and the same slot
+    of every peer; then the ranks meet.  Returns ``pg`` (all ranks' rows)."""
+    launch(pg.local(), pg.peer_ptrs)
+    pg.finish()
+    return pg

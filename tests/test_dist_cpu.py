@@ -58,3 +58,37 @@ def _worker(rank, world, port, rows):
 def test_chunked_all_gather_two_ranks():
     port = _free_port()
     mp.spawn(_worker, args=(2, port, 7), nprocs=2, join=True)
+
+
+def test_peer_slot_addresses():
+    bases = [0x1000, 0x20000, 0x300000]
+    # rank 1 writes slot 1 (bytes [64, 128) of every [3, 64]-byte buffer) of ranks 0 and 2
+    assert ldist.peer_slot_addresses(bases, 1, 64) == [0x1000 + 64, 0x300000 + 64]
+    assert ldist.peer_slot_addresses(bases, 0, 64, offset=16) == [0x20000 + 16, 0x300000 + 16]
+    assert ldist.peer_slot_addresses([0x1000], 0, 64) == []
+    with pytest.raises(ValueError):
+        ldist.peer_slot_addresses(bases, 3, 64)
+
+
+def _peer_worker(rank, world, port, rows):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        pg = ldist.PeerGatheredOutput(rows, (4,), torch.float32, "cpu")
+        assert pg.peer_ptrs == [] and pg.local().shape == (rows, 4)
+
+        def launch(dst, peers):             # stands in for the kernel writing this rank's slot
+            assert peers == []
+            dst.copy_((torch.arange(rows, dtype=torch.float32)[:, None] + 1000.0 * rank).expand(rows, 4))
+
+        got = ldist.fused_sharded_attention(launch, pg).gathered()
+        want = torch.stack([(torch.arange(rows, dtype=torch.float32)[:, None] + 1000.0 * r).expand(rows, 4)
+                            for r in range(world)])
+        assert torch.equal(got, want), (rank, got[:, :3, 0])
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_gathered_output_two_ranks():
+    port = _free_port()
+    mp.spawn(_peer_worker, args=(2, port, 5), nprocs=2, join=True)
