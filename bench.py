@@ -142,7 +142,7 @@ def run_reference(args, w):
     sample = f"{tiles} tiles ({tokens} query tokens) of {w.name} per step, PyTorch eager CPU oracle"
     line = {"impl": "reference", "metric": METRIC, "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "e4m3",
+            "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "e4m3",
             "data": "synthetic", "config": config_dict(w, args),
             "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port",
                              "sample": sample},
@@ -216,8 +216,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-tiles", type=int, default=32)
     ap.add_argument("--e2e-steps", type=int, default=5)
-    ap.add_argument("--gather", choices=("fused", "nccl"), default="fused",
-                    help="N > 1: how the ranks' outputs are gathered")
+    ap.add_argument("--gather", choices=("auto", "fused", "ce", "nccl"), default="auto",
+                    help="N > 1: how the ranks' outputs are gathered (auto: the fastest measured "
+                         "form for this N: copy-engine pushes up to 4 GPUs, NCCL beyond)")
+    ap.add_argument("--scaling", choices=("weak", "strong"), default="weak",
+                    help="N > 1: the configuration per GPU (weak) or split across the GPUs (strong)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tokens", type=int, default=0,
                     help="shrink the workload to this many query tokens per GPU (profiling aid; "
@@ -238,6 +241,12 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    if args.gather == "auto":
+        args.gather = "ce" if world <= 4 else "nccl"
+    if args.scaling == "strong" and world > 1:
+        if w.tokens % (world * w.group):
+            raise SystemExit("strong scaling needs tokens divisible by gpus x tokens-per-tile")
+        w = synth.scaled(w, tokens=w.tokens // world)
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist = None
@@ -267,20 +276,22 @@ def main():
     gather_kind = "none"
     if world > 1:
         from litetopk_b200 import dist as ldist
-        if args.gather == "fused":
+        if args.gather in ("fused", "ce"):
             try:   # the kernel's epilogue writes every rank's copy through peer-mapped memory
                 peer_out = ldist.PeerGatheredOutput(ng, (128, 512), torch.bfloat16, dev)
-                gather_kind = "fused: TMA tile stores of the attention epilogue into every rank's buffer (symmetric memory) + barrier"
+                gather_kind = ("fused: TMA tile stores of the attention epilogue into every rank's buffer (symmetric memory) + barrier"
+                               if args.gather == "fused" else
+                               "ce: chunked copy-engine pushes into every rank's buffer (symmetric memory) on side streams + barrier")
             except Exception as e:     # symmetric memory not available on this box
                 gather_kind = f"nccl (symmetric memory unavailable: {type(e).__name__})"
         flags = torch.tensor([1 if peer_out is not None else 0], dtype=torch.int32, device=dev)
         dist.all_reduce(flags, op=dist.ReduceOp.MIN)
         if int(flags.item()) == 0:
             peer_out = None
-            if gather_kind.startswith("fused"):
+            if gather_kind.startswith(("fused", "ce")):
                 gather_kind = "nccl (symmetric memory unavailable on a peer)"
         if peer_out is None:
-            if args.gather != "fused":
+            if args.gather == "nccl":
                 gather_kind = "nccl: chunked all_gather_into_tensor on a side stream"
             gatherer = ldist.ChunkedAllGather(ng, (128, 512), torch.bfloat16, dev, n_chunks=n_chunks)
     launches = [0]
@@ -302,7 +313,13 @@ def main():
         timed_flag[0] = timed
         api.union_qm_out(idx, u, cnt, msk, None, None, 1, w.s_kv)
         launches[0] += 1
-        if peer_out is not None and gather_on[0]:
+        if peer_out is not None and gather_on[0] and args.gather == "ce":
+            ldist.copy_engine_sharded_attention(attn_chunk, peer_out, n_chunks)
+        elif peer_out is not None and args.gather == "ce":
+            cb = ldist.chunk_bounds(ng, n_chunks)
+            for i in range(n_chunks):
+                attn_chunk(cb[i], cb[i + 1], peer_out.local()[cb[i]:cb[i + 1]])
+        elif peer_out is not None and gather_on[0]:
             ldist.fused_sharded_attention(lambda dst, peers: attn_chunk(0, ng, dst, peers), peer_out)
         elif peer_out is not None:
             attn_chunk(0, ng, peer_out.local())
@@ -395,7 +412,7 @@ def main():
     line = {
         "metric": METRIC, "value": world * w.tokens / (ms * 1e-3), "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "e4m3",
+        "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "e4m3",
         "data": "synthetic", "config": config_dict(w, args),
         "effective_tflops": world * flop / (ms * 1e-3) / 1e12,
         "compute_only": None if ms_compute_only is None else {
@@ -408,7 +425,7 @@ def main():
                      "traffic": ATTN_DRAM_TRAFFIC_BYTES if (w.name == "c1" and not args.tokens) else None,
                      "peak_source": f"2 x bf16 dense {peaks['bf16_tflops']} TFLOP/s of {peaks['source']} "
                                     "(FP8 dense is not in MEASURED_PEAKS.json); nominal FP8 dense 4500",
-                     "kernel_ms_per_launch": attn_ms / (1 if peer_out is not None else n_chunks),
+                     "kernel_ms_per_launch": attn_ms / (1 if (peer_out is not None and args.gather == "fused") else n_chunks),
                      "algorithmic_flop_per_step": flop,
                      "executed_flop_per_step": union_rows * 128 * synth.FLOP_PER_PAIR,
                      "gather_bytes_per_step": union_rows * 576,

@@ -130,9 +130,15 @@ class PeerGatheredOutput:
             ptrs = [int(x) for x in self.handle.buffer_ptrs]
             offset = self.buf.data_ptr() - ptrs[self.rank]
             self.peer_ptrs = peer_slot_addresses(ptrs, self.rank, slot_bytes, offset)
+            # copy-engine form: every peer's buffer as a tensor mapped on this rank, one side
+            # stream per peer (peers in rotated order, so the ranks do not all target one GPU)
+            self.peers = [(self.rank + i) % self.world for i in range(1, self.world)]
+            self.peer_bufs = {p: self.handle.get_buffer(p, shape, dtype) for p in self.peers}
+            self.streams = [torch.cuda.Stream(device=self.device) for _ in self.peers]
         else:
             self.buf = torch.empty(shape, dtype=dtype, device=self.device)
             self.peer_ptrs = []
+            self.peers, self.peer_bufs, self.streams = [], {}, []
 
     def local(self) -> torch.Tensor:
         return self.buf[self.rank]
@@ -140,8 +146,26 @@ class PeerGatheredOutput:
     def gathered(self) -> torch.Tensor:
         return self.buf
 
+    def push_rows(self, lo: int, hi: int) -> None:
+        """Copy rows [lo, hi) of this rank's slot into the same slot of every peer with the
+        copy engines (one device-to-device copy per peer on its own side stream): no SM is
+        taken from the attention kernel that computes the next rows meanwhile."""
+        if not self.peers or hi <= lo:
+            return
+        cur = torch.cuda.current_stream(self.device)
+        ev = torch.cuda.Event()
+        ev.record(cur)
+        src = self.buf[self.rank, lo:hi]
+        for p, st in zip(self.peers, self.streams):
+            st.wait_event(ev)
+            with torch.cuda.stream(st):
+                self.peer_bufs[p][self.rank, lo:hi].copy_(src, non_blocking=True)
+
     def finish(self) -> None:
         if self.handle is not None:
+            cur = torch.cuda.current_stream(self.device)
+            for st in self.streams:
+                cur.wait_stream(st)
             self.handle.barrier()
         else:
             dist.all_gather([self.buf[r] for r in range(self.world)], self.buf[self.rank].clone(),
@@ -154,5 +178,20 @@ def fused_sharded_attention(launch: Callable[[torch.Tensor, List[int]], None],
     whose epilogue writes ``out_rows`` (slot `rank` of this rank's buffer) and the same slot
     of every peer; then the ranks meet.  Returns ``pg`` (all ranks' rows)."""
     launch(pg.local(), pg.peer_ptrs)
+    pg.finish()
+    return pg
+
+
+def copy_engine_sharded_attention(compute_chunk: Callable[[int, int, torch.Tensor], None],
+                                  pg: PeerGatheredOutput, n_chunks: int = 4) -> PeerGatheredOutput:
+    """Run ``compute_chunk(lo, hi, out_rows)`` over this rank's rows chunk by chunk and push
+    each chunk to the peers with copy-engine copies while the next chunk is computed; then
+    the ranks meet.  Returns ``pg`` (all ranks' rows)."""
+    bounds = chunk_bounds(pg.buf.shape[1], n_chunks)
+    for i in range(len(bounds) - 1):
+        lo, hi = bounds[i], bounds[i + 1]
+        if hi > lo:
+            compute_chunk(lo, hi, pg.local()[lo:hi])
+            pg.push_rows(lo, hi)
     pg.finish()
     return pg
