@@ -133,7 +133,6 @@ __device__ int g_attn_status[4];
 template <bool kDebug>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kAttnThreads, 1)
 masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
-                      const __grid_constant__ CUtensorMap map_kv,
                       const __grid_constant__ OutMaps omaps, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -170,7 +169,7 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
       mbar_init(&ms.s_free[i], 8);        // 4 warps of one softmax group x 2 CTAs
       mbar_init(&ms.p_ready[i], 8);
       mbar_init(&ms.k_land[i], kProducerWarps * 32);        // one async arrival per gather thread
-      mbar_init(&ms.v_land[i], kProducerWarps);             // one expect-tx arrival per gather warp
+      mbar_init(&ms.v_land[i], kProducerWarps * 32);        // one async arrival per gather thread
       mbar_init(&ms.qk_done[i], 1);
       mbar_init(&ms.pv_done[i], 1);
       mbar_init(&ms.valid_ready[i], 1);
@@ -179,7 +178,6 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
     }
     fence_mbar_init();
     tma_prefetch_desc(&map_q);
-    tma_prefetch_desc(&map_kv);
     for (int d = 0; d < p.n_out; ++d) tma_prefetch_desc(&omaps.m[d]);
   }
   __syncthreads();
@@ -561,21 +559,18 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         const bool ok = kb < 2 || mbar_test(&ms.pv_done[s], ph ^ 1);
         if (__all_sync(0xffffffffu, ok)) {
           const uint32_t vst = sbase + kOffV + s * kVStage;
-          // the V rows go through the TMA unit (gather4: four rows x 128 bytes per instruction,
-          // 8 per warp and block), so the LSU path carries only the K rows
-          const uint32_t vbar = smem_u32(&ms.v_land[s]);
-          mbar_arrive_expect_tx_elect(&ms.v_land[s], 8u * 512u);
+          // lane: row 16pw + 2i + lane/16 of the block's 128 keys, 16-byte piece lane%16 of this
+          // CTA's 256 value bytes
+          const int pc = lane & 15, nbk = pc >> 3, c8 = pc & 7;
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            int4 rows;
-            rows.x = __shfl_sync(0xffffffffu, vidx, 16 + 4 * j);
-            rows.y = __shfl_sync(0xffffffffu, vidx, 17 + 4 * j);
-            rows.z = __shfl_sync(0xffffffffu, vidx, 18 + 4 * j);
-            rows.w = __shfl_sync(0xffffffffu, vidx, 19 + 4 * j);
-            const uint32_t dst = vst + (16 * pw + 4 * j) * 128;
-            tma_gather4_elect(dst, &map_kv, 256 * (int)cta, rows, vbar);
-            tma_gather4_elect(dst + kVChunk, &map_kv, 256 * (int)cta + 128, rows, vbar);
+          for (int i = 0; i < 8; ++i) {
+            const int rloc = 2 * i + (lane >> 4);
+            const int ri = __shfl_sync(0xffffffffu, vidx, 16 + rloc);
+            const int row = 16 * pw + rloc;
+            cp_async16_hint(vst + nbk * kVChunk + row * 128 + ((c8 ^ (row & 7)) << 4),
+                       kvb + (size_t)ri * pitch + 256 * cta + 16 * pc, pol_keep);
           }
+          cp_async_mbar_arrive_noinc(&ms.v_land[s]);
           cur_next(cv);
           if (cv.tile < p.ng) vidx = load_idx(cv);
           did = true;
@@ -787,7 +782,7 @@ static int launch_fp8(const void* q8, const void* kv8, const int32_t* indices, f
                       void* const* outs, int n_out, float* max_logits, float* lse, int ng, int s_kv, int topk,
                       long long q_row_stride, long long kv_row_stride, long long idx_row_stride,
                       float* dbg, cudaStream_t stream) {
-  CUtensorMap map_q, map_kv;
+  CUtensorMap map_q;
   OutMaps omaps;
   // out is stored as boxes of 32 rows x 32 dims (64 bytes wide, 64-byte swizzle)
   for (int d = 0; d < kMaxOutputs; ++d)
@@ -796,9 +791,6 @@ static int launch_fp8(const void* q8, const void* kv8, const int32_t* indices, f
       return LITEDSA_ERR_CUDA;
   if (!make_map_2d(&map_q, q8, CU_TENSOR_MAP_DATA_TYPE_UINT8, kDQK, (uint64_t)ng * 128,
                    (uint64_t)q_row_stride, 128, 64))
-    return LITEDSA_ERR_CUDA;
-  if (!make_map_2d(&map_kv, kv8, CU_TENSOR_MAP_DATA_TYPE_UINT8, kDQK, (uint64_t)s_kv,
-                   (uint64_t)kv_row_stride, 128, 1))
     return LITEDSA_ERR_CUDA;
   AttnParams p;
   p.memb = memb; p.indices = indices; p.counts = counts;
@@ -812,7 +804,7 @@ static int launch_fp8(const void* q8, const void* kv8, const int32_t* indices, f
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem) !=
       cudaSuccess)
     return LITEDSA_ERR_CUDA;
-  kern<<<2 * min(ng, max_clusters()), kAttnThreads, kAttnSmem, stream>>>(map_q, map_kv, omaps, p);
+  kern<<<2 * min(ng, max_clusters()), kAttnThreads, kAttnSmem, stream>>>(map_q, omaps, p);
   return cudaGetLastError() == cudaSuccess ? LITEDSA_OK : LITEDSA_ERR_CUDA;
 }
 

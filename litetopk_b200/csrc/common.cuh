@@ -426,6 +426,23 @@ __host__ __device__ constexpr uint32_t umma_idesc(uint32_t a_fmt, uint32_t b_fmt
 }
 
 // ---------------------------------------------------------------- small math
+// max of three floats in one instruction (sm_100 has a 3-input FMNMX)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+// (a.x * b + c, a.y * b + c) as one packed FMA
+__device__ __forceinline__ float2 fma2_scalar(float ax, float ay, float b, float c) {
+  unsigned long long pa, pb, pc, pr;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(pa) : "f"(ax), "f"(ay));
+  asm("mov.b64 %0, {%1, %1};" : "=l"(pb) : "f"(b));
+  asm("mov.b64 %0, {%1, %1};" : "=l"(pc) : "f"(c));
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(pr) : "l"(pa), "l"(pb), "l"(pc));
+  float2 r;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(pr));
+  return r;
+}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
