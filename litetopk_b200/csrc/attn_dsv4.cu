@@ -100,7 +100,8 @@ __device__ __forceinline__ void mma_f16_elect(uint32_t d_tmem, uint64_t adesc, u
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kc32,
             const __grid_constant__ CUtensorMap map_kr32, const __grid_constant__ CUtensorMap map_kc64,
-            const __grid_constant__ CUtensorMap map_kr64, const Params p) {
+            const __grid_constant__ CUtensorMap map_kr64,
+            const __grid_constant__ CUtensorMap map_out, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t sbase = (raw + 1023u) & ~1023u;
@@ -130,6 +131,7 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
     tma_prefetch_desc(&map_kr32);
     tma_prefetch_desc(&map_kc64);
     tma_prefetch_desc(&map_kr64);
+    tma_prefetch_desc(&map_out);
   }
   __syncthreads();
   cluster_sync_all();
@@ -256,24 +258,45 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
     if (p.sink != nullptr && li > 0.f) denom += fast_exp2(__ldg(p.sink + row) * kLog2e - m);
     const bool empty = !(li > 0.f);
     const float oscale = empty ? 0.f : __fdividef(1.0f, denom);
-    __nv_bfloat16* orow = p.out + grow * kDV + 256 * h;
-    float o[32];
-#pragma unroll 1
+    // Each warp stages a round (32 rows x 32 dims = 64 bytes per row, 64-byte swizzle: the
+    // 16-byte stores of eight consecutive rows hit distinct banks) in its own 2 KB slice of
+    // the P buffer (free: every PV has completed) and one lane hands the box to TMA:
+    // full-sector asynchronous writes instead of 32 scattered 16-byte stores per instruction.
+    const uint32_t stage_off = kOffP + warp * 2048;
+    uint8_t* st_row = sm + stage_off + (r & 31) * 64;
+    const int sw = (r >> 1) & 3;
+    const int out_y = tile * 128 + (int)cta * 64 + 32 * (warp & 1);
+    const uint32_t emask = empty ? 0u : 0xffffffffu;
+    const uint32_t ocol = tmem + lane_base + kTmemO;
+    float ob[2][32];
+    tmem_ld32(ocol, ob[0]);
+#pragma unroll
     for (int cc = 0; cc < 8; ++cc) {
-      tmem_ld32(tmem + lane_base + kTmemO + cc * 32, o);
+      float* o = ob[cc & 1];
       tmem_wait_ld();
+      if (cc < 7) tmem_ld32(ocol + (cc + 1) * 32, ob[(cc + 1) & 1]);
       uint32_t w[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
-        const float a = empty ? 0.f : o[2 * j] * oscale;
-        const float b = empty ? 0.f : o[2 * j + 1] * oscale;
-        __nv_bfloat162 v2 = __floats2bfloat162_rn(a, b);
-        w[j] = *reinterpret_cast<uint32_t*>(&v2);
+        __nv_bfloat162 v2 = __floats2bfloat162_rn(o[2 * j] * oscale, o[2 * j + 1] * oscale);
+        w[j] = *reinterpret_cast<uint32_t*>(&v2) & emask;      // rows without a key: zeros
       }
-      uint4* dst = reinterpret_cast<uint4*>(orow + cc * 32);
+      if (cc > 0) {   // the previous round's box must have been read out of the slice
+        if (lane == 0) bulk_wait_read_all();
+        __syncwarp();
+      }
 #pragma unroll
-      for (int j = 0; j < 4; ++j) dst[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+      for (int j = 0; j < 4; ++j)
+        *reinterpret_cast<uint4*>(st_row + ((j ^ sw) << 4)) =
+            make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(&map_out, sbase + stage_off, 256 * h + 32 * cc, out_y);
+        bulk_commit_group();
+      }
     }
+    if (lane == 0) bulk_wait_all();   // boxes written before the CTA retires
     tc_fence_before();
   } else if (warp == 4) {
     // ------------------------------------------------------------ TMA producer (tiled loads)
@@ -397,13 +420,16 @@ extern "C" int litedsa_dsv4_c128a_bf16(const void* q, const void* kv_comp, const
   const void* kc = n_comp > 0 ? kv_comp : kv_raw;      // never dereferenced when n_comp == 0
   const uint64_t kc_rows = n_comp > 0 ? (uint64_t)n_comp : 1;
   const int64_t kc_pitch = n_comp > 0 ? kc_row_stride : kr_row_stride;
-  CUtensorMap mq, mkc32, mkr32, mkc64, mkr64;
+  CUtensorMap mq, mkc32, mkr32, mkc64, mkr64, mout;
   const auto BF = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   if (!make_map_2d(&mq, q, BF, kD, (uint64_t)ng * 128, (uint64_t)q_row_stride * 2, 64, 64) ||
       !make_map_2d(&mkc32, kc, BF, kD, kc_rows, (uint64_t)kc_pitch * 2, 64, 32) ||
       !make_map_2d(&mkr32, kv_raw, BF, kD, (uint64_t)s_raw, (uint64_t)kr_row_stride * 2, 64, 32) ||
       !make_map_2d(&mkc64, kc, BF, kD, kc_rows, (uint64_t)kc_pitch * 2, 64, 64) ||
-      !make_map_2d(&mkr64, kv_raw, BF, kD, (uint64_t)s_raw, (uint64_t)kr_row_stride * 2, 64, 64))
+      !make_map_2d(&mkr64, kv_raw, BF, kD, (uint64_t)s_raw, (uint64_t)kr_row_stride * 2, 64, 64) ||
+      // out leaves as boxes of 32 rows x 32 dims (64 bytes wide, 64-byte swizzle)
+      !make_map_2d(&mout, out, BF, kDV, (uint64_t)ng * 128, (uint64_t)kDV * 2, 32, 32,
+                   CU_TENSOR_MAP_SWIZZLE_64B))
     return LITEDSA_ERR_CUDA;
   Params p;
   p.out = reinterpret_cast<__nv_bfloat16*>(out); p.lse = lse; p.sink = attn_sink;
@@ -413,7 +439,7 @@ extern "C" int litedsa_dsv4_c128a_bf16(const void* q, const void* kv_comp, const
       cudaSuccess)
     return LITEDSA_ERR_CUDA;
   dsv4_kernel<<<2 * ng, kThreads, kSmem, reinterpret_cast<cudaStream_t>(stream)>>>(
-      mq, mkc32, mkr32, mkc64, mkr64, p);
+      mq, mkc32, mkr32, mkc64, mkr64, mout, p);
   return cudaGetLastError() == cudaSuccess ? LITEDSA_OK : LITEDSA_ERR_CUDA;
 }
 
