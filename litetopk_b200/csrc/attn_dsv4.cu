@@ -54,8 +54,10 @@ constexpr float kRescaleThreshold = 6.0f;
 struct Misc {
   uint64_t q_full, k_full[2], v_full[2], s_free[2], p_ready;   // used in the leader CTA
   uint64_t qk_done[2], pv_done[2];                             // every CTA (one phase per stage use)
+  uint64_t q_free;                                             // every CTA: the tile's QK^T are complete
+  uint64_t o_free;                                             // leader CTA: O has been read out of TMEM
   uint32_t tmem_base, pad;
-  float xbuf[2][128];
+  float xbuf[3][128];   // [block parity | 2 = end-of-tile row-sum merge][lane]
 };
 static_assert(sizeof(Misc) <= kMiscBytes, "Misc too large");
 
@@ -68,7 +70,7 @@ struct Params {
 };
 
 enum { kSiteQ = 101, kSiteKFull, kSiteVFull, kSiteQkDone, kSitePvDone, kSiteSFree, kSitePReady,
-       kSiteKFree, kSiteVFree, kSitePFree, kSiteEpi };
+       kSiteKFree, kSiteVFree, kSitePFree, kSiteEpi, kSiteQFree, kSiteOFree };
 
 __device__ int g_status[4];
 
@@ -109,15 +111,18 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
   Misc& ms = *reinterpret_cast<Misc*>(sm + kOffMisc);
   int* status = g_status;
 
+  // Persistent: each cluster walks tiles cid, cid + #clusters, ...  Stages, buffers and
+  // barrier phases are indexed by the cluster-wide running block number kb, so the next
+  // tile's Q / K / V loads and first QK^T overlap the previous tile's epilogue.
   const uint32_t cta = cluster_ctarank();
-  const int tile = blockIdx.x >> 1;
+  const int cid = blockIdx.x >> 1, ncl = gridDim.x >> 1;
   const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
-  const TilePlan tp = plan_tile(p, tile);
-  const int nb = tp.nb;
 
   if (threadIdx.x == 0) {
     mbar_init(&ms.q_full, 1);
     mbar_init(&ms.p_ready, 8);
+    mbar_init(&ms.q_free, 1);
+    mbar_init(&ms.o_free, 8);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&ms.k_full[i], 1);
       mbar_init(&ms.v_full[i], 1);
@@ -150,19 +155,25 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
     const int r = tl & 63, h = tl >> 6;           // row of this CTA, key half (32 columns)
     const int row = (int)cta * 64 + r;
     const int q = row / p.h_per_q;                // token of the tile this row belongs to
-    const int pq = tp.p0 + q;
-    const int pref_q = min(pq / p.ratio, p.n_comp);
-    const int lo_q = max(pq - p.window + 1, 0) - tp.wlo;   // window-rank range of this token
-    const int hi_q = pq - tp.wlo + 1;
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
     const float c = p.scale_log2;
     const uint32_t a_s_free[2] = {mapa(smem_u32(&ms.s_free[0]), 0), mapa(smem_u32(&ms.s_free[1]), 0)};
     const uint32_t a_p_ready = mapa(smem_u32(&ms.p_ready), 0);
+    const uint32_t a_o_free = mapa(smem_u32(&ms.o_free), 0);
+    int kb0 = 0;
+   for (int tile = cid; tile < p.ng; tile += ncl) {
+    const TilePlan tp = plan_tile(p, tile);
+    const int nb = tp.nb;
+    const int pq = tp.p0 + q;
+    const int pref_q = min(pq / p.ratio, p.n_comp);
+    const int lo_q = max(pq - p.window + 1, 0) - tp.wlo;   // window-rank range of this token
+    const int hi_q = pq - tp.wlo + 1;
     float m = kMInit, li = 0.f, real_m = -INFINITY;
 
     for (int k = 0; k < nb; ++k) {
-      const int s = k & 1;
-      const uint32_t ph = (k >> 1) & 1;
+      const int kb = kb0 + k;
+      const int s = kb & 1;
+      const uint32_t ph = (kb >> 1) & 1;
       mbar_wait(&ms.qk_done[s], ph, status, kSiteQkDone, k);
       tc_fence_after();
       float sv[32];
@@ -191,9 +202,9 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
         cur = fmaxf(cur, sv[j]);
       }
       cur *= c;
-      ms.xbuf[k & 1][tl] = cur;
+      ms.xbuf[kb & 1][tl] = cur;
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      cur = fmaxf(cur, ms.xbuf[k & 1][tl ^ 64]);
+      cur = fmaxf(cur, ms.xbuf[kb & 1][tl ^ 64]);
       real_m = fmaxf(real_m, cur);
       const bool rescale = __any_sync(0xffffffffu, cur - m > kRescaleThreshold);
       float new_m = m, scale_old = 1.f;
@@ -213,8 +224,9 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
         __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
         pk[j >> 1] = *reinterpret_cast<uint32_t*>(&b2);
       }
-      // the single P buffer was last read by PV(k-1)
-      if (k >= 1) mbar_wait(&ms.pv_done[(k - 1) & 1], ((k - 1) >> 1) & 1, status, kSitePFree, k);
+      // the single P buffer was last read by the PV of the previous block (of this or the
+      // previous tile)
+      if (kb >= 1) mbar_wait(&ms.pv_done[(kb - 1) & 1], ((kb - 1) >> 1) & 1, status, kSitePFree, k);
       // P: [64 rows][64 keys] bf16, K-major core matrices: 8-key group cg at cg*1024 + row*16
       uint8_t* pdst = sm + kOffP + (4 * h) * 1024 + r * 16;
 #pragma unroll
@@ -242,9 +254,10 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
     }
 
     // epilogue
-    ms.xbuf[nb & 1][tl] = li;
+    const int kbl = kb0 + nb - 1;                 // last block of the tile
+    ms.xbuf[2][tl] = li;
     asm volatile("bar.sync 1, 128;" ::: "memory");
-    li += ms.xbuf[nb & 1][tl ^ 64];
+    li += ms.xbuf[2][tl ^ 64];
     if (real_m == -INFINITY) { li = 0.f; m = -INFINITY; }
     const size_t grow = (size_t)tile * 128 + row;
     if (h == 0) {
@@ -252,7 +265,7 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
       if (!(li > 0.f)) l = INFINITY;
       p.lse[grow] = l;
     }
-    mbar_wait(&ms.pv_done[(nb - 1) & 1], ((nb - 1) >> 1) & 1, status, kSiteEpi, nb);
+    mbar_wait(&ms.pv_done[kbl & 1], (kbl >> 1) & 1, status, kSiteEpi, nb);
     tc_fence_after();
     float denom = li;
     if (p.sink != nullptr && li > 0.f) denom += fast_exp2(__ldg(p.sink + row) * kLog2e - m);
@@ -274,7 +287,14 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
     for (int cc = 0; cc < 8; ++cc) {
       float* o = ob[cc & 1];
       tmem_wait_ld();
-      if (cc < 7) tmem_ld32(ocol + (cc + 1) * 32, ob[(cc + 1) & 1]);
+      if (cc < 7) {
+        tmem_ld32(ocol + (cc + 1) * 32, ob[(cc + 1) & 1]);
+      } else {
+        // O has been read: the next tile's first PV may overwrite it
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(a_o_free);
+      }
       uint32_t w[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
@@ -296,6 +316,12 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
         bulk_commit_group();
       }
     }
+    // The slices are P again in the next tile: every issuing lane waits for its last box to
+    // be read, and each P store of the next tile comes after a barrier of the four warps
+    // (the row-max exchange) that the issuing lanes only reach after this wait.
+    if (lane == 0) bulk_wait_read_all();
+    kb0 += nb;
+   }
     if (lane == 0) bulk_wait_all();   // boxes written before the CTA retires
     tc_fence_before();
   } else if (warp == 4) {
@@ -304,28 +330,37 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
       const uint32_t a_q_full = mapa(smem_u32(&ms.q_full), 0);
       const uint32_t a_k_full[2] = {mapa(smem_u32(&ms.k_full[0]), 0), mapa(smem_u32(&ms.k_full[1]), 0)};
       const uint32_t a_v_full[2] = {mapa(smem_u32(&ms.v_full[0]), 0), mapa(smem_u32(&ms.v_full[1]), 0)};
-      if (cta == 0) mbar_arrive_expect_tx(&ms.q_full, 2 * kQBytes);
-      for (int j = 0; j < kQChunks; ++j)
-        tma_load_2d_pair(sbase + kOffQ + j * kQChunkBytes, &map_q, 64 * j, tile * 128 + (int)cta * 64,
-                         a_q_full);
-      for (int k = 0; k < nb; ++k) {
-        const int s = k & 1;
-        const uint32_t ph = (k >> 1) & 1;
-        const bool comp = k < tp.nbc;
-        const int row0 = comp ? k * kBlockKeys : tp.wlo + (k - tp.nbc) * kBlockKeys;
-        const CUtensorMap* m32 = comp ? &map_kc32 : &map_kr32;
-        const CUtensorMap* m64 = comp ? &map_kc64 : &map_kr64;
-        if (k >= 2) mbar_wait(&ms.qk_done[s], ph ^ 1, status, kSiteKFree, k);   // K stage free
-        if (cta == 0) mbar_arrive_expect_tx(&ms.k_full[s], 2 * kKStage);
+      int kb0 = 0, it = 0;
+      for (int tile = cid; tile < p.ng; tile += ncl, ++it) {
+        const TilePlan tp = plan_tile(p, tile);
+        const int nb = tp.nb;
+        // the previous tile's Q must have been consumed by its last QK^T
+        if (it > 0) mbar_wait(&ms.q_free, (it - 1) & 1, status, kSiteQFree, it);
+        if (cta == 0) mbar_arrive_expect_tx(&ms.q_full, 2 * kQBytes);
         for (int j = 0; j < kQChunks; ++j)
-          tma_load_2d_pair(sbase + kOffK + s * kKStage + j * kKChunkBytes, m32, 64 * j,
-                           row0 + 32 * (int)cta, a_k_full[s]);
-        // V stage s was last read by PV(k-2)
-        if (k >= 2) mbar_wait(&ms.pv_done[s], ph ^ 1, status, kSiteVFree, k);
-        if (cta == 0) mbar_arrive_expect_tx(&ms.v_full[s], 2 * kVStage);
-        for (int j = 0; j < 4; ++j)
-          tma_load_2d_pair(sbase + kOffV + s * kVStage + j * kVChunkBytes, m64,
-                           256 * (int)cta + 64 * j, row0, a_v_full[s]);
+          tma_load_2d_pair(sbase + kOffQ + j * kQChunkBytes, &map_q, 64 * j, tile * 128 + (int)cta * 64,
+                           a_q_full);
+        for (int k = 0; k < nb; ++k) {
+          const int kb = kb0 + k;
+          const int s = kb & 1;
+          const uint32_t ph = (kb >> 1) & 1;
+          const bool comp = k < tp.nbc;
+          const int row0 = comp ? k * kBlockKeys : tp.wlo + (k - tp.nbc) * kBlockKeys;
+          const CUtensorMap* m32 = comp ? &map_kc32 : &map_kr32;
+          const CUtensorMap* m64 = comp ? &map_kc64 : &map_kr64;
+          if (kb >= 2) mbar_wait(&ms.qk_done[s], ph ^ 1, status, kSiteKFree, k);   // K stage free
+          if (cta == 0) mbar_arrive_expect_tx(&ms.k_full[s], 2 * kKStage);
+          for (int j = 0; j < kQChunks; ++j)
+            tma_load_2d_pair(sbase + kOffK + s * kKStage + j * kKChunkBytes, m32, 64 * j,
+                             row0 + 32 * (int)cta, a_k_full[s]);
+          // V stage s was last read by the PV of block kb-2
+          if (kb >= 2) mbar_wait(&ms.pv_done[s], ph ^ 1, status, kSiteVFree, k);
+          if (cta == 0) mbar_arrive_expect_tx(&ms.v_full[s], 2 * kVStage);
+          for (int j = 0; j < 4; ++j)
+            tma_load_2d_pair(sbase + kOffV + s * kVStage + j * kVChunkBytes, m64,
+                             256 * (int)cta + 64 * j, row0, a_v_full[s]);
+        }
+        kb0 += nb;
       }
     }
   } else if (cta == 0) {
@@ -334,50 +369,63 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
     constexpr uint32_t idesc_pv = umma_idesc(1, 1, false, true, 128, 256);
     const uint32_t a_qk_done_peer[2] = {mapa(smem_u32(&ms.qk_done[0]), 1), mapa(smem_u32(&ms.qk_done[1]), 1)};
     const uint32_t a_pv_done_peer[2] = {mapa(smem_u32(&ms.pv_done[0]), 1), mapa(smem_u32(&ms.pv_done[1]), 1)};
-    mbar_wait(&ms.q_full, 0, status, kSiteQ, 0);
-    __syncwarp();
-    for (int k = 0; k <= nb; ++k) {
-      if (k < nb) {
-        const int s = k & 1;
-        const uint32_t ph = (k >> 1) & 1;
-        mbar_wait(&ms.k_full[s], ph, status, kSiteKFull, k);
-        if (k >= 2) mbar_wait(&ms.s_free[s], ph ^ 1, status, kSiteSFree, k);
-        __syncwarp();
-        tc_fence_after();
-        const uint32_t d = tmem + (s ? kTmemS1 : kTmemS0);
-        const uint64_t ad0 = umma_desc(sbase + kOffQ, 16, 1024, kSwz128);
-        const uint64_t bd0 = umma_desc(sbase + kOffK + s * kKStage, 16, 1024, kSwz128);
+    const uint32_t a_q_free_peer = mapa(smem_u32(&ms.q_free), 1);
+    int kb0 = 0, it = 0;
+    for (int tile = cid; tile < p.ng; tile += ncl, ++it) {
+      const int nb = plan_tile(p, tile).nb;
+      mbar_wait(&ms.q_full, it & 1, status, kSiteQ, it);
+      __syncwarp();
+      for (int k = 0; k <= nb; ++k) {
+        if (k < nb) {
+          const int kb = kb0 + k;
+          const int s = kb & 1;
+          const uint32_t ph = (kb >> 1) & 1;
+          mbar_wait(&ms.k_full[s], ph, status, kSiteKFull, k);
+          if (kb >= 2) mbar_wait(&ms.s_free[s], ph ^ 1, status, kSiteSFree, k);
+          __syncwarp();
+          tc_fence_after();
+          const uint32_t d = tmem + (s ? kTmemS1 : kTmemS0);
+          const uint64_t ad0 = umma_desc(sbase + kOffQ, 16, 1024, kSwz128);
+          const uint64_t bd0 = umma_desc(sbase + kOffK + s * kKStage, 16, 1024, kSwz128);
 #pragma unroll
-        for (int j = 0; j < kQChunks; ++j) {
+          for (int j = 0; j < kQChunks; ++j) {
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            mma_f16_elect(d, ad0 + (uint64_t)(j * (kQChunkBytes >> 4) + kk * 2),
-                          bd0 + (uint64_t)(j * (kKChunkBytes >> 4) + kk * 2), idesc_qk,
-                          (j | kk) ? 1u : 0u);
+            for (int kk = 0; kk < 4; ++kk)
+              mma_f16_elect(d, ad0 + (uint64_t)(j * (kQChunkBytes >> 4) + kk * 2),
+                            bd0 + (uint64_t)(j * (kKChunkBytes >> 4) + kk * 2), idesc_qk,
+                            (j | kk) ? 1u : 0u);
+          }
+          mma_commit_pair_elect(smem_u32(&ms.qk_done[s]));
+          mma_commit_pair_elect(a_qk_done_peer[s]);
+          if (k == nb - 1) {     // the Q tile is no longer needed once these MMAs complete
+            mma_commit_pair_elect(smem_u32(&ms.q_free));
+            mma_commit_pair_elect(a_q_free_peer);
+          }
         }
-        mma_commit_pair_elect(smem_u32(&ms.qk_done[s]));
-        mma_commit_pair_elect(a_qk_done_peer[s]);
-      }
-      if (k > 0) {
-        const int kb = k - 1;
-        const int s = kb & 1;
-        mbar_wait(&ms.p_ready, kb & 1, status, kSitePReady, kb);
-        mbar_wait(&ms.v_full[s], (kb >> 1) & 1, status, kSiteVFull, kb);
-        __syncwarp();
-        tc_fence_after();
-        const uint64_t ad0 = umma_desc(sbase + kOffP, 1024, 128, kSwzNone);
-        const uint64_t bd0 = umma_desc(sbase + kOffV + s * kVStage, kVChunkBytes, 1024, kSwz128);
+        if (k > 0) {
+          const int kl = k - 1, kb = kb0 + kl;
+          const int s = kb & 1;
+          mbar_wait(&ms.p_ready, kb & 1, status, kSitePReady, kl);
+          mbar_wait(&ms.v_full[s], (kb >> 1) & 1, status, kSiteVFull, kl);
+          // the tile's first PV overwrites O: the previous tile must have read it out
+          if (kl == 0 && it > 0) mbar_wait(&ms.o_free, (it - 1) & 1, status, kSiteOFree, it);
+          __syncwarp();
+          tc_fence_after();
+          const uint64_t ad0 = umma_desc(sbase + kOffP, 1024, 128, kSwzNone);
+          const uint64_t bd0 = umma_desc(sbase + kOffV + s * kVStage, kVChunkBytes, 1024, kSwz128);
 #pragma unroll
-        for (int nbk = 0; nbk < 2; ++nbk) {
+          for (int nbk = 0; nbk < 2; ++nbk) {
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            mma_f16_elect(tmem + kTmemO + nbk * 128, ad0 + (uint64_t)(ks * (2048 >> 4)),
-                          bd0 + (uint64_t)(nbk * (2 * kVChunkBytes >> 4) + ks * (2048 >> 4)), idesc_pv,
-                          (kb | ks) ? 1u : 0u);
+            for (int ks = 0; ks < 4; ++ks)
+              mma_f16_elect(tmem + kTmemO + nbk * 128, ad0 + (uint64_t)(ks * (2048 >> 4)),
+                            bd0 + (uint64_t)(nbk * (2 * kVChunkBytes >> 4) + ks * (2048 >> 4)), idesc_pv,
+                            (kl | ks) ? 1u : 0u);
+          }
+          mma_commit_pair_elect(smem_u32(&ms.pv_done[s]));
+          mma_commit_pair_elect(a_pv_done_peer[s]);
         }
-        mma_commit_pair_elect(smem_u32(&ms.pv_done[s]));
-        mma_commit_pair_elect(a_pv_done_peer[s]);
       }
+      kb0 += nb;
     }
   }
 
@@ -386,6 +434,30 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
   cluster_sync_all();
   if (warp == 5) tmem_dealloc_pair(tmem, kTmemCols);
   if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&status[3], 1);
+}
+
+// how many 2-CTA clusters of this kernel the current device can hold at once
+static int max_clusters() {
+  static thread_local int cached_dev = -1, cached = 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev == cached_dev) return cached;
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int n = sms / 2;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(sms, 1, 1); cfg.blockDim = dim3(kThreads, 1, 1); cfg.dynamicSmemBytes = kSmem;
+  cudaLaunchAttribute at;
+  at.id = cudaLaunchAttributeClusterDimension;
+  at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+  cfg.attrs = &at; cfg.numAttrs = 1;
+  int q = 0;
+  if (cudaFuncSetAttribute(dsv4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) == cudaSuccess &&
+      cudaOccupancyMaxActiveClusters(&q, dsv4_kernel, &cfg) == cudaSuccess && q > 0)
+    n = q;
+  cudaGetLastError();
+  cached_dev = dev; cached = n;
+  return n;
 }
 
 }  // namespace dsv4
@@ -438,7 +510,7 @@ extern "C" int litedsa_dsv4_c128a_bf16(const void* q, const void* kv_comp, const
   if (cudaFuncSetAttribute(dsv4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) !=
       cudaSuccess)
     return LITEDSA_ERR_CUDA;
-  dsv4_kernel<<<2 * ng, kThreads, kSmem, reinterpret_cast<cudaStream_t>(stream)>>>(
+  dsv4_kernel<<<2 * min(ng, max_clusters()), kThreads, kSmem, reinterpret_cast<cudaStream_t>(stream)>>>(
       mq, mkc32, mkr32, mkc64, mkr64, mout, p);
   return cudaGetLastError() == cudaSuccess ? LITEDSA_OK : LITEDSA_ERR_CUDA;
 }
