@@ -23,7 +23,8 @@
 namespace lt {
 namespace dsv4 {
 
-constexpr int kThreads = 192;                         // 4 softmax warps, 1 TMA warp, 1 MMA warp
+constexpr int kThreads = 320;                         // 4 softmax warps, 1 TMA warp, 1 MMA warp, 4 epilogue warps
+constexpr int kWarpEpi0 = 6;
 constexpr int kBlockKeys = 64;
 constexpr int kD = 576, kDV = 512;
 constexpr int kQChunks = 9;                           // 64 bf16 = 128 bytes per chunk
@@ -38,9 +39,11 @@ constexpr uint32_t kOffQ = 0;
 constexpr uint32_t kOffK = kOffQ + kQBytes;
 constexpr uint32_t kOffV = kOffK + 2 * kKStage;
 constexpr uint32_t kOffP = kOffV + 2 * kVStage;
-constexpr uint32_t kOffMisc = kOffP + kPBytes;        // 221184
-constexpr uint32_t kMiscBytes = 2048;
-constexpr uint32_t kSmem = kOffMisc + kMiscBytes + 1024;
+constexpr uint32_t kOffStage = kOffP + kPBytes;       // 221184: 4 x 2 KB output staging slices (epilogue warps)
+constexpr uint32_t kOffMisc = kOffStage + 4 * 2048;
+constexpr uint32_t kMiscBytes = 2304;
+constexpr uint32_t kSmemUsed = kOffMisc + kMiscBytes;
+constexpr uint32_t kSmem = 232448;                    // all of it: 768 bytes of alignment slack remain
 static_assert(kSmem <= 232448, "shared-memory plan exceeds the 227 KB per-CTA limit");
 
 constexpr uint32_t kTmemCols = 512;
@@ -56,8 +59,10 @@ struct Misc {
   uint64_t qk_done[2], pv_done[2];                             // every CTA (one phase per stage use)
   uint64_t q_free;                                             // every CTA: the tile's QK^T are complete
   uint64_t o_free;                                             // leader CTA: O has been read out of TMEM
+  uint64_t epi_ready;                                          // every CTA: the tile's row scales are published
   uint32_t tmem_base, pad;
   float xbuf[3][128];   // [block parity | 2 = end-of-tile row-sum merge][lane]
+  float oscale[2][64];  // [tile parity][row]: 1 / normaliser, 0 for rows without a key
 };
 static_assert(sizeof(Misc) <= kMiscBytes, "Misc too large");
 
@@ -70,7 +75,7 @@ struct Params {
 };
 
 enum { kSiteQ = 101, kSiteKFull, kSiteVFull, kSiteQkDone, kSitePvDone, kSiteSFree, kSitePReady,
-       kSiteKFree, kSiteVFree, kSitePFree, kSiteEpi, kSiteQFree, kSiteOFree };
+       kSiteKFree, kSiteVFree, kSitePFree, kSiteEpi, kSiteQFree, kSiteOFree, kSiteSmem };
 
 __device__ int g_status[4];
 
@@ -110,6 +115,12 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
   uint8_t* sm = smem_raw + (sbase - raw);
   Misc& ms = *reinterpret_cast<Misc*>(sm + kOffMisc);
   int* status = g_status;
+  // the plan leaves less than 1024 bytes for aligning the base: refuse to run (uniformly, in
+  // both CTAs, before any barrier exists) if this launch's base needs more
+  if ((sbase - raw) + kSmemUsed > kSmem) {
+    if (threadIdx.x == 0 && atomicCAS(status, 0, (int)kSiteSmem) == 0) status[1] = (int)blockIdx.x;
+    return;
+  }
 
   // Persistent: each cluster walks tiles cid, cid + #clusters, ...  Stages, buffers and
   // barrier phases are indexed by the cluster-wide running block number kb, so the next
@@ -123,6 +134,7 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
     mbar_init(&ms.p_ready, 8);
     mbar_init(&ms.q_free, 1);
     mbar_init(&ms.o_free, 8);
+    mbar_init(&ms.epi_ready, 4);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&ms.k_full[i], 1);
       mbar_init(&ms.v_full[i], 1);
@@ -159,8 +171,7 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
     const float c = p.scale_log2;
     const uint32_t a_s_free[2] = {mapa(smem_u32(&ms.s_free[0]), 0), mapa(smem_u32(&ms.s_free[1]), 0)};
     const uint32_t a_p_ready = mapa(smem_u32(&ms.p_ready), 0);
-    const uint32_t a_o_free = mapa(smem_u32(&ms.o_free), 0);
-    int kb0 = 0;
+    int kb0 = 0, it = 0;
    for (int tile = cid; tile < p.ng; tile += ncl) {
     const TilePlan tp = plan_tile(p, tile);
     const int nb = tp.nb;
@@ -254,7 +265,6 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
     }
 
     // epilogue
-    const int kbl = kb0 + nb - 1;                 // last block of the tile
     ms.xbuf[2][tl] = li;
     asm volatile("bar.sync 1, 128;" ::: "memory");
     li += ms.xbuf[2][tl ^ 64];
@@ -265,65 +275,15 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
       if (!(li > 0.f)) l = INFINITY;
       p.lse[grow] = l;
     }
-    mbar_wait(&ms.pv_done[kbl & 1], (kbl >> 1) & 1, status, kSiteEpi, nb);
-    tc_fence_after();
+    // hand the tile over to the epilogue warps: all they need is 1 / normaliser per row
     float denom = li;
     if (p.sink != nullptr && li > 0.f) denom += fast_exp2(__ldg(p.sink + row) * kLog2e - m);
-    const bool empty = !(li > 0.f);
-    const float oscale = empty ? 0.f : __fdividef(1.0f, denom);
-    // Each warp stages a round (32 rows x 32 dims = 64 bytes per row, 64-byte swizzle: the
-    // 16-byte stores of eight consecutive rows hit distinct banks) in its own 2 KB slice of
-    // the P buffer (free: every PV has completed) and one lane hands the box to TMA:
-    // full-sector asynchronous writes instead of 32 scattered 16-byte stores per instruction.
-    const uint32_t stage_off = kOffP + warp * 2048;
-    uint8_t* st_row = sm + stage_off + (r & 31) * 64;
-    const int sw = (r >> 1) & 3;
-    const int out_y = tile * 128 + (int)cta * 64 + 32 * (warp & 1);
-    const uint32_t emask = empty ? 0u : 0xffffffffu;
-    const uint32_t ocol = tmem + lane_base + kTmemO;
-    float ob[2][32];
-    tmem_ld32(ocol, ob[0]);
-#pragma unroll
-    for (int cc = 0; cc < 8; ++cc) {
-      float* o = ob[cc & 1];
-      tmem_wait_ld();
-      if (cc < 7) {
-        tmem_ld32(ocol + (cc + 1) * 32, ob[(cc + 1) & 1]);
-      } else {
-        // O has been read: the next tile's first PV may overwrite it
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(a_o_free);
-      }
-      uint32_t w[16];
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        __nv_bfloat162 v2 = __floats2bfloat162_rn(o[2 * j] * oscale, o[2 * j + 1] * oscale);
-        w[j] = *reinterpret_cast<uint32_t*>(&v2) & emask;      // rows without a key: zeros
-      }
-      if (cc > 0) {   // the previous round's box must have been read out of the slice
-        if (lane == 0) bulk_wait_read_all();
-        __syncwarp();
-      }
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-        *reinterpret_cast<uint4*>(st_row + ((j ^ sw) << 4)) =
-            make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        tma_store_2d(&map_out, sbase + stage_off, 256 * h + 32 * cc, out_y);
-        bulk_commit_group();
-      }
-    }
-    // The slices are P again in the next tile: every issuing lane waits for its last box to
-    // be read, and each P store of the next tile comes after a barrier of the four warps
-    // (the row-max exchange) that the issuing lanes only reach after this wait.
-    if (lane == 0) bulk_wait_read_all();
+    if (h == 0) ms.oscale[it & 1][r] = (li > 0.f) ? __fdividef(1.0f, denom) : 0.f;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&ms.epi_ready);
     kb0 += nb;
+    ++it;
    }
-    if (lane == 0) bulk_wait_all();   // boxes written before the CTA retires
-    tc_fence_before();
   } else if (warp == 4) {
     // ------------------------------------------------------------ TMA producer (tiled loads)
     if (lane == 0) {
@@ -363,7 +323,69 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
         kb0 += nb;
       }
     }
-  } else if (cta == 0) {
+  } else if (warp >= kWarpEpi0) {
+    // ------------------------------------------------------------ epilogue warps
+    // O out of TMEM, x 1 / normaliser, bf16, TMA tile stores -- while the softmax warps already
+    // work on the next tile.  A warp reads the TMEM lanes of its quarter (warp % 4): rows r of
+    // key half h, all 256 columns in 8 rounds of 32 dims.  A round (32 rows x 64 bytes,
+    // 64-byte swizzle: the 16-byte stores of eight consecutive rows hit distinct banks) is
+    // staged in the warp's own 2 KB slice and one lane hands the box to TMA.
+    const int tl = ((warp & 3) << 5) | lane;
+    const int r = tl & 63, h = tl >> 6;
+    const uint32_t ocol = tmem + ((uint32_t)((warp & 3) * 32) << 16) + kTmemO;
+    const uint32_t stage_off = kOffStage + (warp - kWarpEpi0) * 2048;
+    uint8_t* st_row = sm + stage_off + (r & 31) * 64;
+    const int sw = (r >> 1) & 3;
+    const uint32_t a_o_free = mapa(smem_u32(&ms.o_free), 0);
+    int kb0 = 0, it = 0;
+    for (int tile = cid; tile < p.ng; tile += ncl, ++it) {
+      const int nb = plan_tile(p, tile).nb;
+      const int kbl = kb0 + nb - 1;                 // last block of the tile
+      mbar_wait(&ms.epi_ready, it & 1, status, kSiteEpi, it);
+      mbar_wait(&ms.pv_done[kbl & 1], (kbl >> 1) & 1, status, kSiteEpi, nb);
+      tc_fence_after();
+      const float oscale = ms.oscale[it & 1][r];
+      const uint32_t emask = oscale != 0.f ? 0xffffffffu : 0u;
+      const int out_y = tile * 128 + (int)cta * 64 + 32 * (warp & 1);
+      float ob[2][32];
+      tmem_ld32(ocol, ob[0]);
+#pragma unroll
+      for (int cc = 0; cc < 8; ++cc) {
+        float* o = ob[cc & 1];
+        tmem_wait_ld();
+        if (cc < 7) {
+          tmem_ld32(ocol + (cc + 1) * 32, ob[(cc + 1) & 1]);
+        } else {
+          // O has been read: the next tile's first PV may overwrite it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(a_o_free);
+        }
+        uint32_t w[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          __nv_bfloat162 v2 = __floats2bfloat162_rn(o[2 * j] * oscale, o[2 * j + 1] * oscale);
+          w[j] = *reinterpret_cast<uint32_t*>(&v2) & emask;      // rows without a key: zeros
+        }
+        // the previous round's box must have been read out of the slice
+        if (lane == 0) bulk_wait_read_all();
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          *reinterpret_cast<uint4*>(st_row + ((j ^ sw) << 4)) =
+              make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&map_out, sbase + stage_off, 256 * h + 32 * cc, out_y);
+          bulk_commit_group();
+        }
+      }
+      kb0 += nb;
+    }
+    if (lane == 0) bulk_wait_all();   // boxes written before the CTA retires
+    tc_fence_before();
+  } else if (warp == 5 && cta == 0) {
     // ------------------------------------------------------------ MMA issue (whole warp, elected lane)
     constexpr uint32_t idesc_qk = umma_idesc(1, 1, false, false, 128, 64);
     constexpr uint32_t idesc_pv = umma_idesc(1, 1, false, true, 128, 256);
@@ -434,6 +456,38 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
   cluster_sync_all();
   if (warp == 5) tmem_dealloc_pair(tmem, kTmemCols);
   if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&status[3], 1);
+}
+
+// The kernel's shared-memory plan leaves 768 bytes for aligning its tiles to 1024 bytes.
+// Dynamic shared memory of a kernel without static shared memory starts at a fixed offset
+// of the CTA's window; this probe (same configuration: no static shared memory, the same
+// dynamic size) reports that offset once per device so that the host can refuse to launch
+// instead of letting the kernel give up.
+__global__ void smem_base_probe(unsigned* out) {
+  extern __shared__ uint8_t probe_raw[];
+  if (threadIdx.x == 0) *out = smem_u32(probe_raw) & 1023u;
+}
+static bool smem_alignment_ok() {
+  static thread_local int cached_dev = -1;
+  static thread_local bool cached = false;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev == cached_dev) return cached;
+  bool ok = false;
+  unsigned* d = nullptr;
+  unsigned h = 0xffffffffu;
+  if (cudaFuncSetAttribute(smem_base_probe, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) == cudaSuccess &&
+      cudaMalloc(&d, sizeof(unsigned)) == cudaSuccess) {
+    smem_base_probe<<<1, 32, kSmem>>>(d);
+    if (cudaMemcpy(&h, d, sizeof(unsigned), cudaMemcpyDeviceToHost) == cudaSuccess) {
+      const unsigned pad = (1024u - h) & 1023u;
+      ok = pad + kSmemUsed <= kSmem;
+    }
+    cudaFree(d);
+  }
+  cudaGetLastError();
+  cached_dev = dev; cached = ok;
+  return ok;
 }
 
 // how many 2-CTA clusters of this kernel the current device can hold at once
@@ -507,6 +561,7 @@ extern "C" int litedsa_dsv4_c128a_bf16(const void* q, const void* kv_comp, const
   p.out = reinterpret_cast<__nv_bfloat16*>(out); p.lse = lse; p.sink = attn_sink;
   p.ng = ng; p.n_comp = n_comp; p.s_raw = s_raw; p.G = G; p.h_per_q = h_per_q; p.pos0 = pos0;
   p.window = window; p.ratio = ratio; p.scale_log2 = sm_scale * kLog2e;
+  if (!smem_alignment_ok()) return LITEDSA_ERR_UNSUPPORTED;   // first call per device: synchronous probe
   if (cudaFuncSetAttribute(dsv4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) !=
       cudaSuccess)
     return LITEDSA_ERR_CUDA;
