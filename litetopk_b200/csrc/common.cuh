@@ -121,29 +121,7 @@ __device__ __forceinline__ void mbar_arrive_cluster_release(uint32_t cluster_add
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
                : "memory");
 }
-__device__ __forceinline__ bool mbar_test_cluster(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// 16-byte store to shared memory of any CTA of the cluster (shared::cluster address)
-__device__ __forceinline__ void st_shared_cluster_v4(uint32_t cluster_addr, uint4 v) {
-  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "r"(v.x),
-               "r"(v.y), "r"(v.z), "r"(v.w)
-               : "memory");
-}
 
-// ---------------------------------------------------------------- fences
-// generic-proxy writes (own and distributed shared memory) -> visible to the async proxy
-__device__ __forceinline__ void fence_proxy_async_all() {
-  asm volatile("fence.proxy.async;" ::: "memory");
-}
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
@@ -168,59 +146,7 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_smem, const CUtens
       ::"r"(dst_smem), "l"(map), "r"(x), "r"(y), "r"(mbar_cluster_addr)
       : "memory");
 }
-// gather of 4 arbitrary rows x one box of columns starting at column x
-__device__ __forceinline__ void tma_gather4_pair(uint32_t dst_smem, const CUtensorMap* map, int x,
-                                                 int4 rows, uint32_t mbar_cluster_addr) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes"
-      ".cta_group::2 [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
-      ::"r"(dst_smem), "l"(map), "r"(x), "r"(rows.x), "r"(rows.y), "r"(rows.z), "r"(rows.w),
-        "r"(mbar_cluster_addr)
-      : "memory");
-}
 
-// gather of 4 rows into this CTA's smem, completion on a barrier of this CTA
-__device__ __forceinline__ void tma_gather4(uint32_t dst_smem, const CUtensorMap* map, int x,
-                                            int4 rows, uint32_t mbar_smem) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
-      ::"r"(dst_smem), "l"(map), "r"(x), "r"(rows.x), "r"(rows.y), "r"(rows.z), "r"(rows.w),
-        "r"(mbar_smem)
-      : "memory");
-}
-// elected-lane forms for fully converged warps: the surrounding code stays warp-uniform, so
-// the compiler can keep TMA operands in uniform registers instead of converting per lane
-__device__ __forceinline__ void tma_gather4_elect(uint32_t dst_smem, const CUtensorMap* map, int x,
-                                                  int4 rows, uint32_t mbar_smem) {
-  asm volatile(
-      "{\n\t.reg .pred pe;\n\telect.sync _|pe, 0xffffffff;\n\t"
-      "@pe cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%2, %3, %4, %5, %6}], [%7];\n\t}"
-      ::"r"(dst_smem), "l"(map), "r"(x), "r"(rows.x), "r"(rows.y), "r"(rows.z), "r"(rows.w),
-        "r"(mbar_smem)
-      : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx_elect(uint64_t* bar, uint32_t bytes) {
-  asm volatile(
-      "{\n\t.reg .pred pe;\n\telect.sync _|pe, 0xffffffff;\n\t"
-      "@pe mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t}"
-      ::"r"(smem_u32(bar)), "r"(bytes)
-      : "memory");
-}
-// shared -> (distributed) shared bulk copy inside the cluster; dst and mbar are shared::cluster
-// addresses of the SAME CTA, src is a shared::cta address of the issuing CTA
-__device__ __forceinline__ void bulk_copy_s2s(uint32_t dst_cluster, uint32_t src_smem,
-                                              uint32_t bytes, uint32_t mbar_cluster) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-      ::"r"(dst_cluster), "r"(src_smem), "r"(bytes), "r"(mbar_cluster)
-      : "memory");
-}
-
-// 16-byte asynchronous global -> shared copy (LSU path, any shared destination) and the
-// asynchronous arrival that fires when all earlier cp.async of the thread have landed
-// (.noinc: the arrival counts against the barrier's expected count)
 // TMA tile store shared -> global (bulk async-group completion)
 __device__ __forceinline__ void tma_store_2d(const void* map, uint32_t src_smem, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
@@ -249,6 +175,9 @@ __device__ __forceinline__ uint64_t l2_policy_evict_last() {
   asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
   return pol;
 }
+// 16-byte asynchronous global -> shared copy (LSU path, any shared destination) with an L2
+// eviction hint, and below the asynchronous arrival that fires when all earlier cp.async of
+// the thread have landed (.noinc: the arrival counts against the barrier's expected count)
 __device__ __forceinline__ void cp_async16_hint(uint32_t dst_smem, const void* src, uint64_t pol) {
   asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;"
                ::"r"(dst_smem), "l"(src), "l"(pol) : "memory");
@@ -268,9 +197,6 @@ __device__ __forceinline__ void tma_load_2d_pair_hint(uint32_t dst_smem, const C
       ::"r"(dst_smem), "l"(map), "r"(x), "r"(y), "r"(mbar_cluster_addr), "l"(pol)
       : "memory");
 }
-__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
-}
 __device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint64_t* bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -288,23 +214,6 @@ __device__ __forceinline__ void tmem_relinquish_pair() {
 __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
                : "memory");
-}
-// D[tmem] (+)= A[smem desc] * B[smem desc], one instruction for the CTA pair
-__device__ __forceinline__ void mma_f8_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
-                                            uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void mma_f16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
-                                             uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
 }
 // A whole K-loop of MMAs in one instruction stream, executed by a fully converged warp whose
 // elected lane issues (warp-uniform code lets the descriptors live in uniform registers).
@@ -350,12 +259,6 @@ __device__ __forceinline__ void mma_f8_pair_pv8(uint32_t d_tmem, uint32_t idesc,
       "}"
       ::"r"(d_tmem), "r"(idesc), "r"(a_lo), "r"(b_lo), "r"(a_hi), "r"(b_hi), "r"(accumulate_first)
       : "memory");
-}
-// all MMAs issued so far by this thread -> one arrival on the barrier at `cluster_addr`
-__device__ __forceinline__ void mma_commit_pair(uint32_t cluster_addr) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                   cluster_addr)
-               : "memory");
 }
 
 // 32 lanes x 32 consecutive fp32 columns: thread i of the warp gets lane (base_lane + i)
@@ -425,24 +328,6 @@ __host__ __device__ constexpr uint32_t umma_idesc(uint32_t a_fmt, uint32_t b_fmt
          ((b_mn ? 1u : 0u) << 16) | ((N >> 3) << 17) | ((M >> 4) << 24);
 }
 
-// ---------------------------------------------------------------- small math
-// max of three floats in one instruction (sm_100 has a 3-input FMNMX)
-__device__ __forceinline__ float fmax3(float a, float b, float c) {
-  float r;
-  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
-  return r;
-}
-// (a.x * b + c, a.y * b + c) as one packed FMA
-__device__ __forceinline__ float2 fma2_scalar(float ax, float ay, float b, float c) {
-  unsigned long long pa, pb, pc, pr;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(pa) : "f"(ax), "f"(ay));
-  asm("mov.b64 %0, {%1, %1};" : "=l"(pb) : "f"(b));
-  asm("mov.b64 %0, {%1, %1};" : "=l"(pc) : "f"(c));
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(pr) : "l"(pa), "l"(pb), "l"(pc));
-  float2 r;
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(pr));
-  return r;
-}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
