@@ -48,6 +48,16 @@ def test_python_api_rejects_cpu_tensors(built_lib):
         api.union_qm(torch.zeros((4, 64), dtype=torch.int64), 2)
 
 
+def test_host_buffer_entry_validates_without_a_gpu(built_lib):
+    import torch
+    from litetopk_b200 import api
+    q = torch.zeros((4, 64, 576), dtype=torch.bfloat16)
+    idx = torch.zeros((4, 64), dtype=torch.int32)
+    kv_cpu = torch.zeros((128, 576), dtype=torch.uint8)
+    with pytest.raises(ValueError, match="CUDA"):          # the cache must live on a GPU: no CPU path
+        api.sparse_prefill_host(q, kv_cpu, idx, 0.1)
+
+
 def test_product_code_never_imports_the_oracle():
     for f in (ROOT / "litetopk_b200").rglob("*.py"):
         src = f.read_text()
