@@ -149,6 +149,10 @@ int litedsa_repack_kv656(const void* kv656, void* kv576, int s_kv, int64_t out_p
  *   attn_sink [128] fp32 per packed row or NULL: adds exp(sink) to the OUTPUT normaliser only
  *   out [ng, 128, 512] bf16;  lse [ng, 128] fp32 (natural log, without the sink)
  * Requires pos0 + ng * (128 / h_per_q) <= s_raw.
+ * The kernel uses all 227 KB of shared memory and needs its dynamic base within 768 bytes of
+ * a 1024-byte boundary: the first call on each device launches a one-thread probe and reads
+ * its answer back synchronously (make that call outside stream capture); when the base
+ * does not fit the call returns LITEDSA_ERR_UNSUPPORTED.
  */
 int litedsa_dsv4_c128a_bf16(const void* q, const void* kv_comp, const void* kv_raw, int ng,
                             int h_per_q, int n_comp, int s_raw, int pos0, int window, int ratio,

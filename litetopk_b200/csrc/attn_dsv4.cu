@@ -463,9 +463,10 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
 // of the CTA's window; this probe (same configuration: no static shared memory, the same
 // dynamic size) reports that offset once per device so that the host can refuse to launch
 // instead of letting the kernel give up.
-__global__ void smem_base_probe(unsigned* out) {
+__device__ unsigned g_smem_base_mod1024;
+__global__ void smem_base_probe() {
   extern __shared__ uint8_t probe_raw[];
-  if (threadIdx.x == 0) *out = smem_u32(probe_raw) & 1023u;
+  if (threadIdx.x == 0) g_smem_base_mod1024 = smem_u32(probe_raw) & 1023u;
 }
 static bool smem_alignment_ok() {
   static thread_local int cached_dev = -1;
@@ -474,16 +475,13 @@ static bool smem_alignment_ok() {
   cudaGetDevice(&dev);
   if (dev == cached_dev) return cached;
   bool ok = false;
-  unsigned* d = nullptr;
   unsigned h = 0xffffffffu;
-  if (cudaFuncSetAttribute(smem_base_probe, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) == cudaSuccess &&
-      cudaMalloc(&d, sizeof(unsigned)) == cudaSuccess) {
-    smem_base_probe<<<1, 32, kSmem>>>(d);
-    if (cudaMemcpy(&h, d, sizeof(unsigned), cudaMemcpyDeviceToHost) == cudaSuccess) {
+  if (cudaFuncSetAttribute(smem_base_probe, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) == cudaSuccess) {
+    smem_base_probe<<<1, 32, kSmem>>>();
+    if (cudaMemcpyFromSymbol(&h, g_smem_base_mod1024, sizeof(unsigned)) == cudaSuccess) {
       const unsigned pad = (1024u - h) & 1023u;
       ok = pad + kSmemUsed <= kSmem;
     }
-    cudaFree(d);
   }
   cudaGetLastError();
   cached_dev = dev; cached = ok;
