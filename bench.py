@@ -216,6 +216,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-tiles", type=int, default=32)
     ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--e2e-q", choices=("e4m3", "bf16"), default="e4m3",
+                    help="dtype of the host-resident queries of the end-to-end leg")
     ap.add_argument("--gather", choices=("auto", "fused", "ce", "nccl"), default="auto",
                     help="N > 1: how the ranks' outputs are gathered (auto: the fastest measured "
                          "form for this N: copy-engine pushes up to 4 GPUs, NCCL beyond)")
@@ -375,7 +377,11 @@ def main():
         gather_on[0] = True
 
     # ---- end to end through the public API with host buffers (rank-local), copies inside the timing
-    q_host = q.cpu().pin_memory(); idx_host = idx.cpu().pin_memory()
+    # q travels as e4m3 codes, the input dtype of the reference operator
+    # (masked_mla_fp8(q8, ...), kernels/b200/dsa/litedsa.cu:77); --e2e-q bf16 uploads bf16 queries
+    # and quantises them on the device inside the timed region instead
+    q_src = q if args.e2e_q == "bf16" else q8.view(w.tokens, w.heads, 576)
+    q_host = q_src.cpu().pin_memory(); idx_host = idx.cpu().pin_memory()
     out_host = torch.empty((w.tokens, w.heads, 512), dtype=torch.bfloat16).pin_memory()
     lse_host = torch.empty((w.tokens, w.heads), dtype=torch.float32).pin_memory()
 
@@ -398,7 +404,7 @@ def main():
         t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t[0])
-    h2d = q_host.numel() * 2 + idx_host.numel() * 4
+    h2d = q_host.numel() * q_host.element_size() + idx_host.numel() * 4
     d2h = out_host.numel() * 2 + lse_host.numel() * 4
 
     # ---- work model: 2176 FLOP per attended (query-head, key) pair; gather bytes per union row
@@ -431,7 +437,8 @@ def main():
                      "gather_bytes_per_step": union_rows * 576,
                      "gather_gbs": union_rows * 576 / (attn_ms * 1e-3) / 1e9},
         "e2e": {"value": world * w.tokens / (e2e_ms * 1e-3), "unit": "tokens/s",
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                "host_q_dtype": args.e2e_q},
         "gpu_launches": launches_per_step * args.steps,
         "gpu_launches_per_step": launches_per_step,
         "clocks": None, "cpu_baseline": None,
