@@ -40,8 +40,9 @@ constexpr unsigned kIdleSleepNs = 8;       // back-off of an idle poll
 
 
 constexpr int kSoftmaxWarps = 8, kProducerWarps = 8;
-constexpr int kWarpMma = 16, kWarpCopy = 17, kWarpRelay = 18, kWarpValid = 19;
-constexpr int kAttnThreads = 640;
+constexpr int kWarpMma = 16, kWarpCopy = 17, kWarpRelay = 18, kWarpValid = 19, kWarpEpi0 = 20;
+constexpr int kEpiWarps = 4;
+constexpr int kAttnThreads = 768;
 constexpr int kBlockKeys = 128;                      // keys per softmax block (whole pair)
 constexpr int kDQK = 576, kDV = 512;
 constexpr int kChunks = 5;                           // 128-byte column chunks per row
@@ -161,7 +162,7 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
   if (threadIdx.x == 0) {
     mbar_init(&ms.q_full, 1);
     mbar_init(&ms.q_free, 1);
-    mbar_init(&ms.o_free, 2 * kProducerWarps);
+    mbar_init(&ms.o_free, 2 * kEpiWarps);
     mbar_init(&ms.epi_ready, kSoftmaxWarps);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&ms.k_peer[i], 1);
@@ -413,22 +414,9 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         c.nb = c.tile < p.ng ? blocks_of(tile_count(c.tile)) : 0;
       }
     };
-    Cursor ck, cv, ce;   // K gather, V gather, epilogue
+    Cursor ck, cv;   // K gather, V gather
     cur_init(ck);
     cur_init(cv);
-    cur_init(ce);
-    // Epilogue duty: gather warp pw reads the TMEM lanes of its quarter (warp % 4), i.e. rows
-    // r of key half h, dims [256h + 128(pw / 4), +128), 32 dims (64 bytes) per round.  A round
-    // is staged in the warp's own 2 KB slice (32 rows x 64 bytes, 64-byte swizzle: the 16-byte
-    // stores of eight consecutive rows hit distinct banks) and one lane hands the box to TMA:
-    // full-sector asynchronous writes, no barrier wider than the warp.
-    const int e_tl = ((warp & 3) << 5) | lane, e_r = e_tl & 63, e_h = e_tl >> 6, e_g = pw >> 2;
-    const uint32_t e_stage = kOffStage + pw * 2048;
-    uint8_t* e_st_row = sm + e_stage + (e_r & 31) * 64;
-    const int e_sw = (e_r >> 1) & 3;
-    const uint32_t e_ocol = tmem + ((uint32_t)((warp & 3) * 32) << 16) + kTmemO + e_g * 128;
-    const uint32_t a_o_free = mapa(smem_u32(&ms.o_free), 0);
-    int e_round = 0;
     // the KV cache is re-read by every tile (keep it in L2); q and out stream through once
     const uint64_t pol_keep = l2_policy_evict_last(), pol_stream = l2_policy_evict_first();
     // lane l < 16 holds the index of own key 8pw + l%8 (K tile rows), lane l >= 16 of key
@@ -447,64 +435,8 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
     unsigned long long idle_since = 0;
     unsigned idle_iters = 0;
     bool aborted = false;
-    while ((ck.tile < p.ng || cv.tile < p.ng || ce.tile < p.ng || (pw == 0 && q_tile < p.ng)) && !aborted) {
+    while ((ck.tile < p.ng || cv.tile < p.ng || (pw == 0 && q_tile < p.ng)) && !aborted) {
       bool did = false;
-      if (ce.tile < p.ng) {
-        const int kbl = ce.kb0 + ce.nb - 1;          // last block of the tile
-        // the row scales are published and the tile's last PV has completed
-        const bool ok = e_round > 0 || (mbar_test(&ms.epi_ready, ce.it & 1) &&
-                                        mbar_test(&ms.pv_done[kbl & 1], (kbl >> 1) & 1));
-        if (__all_sync(0xffffffffu, ok)) {
-          if (kDebug) ts_on = ts != nullptr && (ce.tile == p.ng / 2) && lane == 0;
-          if (pw == 0) LT_TS(3, 1 + e_round, 0);
-          const float oscale = ms.oscale[ce.it & 1][e_r];
-          const uint32_t emask = oscale != 0.f ? 0xffffffffu : 0u;
-          float o[32];
-          tc_fence_after();
-          tmem_ld32(e_ocol + e_round * 32, o);
-          tmem_wait_ld();
-          if (e_round == 3) {
-            // O has been read: the next tile's first PV may overwrite it
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(a_o_free);
-          }
-          if (kDebug && p.dbg && ce.tile == 0) {
-            float* d = p.dbg + (size_t)p.cap * 128 + (size_t)((int)cta * 64 + e_r) * 512 + 256 * e_h +
-                       128 * e_g + e_round * 32;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) d[j] = o[j];
-          }
-          uint32_t w[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            __nv_bfloat162 v2 = __floats2bfloat162_rn(o[2 * j] * oscale, o[2 * j + 1] * oscale);
-            w[j] = *reinterpret_cast<uint32_t*>(&v2) & emask;    // rows without a valid key: zeros
-          }
-          // the previous round's box must have been read out of the slice
-          if (lane == 0) bulk_wait_read_all();
-          __syncwarp();
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            *reinterpret_cast<uint4*>(e_st_row + ((j ^ e_sw) << 4)) =
-                make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            for (int d = 0; d < p.n_out; ++d)
-              tma_store_2d_hint(&omaps.m[d], sbase + e_stage, 256 * e_h + 128 * e_g + 32 * e_round,
-                                ce.tile * 128 + (int)cta * 64 + 32 * (warp & 1), pol_stream);
-            bulk_commit_group();
-          }
-          if (pw == 0) LT_TS(3, 1 + e_round, 1);
-          if (++e_round == 4) {
-            e_round = 0;
-            ce.k = ce.nb - 1;
-            cur_next(ce);
-          }
-          did = true;
-        }
-      }
       if (pw == 0 && q_tile < p.ng) {
         // the previous tile's Q must have been consumed by its last QK^T
         const bool okq = q_it == 0 || mbar_test(&ms.q_free, (q_it - 1) & 1);
@@ -593,7 +525,6 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         aborted = __any_sync(0xffffffffu, stop);
       }
     }
-    if (lane == 0) bulk_wait_all();   // output boxes written before the CTA retires
   } else {
    if (warp == kWarpMma) {
     // ------------------------------------------------------------ MMA issue (leader CTA only)
@@ -693,6 +624,81 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         kb0 += nb;
       }
     }
+  } else if (warp >= kWarpEpi0) {
+    // ------------------------------------------------------------ epilogue warps
+    // O out of TMEM, x out_scale / l, bf16, TMA tile stores -- while the softmax warps already
+    // work on the next tile.  A warp reads the TMEM lanes of its quarter (warp % 4): rows r of
+    // key half h, dims [256h, 256h + 256) in 8 rounds of 32 dims (64 bytes per row).  A round
+    // is staged in one of the warp's two 2 KB slices (32 rows x 64 bytes, 64-byte swizzle: the
+    // 16-byte stores of eight consecutive rows hit distinct banks) and one lane hands the box
+    // to TMA: full-sector asynchronous writes, no barrier wider than the warp.
+    const int ew = warp - kWarpEpi0;
+    const int e_tl = ((warp & 3) << 5) | lane, e_r = e_tl & 63, e_h = e_tl >> 6;
+    const int e_sw = (e_r >> 1) & 3;
+    const uint32_t e_ocol = tmem + ((uint32_t)((warp & 3) * 32) << 16) + kTmemO;
+    const uint32_t a_o_free = mapa(smem_u32(&ms.o_free), 0);
+    const uint64_t pol_stream = l2_policy_evict_first();
+    int kb0 = 0, it = 0;
+    for (int tile = cid; tile < p.ng; tile += ncl, ++it) {
+      const int nb = blocks_of(tile_count(tile));
+      const int kbl = kb0 + nb - 1;                // last block of the tile
+      if (kDebug) ts_on = ts != nullptr && (tile == p.ng / 2) && lane == 0;
+      // the row scales are published and the tile's last PV has completed
+      mbar_wait(&ms.epi_ready, it & 1, status, kSiteEpi, it);
+      mbar_wait(&ms.pv_done[kbl & 1], (kbl >> 1) & 1, status, kSiteEpi, nb);
+      tc_fence_after();
+      if (ew == 0) LT_TS(3, 1, 0);
+      const float oscale = ms.oscale[it & 1][e_r];
+      const uint32_t emask = oscale != 0.f ? 0xffffffffu : 0u;
+      const int out_y = tile * 128 + (int)cta * 64 + 32 * (warp & 1);
+      float ob[2][32];
+      tmem_ld32(e_ocol, ob[0]);
+#pragma unroll
+      for (int cc = 0; cc < 8; ++cc) {
+        float* o = ob[cc & 1];
+        tmem_wait_ld();
+        if (cc < 7) {
+          tmem_ld32(e_ocol + (cc + 1) * 32, ob[(cc + 1) & 1]);
+        } else {
+          // O has been read: the next tile's first PV may overwrite it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(a_o_free);
+          if (ew == 0) LT_TS(3, 1, 1);
+        }
+        if (kDebug && p.dbg && tile == 0) {
+          float* d = p.dbg + (size_t)p.cap * 128 + (size_t)((int)cta * 64 + e_r) * 512 + 256 * e_h + cc * 32;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) d[j] = o[j];
+        }
+        uint32_t w[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          __nv_bfloat162 v2 = __floats2bfloat162_rn(o[2 * j] * oscale, o[2 * j + 1] * oscale);
+          w[j] = *reinterpret_cast<uint32_t*>(&v2) & emask;    // rows without a valid key: zeros
+        }
+        // two slices per warp: the box sent two rounds ago must have been read out
+        if (lane == 0) bulk_wait_read_1();
+        __syncwarp();
+        const uint32_t slice = kOffStage + (uint32_t)(ew * 2 + (cc & 1)) * 2048;
+        uint8_t* st_row = sm + slice + (e_r & 31) * 64;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          *reinterpret_cast<uint4*>(st_row + ((j ^ e_sw) << 4)) =
+              make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          for (int d = 0; d < p.n_out; ++d)
+            tma_store_2d_hint(&omaps.m[d], sbase + slice, 256 * e_h + 32 * cc, out_y, pol_stream);
+          bulk_commit_group();
+        }
+      }
+      if (ew == 0) LT_TS(3, 1, 2);
+      kb0 += nb;
+    }
+    if (lane == 0) bulk_wait_all();   // output boxes written before the CTA retires
+    tc_fence_before();
   } else if (warp == kWarpCopy || warp == kWarpRelay) {
     // ------------------------------------------------------------ "landed" relays to the leader CTA
     // The MMA thread lives in the leader CTA and can only wait on its own barriers: in the
