@@ -15,17 +15,18 @@
 //     each CTA owns 64 query rows.  Both GEMMs are single tcgen05 cta_group::2 instructions
 //     spanning the pair: QK^T splits the 128 keys of a block across the CTAs (N split), PV
 //     splits the 512 value dims (N split).
-//   * 20 warps per CTA:
+//   * 24 warps per CTA:
 //       warps 0-7   softmax, two groups of four warps on alternate key blocks (one TMEM lane
 //                   per thread, 64 S columns each);
 //       warps 8-15  KV row gather with 16-byte cp.async copies written straight into the
 //                   128-byte-swizzled tile layout (K: own 64 keys x 576 bytes; V: all 128 keys
-//                   x this CTA's 256 value bytes), the Q tile (TMA), and the tile epilogue:
-//                   O out of TMEM, x out_scale / l, bf16, staged per warp and written with
-//                   TMA tile stores while the softmax warps already work on the next tile;
+//                   x this CTA's 256 value bytes) and the Q tile (TMA);
 //       warp 16     MMA issue (leader CTA; whole warp polls, one elected lane issues);
 //       warps 17-18 relay "K / V landed" from the peer CTA to the leader's barriers;
-//       warp 19     index-validity bits.
+//       warp 19     index-validity bits;
+//       warps 20-23 tile epilogue: O out of TMEM, x out_scale / l, bf16, staged per warp and
+//                   written with TMA tile stores while the softmax warps already work on the
+//                   next tile.
 //   * K tiles are five 128-byte-swizzled column chunks per 64 keys (the fifth holds the 64
 //     rope bytes, its other half kept zero), V tiles two MN-major chunks per 128 keys.
 //   * completion is tracked with mbarriers only; every wait is bounded (common.cuh) and
