@@ -62,3 +62,39 @@ def test_product_code_never_imports_the_oracle():
     for f in (ROOT / "litetopk_b200").rglob("*.py"):
         src = f.read_text()
         assert not re.search(r"^\s*(from|import)\s+oracle\b", src, flags=re.M), f
+
+
+def test_entry_points_reject_bad_arguments_before_any_cuda_call(built_lib):
+    # argument and shape rules are checked on the host first, so these calls need no GPU;
+    # the pointers are fake but never dereferenced
+    from litetopk_b200 import _lib
+    L = built_lib
+    P = 0x1000        # 16-byte aligned non-null
+    ARG, SHAPE, UNSUP = _lib.ERR_ARG, _lib.ERR_SHAPE, _lib.ERR_UNSUPPORTED
+    # union: null output, T != ng * G, cap not a multiple of 128, k not a multiple of 4
+    assert L.litedsa_union_qm(P, None, P, P, None, None, 4, 64, 2, 128, 2, 0, 0, 1, 1024, 0, None) == ARG
+    assert L.litedsa_union_qm(P, P, P, P, None, None, 5, 64, 2, 128, 2, 0, 0, 1, 1024, 0, None) == SHAPE
+    assert L.litedsa_union_qm(P, P, P, P, None, None, 4, 50, 2, 100, 2, 0, 0, 1, 1024, 0, None) == SHAPE
+    assert L.litedsa_union_qm(P, P, P, P, None, None, 128, 2, 1, 256, 128, 0, 0, 1, 1024, 0, None) == SHAPE
+    # attention: null q, topk not a multiple of 128, heads not dividing 128, misaligned base
+    ok = dict(sm=0.1, os=1.0)
+    assert L.litedsa_masked_mla_fp8(None, P, P, ok["sm"], ok["os"], None, P, 64, P, None, P,
+                                    2, 128, 128, 576, 576, 128, None, None) == ARG
+    assert L.litedsa_masked_mla_fp8(P, P, P, ok["sm"], ok["os"], None, P, 64, P, None, P,
+                                    2, 128, 100, 576, 576, 128, None, None) == SHAPE
+    assert L.litedsa_masked_mla_fp8(P, P, P, ok["sm"], ok["os"], None, P, 48, P, None, P,
+                                    2, 128, 128, 576, 576, 128, None, None) == SHAPE
+    assert L.litedsa_masked_mla_fp8(P + 8, P, P, ok["sm"], ok["os"], None, P, 64, P, None, P,
+                                    2, 128, 128, 576, 576, 128, None, None) == UNSUP
+    # multi-destination form: destination count out of range, null destination
+    outs = (ctypes.c_void_p * 9)(*([P] * 9))
+    assert L.litedsa_masked_mla_fp8_multi(P, P, P, ok["sm"], ok["os"], None, P, 64, outs, 9, None, P,
+                                          2, 128, 128, 576, 576, 128, None) == SHAPE
+    outs2 = (ctypes.c_void_p * 2)(P, None)
+    assert L.litedsa_masked_mla_fp8_multi(P, P, P, ok["sm"], ok["os"], None, P, 64, outs2, 2, None, P,
+                                          2, 128, 128, 576, 576, 128, None) == ARG
+    # DSv4: queries outside the cache, heads not dividing 128
+    assert L.litedsa_dsv4_c128a_bf16(P, None, P, 4, 64, 0, 4, 0, 128, 128, 0.1, None, P, P,
+                                     576, 576, 576, None) == SHAPE
+    assert L.litedsa_dsv4_c128a_bf16(P, None, P, 1, 48, 0, 64, 0, 128, 128, 0.1, None, P, P,
+                                     576, 576, 576, None) == SHAPE
