@@ -1,6 +1,7 @@
 """Two ranks on two GPUs: the attention kernel's epilogue writes each rank's outputs into
-both ranks' gathered buffers (peer-mapped symmetric memory); the gathered result must be
-bit-identical with one GPU computing every tile.  Skipped with fewer than two GPUs."""
+both ranks' gathered buffers (peer-mapped symmetric memory), and the copy-engine form pushes
+chunks to the peer; either way the gathered result must be bit-identical with one GPU
+computing every tile.  Skipped with fewer than two GPUs."""
 import os
 import socket
 
@@ -60,6 +61,16 @@ def _worker(rank, world, port):
         got = pg.gathered().reshape(ng, 128, 512)
         assert torch.equal(got, want), f"rank {rank}: gathered output differs"
         assert torch.equal(lse, lse_all[lo:hi])
+        # the copy-engine form: chunks computed locally, pushed to the peer on side streams
+        pg.gathered().zero_()
+        torch.cuda.synchronize()
+        dist.barrier()
+        ldist.copy_engine_sharded_attention(
+            lambda a, b, dst: api.masked_mla_fp8_out(q8t[lo + a:lo + b], kv8, u[lo + a:lo + b], sm, ks,
+                                                     c[lo + a:lo + b], m[lo + a:lo + b], w.heads, dst,
+                                                     None, lse[a:b]), pg, n_chunks=3)
+        torch.cuda.synchronize()
+        assert torch.equal(pg.gathered().reshape(ng, 128, 512), want), f"rank {rank}: copy-engine gather differs"
         assert api.attn_status()[0] == 0
         dist.barrier()
     finally:
