@@ -678,21 +678,26 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
           __nv_bfloat162 v2 = __floats2bfloat162_rn(o[2 * j] * oscale, o[2 * j + 1] * oscale);
           w[j] = *reinterpret_cast<uint32_t*>(&v2) & emask;    // rows without a valid key: zeros
         }
-        // two slices per warp: the box sent two rounds ago must have been read out
-        if (lane == 0) bulk_wait_read_1();
-        __syncwarp();
-        const uint32_t slice = kOffStage + (uint32_t)(ew * 2 + (cc & 1)) * 2048;
-        uint8_t* st_row = sm + slice + (e_r & 31) * 64;
+        // two rounds make one box of 32 rows x 128 bytes (128-byte swizzle) in the warp's 4 KB
+        // slice; before the first of them the previous box must have been read out
+        if ((cc & 1) == 0) {
+          if (lane == 0) bulk_wait_read_all();
+          __syncwarp();
+        }
+        const uint32_t slice = kOffStage + (uint32_t)ew * 4096;
+        uint8_t* st_row = sm + slice + (e_r & 31) * 128;
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          *reinterpret_cast<uint4*>(st_row + ((j ^ e_sw) << 4)) =
+          *reinterpret_cast<uint4*>(st_row + (((4 * (cc & 1) + j) ^ (e_r & 7)) << 4)) =
               make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          for (int d = 0; d < p.n_out; ++d)
-            tma_store_2d_hint(&omaps.m[d], sbase + slice, 256 * e_h + 32 * cc, out_y, pol_stream);
-          bulk_commit_group();
+        if (cc & 1) {
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            for (int d = 0; d < p.n_out; ++d)
+              tma_store_2d_hint(&omaps.m[d], sbase + slice, 256 * e_h + 64 * (cc >> 1), out_y, pol_stream);
+            bulk_commit_group();
+          }
         }
       }
       if (ew == 0) LT_TS(3, 1, 2);
@@ -794,7 +799,7 @@ static int launch_fp8(const void* q8, const void* kv8, const int32_t* indices, f
   // out is stored as boxes of 32 rows x 32 dims (64 bytes wide, 64-byte swizzle)
   for (int d = 0; d < kMaxOutputs; ++d)
     if (!make_map_2d(&omaps.m[d], outs[d < n_out ? d : 0], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, kDV,
-                     (uint64_t)ng * 128, (uint64_t)kDV * 2, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B))
+                     (uint64_t)ng * 128, (uint64_t)kDV * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B))
       return LITEDSA_ERR_CUDA;
   if (!make_map_2d(&map_q, q8, CU_TENSOR_MAP_DATA_TYPE_UINT8, kDQK, (uint64_t)ng * 128,
                    (uint64_t)q_row_stride, 128, 64))
