@@ -59,7 +59,7 @@ constexpr uint32_t kOffV = kOffK + 2 * kKStage;
 constexpr uint32_t kOffP = kOffV + 2 * kVStage;
 constexpr uint32_t kOffMisc = kOffP + 2 * kPBytes;   // 204800
 constexpr uint32_t kMiscBytes = 7168;
-constexpr uint32_t kOffStage = kOffMisc + kMiscBytes;  // 8 x 2 KB output staging slices
+constexpr uint32_t kOffStage = kOffMisc + kMiscBytes;  // 4 x 4 KB output staging slices (epilogue warps)
 constexpr uint32_t kStageBytes = 8 * 2048;
 constexpr uint32_t kAttnSmem = kOffStage + kStageBytes + 1024;  // + alignment slack
 static_assert(kAttnSmem <= 232448, "shared-memory plan exceeds the 227 KB per-CTA limit");
@@ -629,13 +629,12 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
     // ------------------------------------------------------------ epilogue warps
     // O out of TMEM, x out_scale / l, bf16, TMA tile stores -- while the softmax warps already
     // work on the next tile.  A warp reads the TMEM lanes of its quarter (warp % 4): rows r of
-    // key half h, dims [256h, 256h + 256) in 8 rounds of 32 dims (64 bytes per row).  A round
-    // is staged in one of the warp's two 2 KB slices (32 rows x 64 bytes, 64-byte swizzle: the
-    // 16-byte stores of eight consecutive rows hit distinct banks) and one lane hands the box
-    // to TMA: full-sector asynchronous writes, no barrier wider than the warp.
+    // key half h, dims [256h, 256h + 256) in 8 rounds of 32 dims.  Two rounds are staged as one
+    // box of 32 rows x 128 bytes in the warp's 4 KB slice (128-byte swizzle: the 16-byte stores
+    // of eight consecutive rows hit distinct banks) and one lane hands the box to TMA:
+    // full-line asynchronous writes, no barrier wider than the warp.
     const int ew = warp - kWarpEpi0;
     const int e_tl = ((warp & 3) << 5) | lane, e_r = e_tl & 63, e_h = e_tl >> 6;
-    const int e_sw = (e_r >> 1) & 3;
     const uint32_t e_ocol = tmem + ((uint32_t)((warp & 3) * 32) << 16) + kTmemO;
     const uint32_t a_o_free = mapa(smem_u32(&ms.o_free), 0);
     const uint64_t pol_stream = l2_policy_evict_first();
@@ -796,7 +795,7 @@ static int launch_fp8(const void* q8, const void* kv8, const int32_t* indices, f
                       float* dbg, cudaStream_t stream) {
   CUtensorMap map_q;
   OutMaps omaps;
-  // out is stored as boxes of 32 rows x 32 dims (64 bytes wide, 64-byte swizzle)
+  // out is stored as boxes of 32 rows x 64 dims (128 bytes wide, 128-byte swizzle)
   for (int d = 0; d < kMaxOutputs; ++d)
     if (!make_map_2d(&omaps.m[d], outs[d < n_out ? d : 0], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, kDV,
                      (uint64_t)ng * 128, (uint64_t)kDV * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B))
