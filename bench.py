@@ -40,7 +40,7 @@ from litetopk_b200 import synth  # noqa: E402
 METRIC = "sparse_mla_prefill_query_tokens_per_s"
 # DRAM bytes per launch of masked_mla_fp8_kernel on the benchmark workload, from the ncu
 # capture summarised in profiles/masked_mla_fp8_kernel_c1_2048tok.md (scaled to 8192 tokens)
-ATTN_DRAM_TRAFFIC_BYTES = 721_000_000  # 194.4 MB captured on 2048 tokens, q/out/index part scaled x4
+ATTN_DRAM_TRAFFIC_BYTES = 700_000_000  # 189.3 MB captured on 2048 tokens, q/out/index part scaled x4
 
 
 def load_peaks():
