@@ -220,8 +220,7 @@ def main():
                     help="dtype of the host-resident queries of the end-to-end leg")
     ap.add_argument("--gather", choices=("auto", "fused", "ce", "nccl"), default="auto",
                     help="N > 1: how the ranks' outputs are gathered (auto: the fastest measured "
-                         "form for this N: epilogue peer stores at 2 GPUs, copy-engine pushes at "
-                         "4, NCCL beyond)")
+                         "form for this N: epilogue peer stores up to 4 GPUs, NCCL beyond)")
     ap.add_argument("--scaling", choices=("weak", "strong"), default="weak",
                     help="N > 1: the configuration per GPU (weak) or split across the GPUs (strong)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -245,7 +244,7 @@ def main():
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     if args.gather == "auto":
-        args.gather = "fused" if world <= 2 else ("ce" if world <= 4 else "nccl")
+        args.gather = "fused" if world <= 4 else "nccl"
     if args.scaling == "strong" and world > 1:
         if w.tokens % (world * w.group):
             raise SystemExit("strong scaling needs tokens divisible by gpus x tokens-per-tile")
