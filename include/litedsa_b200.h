@@ -76,7 +76,6 @@ int litedsa_union_qm(const int32_t* topk_indices, int32_t* u_phys, int32_t* coun
  *   memb_qm  [ng, 128/h_per_q, topk/32] uint32 membership bits (bit r <=> rank r)
  *   out      [ng, 128, 512] bf16 = out_scale * softmax(sm_scale * q.k) @ kv8[:, :512]
  *   max_logits [ng, 128] fp32 (natural-log units) or NULL;  lse [ng, 128] fp32
- *   debug_dump  NULL in production (bring-up aid: raw S / O of tile 0)
  * Rules: topk % 128 == 0; h_per_q divides 128; 128 / h_per_q <= 16; bases 16-byte aligned.
  * A row with no valid key gets out = 0, lse = +inf, max_logits = -inf.
  */
@@ -84,8 +83,28 @@ int litedsa_masked_mla_fp8(const void* q8, const void* kv8, const int32_t* indic
                            float sm_scale, float out_scale, const int32_t* topk_length,
                            const uint32_t* memb_qm, int h_per_q, void* out, float* max_logits,
                            float* lse, int ng, int s_kv, int topk, int64_t q_row_stride,
-                           int64_t kv_row_stride, int64_t indices_row_stride,
-                           float* debug_dump, void* stream);
+                           int64_t kv_row_stride, int64_t indices_row_stride, void* stream);
+
+/*
+ * litedsa_masked_mla_fp8 plus the optional modes that the reference kernel's parameter
+ * block carries but its binding leaves switched off (kernels/b200/dsa/litedsa.cu:127-132):
+ *   attn_sink [128] fp32 per packed row or NULL: exp(sink) joins the OUTPUT normaliser only,
+ *            lse is unchanged (litedsa_attention_sm100.cuh:2127-2133);
+ *   topk_length_per_q [ng, 128/h_per_q] int32 or NULL: token q of a tile attends only union
+ *            ranks < its bound (a causal prefix of the ascending list); the key-block loop
+ *            runs to the LAST token's bound and topk_length is ignored; memb_qm may then be
+ *            NULL (litedsa_attention_sm100.cuh:1378-1385, 1846-1851, 1988-1996);
+ *   q_group_div >= 1: that many consecutive tiles (slices of one long union list) share ONE
+ *            Q tile, so q8 is [ng / q_group_div, 128, 576]; the outputs stay per tile and the
+ *            caller merges them with their lse (litedsa_attention_sm100.cuh:1383-1385, 1909).
+ */
+int litedsa_masked_mla_fp8_ex(const void* q8, const void* kv8, const int32_t* indices,
+                              float sm_scale, float out_scale, const int32_t* topk_length,
+                              const uint32_t* memb_qm, int h_per_q, void* out, float* max_logits,
+                              float* lse, int ng, int s_kv, int topk, int64_t q_row_stride,
+                              int64_t kv_row_stride, int64_t indices_row_stride,
+                              const float* attn_sink, const int32_t* topk_length_per_q,
+                              int q_group_div, void* stream);
 
 /*
  * litedsa_masked_mla_fp8 with the all-gather of a query-sharded multi-GPU run folded into
@@ -105,13 +124,34 @@ int litedsa_masked_mla_fp8_multi(const void* q8, const void* kv8, const int32_t*
                                  int64_t indices_row_stride, void* stream);
 
 /*
- * Synchronous read (and optional reset) of the attention kernels' device status word on
- * the current device.  out4_host[0] = first bounded wait that expired (0 = none),
- * [1] = block, [2] = loop iteration, [3] = launches completed since the last reset.
- * Returns LITEDSA_ERR_TIMEOUT when out4_host[0] != 0.  No counterpart in the reference,
+ * Synchronous read (and optional reset) of the FP8 attention kernels' device status block
+ * on the current device.  out4_host[0] = first bounded wait that expired since the last
+ * reset (0 = none), [1] = its block, [2] = its loop iteration, [3] = launches completed
+ * since the last reset.  Returns LITEDSA_ERR_TIMEOUT when out4_host[0] != 0.
+ * The record is STICKY: it stays until a call with reset != 0, so a caller that polls it
+ * after a batch of launches learns that one of them gave up (that launch's outputs are
+ * invalid).  An expired wait ends only its own launch: every launch carries its own epoch,
+ * and later launches run normally without a reset.  Entry points themselves stay
+ * asynchronous and return LITEDSA_OK at enqueue time.  No counterpart in the reference,
  * whose waits are unbounded (litedsa_attention_sm100.cuh:1965, 2371).
  */
 int litedsa_attn_status(int* out4_host, int reset);
+
+/*
+ * Limit of one device-side wait for all later launches of this process, in nanoseconds
+ * (0 restores the default, 2 s).  *previous_ns (may be NULL) receives the old value.
+ */
+int litedsa_set_wait_limit_ns(uint64_t limit_ns, uint64_t* previous_ns);
+
+/*
+ * Self-test of the bounded wait (for test suites).  Launches a one-warp kernel that waits,
+ * with the given limit (1 ns .. 1 s), on an mbarrier nobody arrives on, and synchronises.
+ * The wait must give up and the kernel return normally: *returned_device (device int32)
+ * becomes 2 (1 would mean the wait succeeded), the FP8 status block records the site, and
+ * the function returns LITEDSA_ERR_TIMEOUT -- the expected outcome.  Nothing hangs, traps
+ * or faults.  Reset the status block afterwards (litedsa_attn_status(NULL, 1)).
+ */
+int litedsa_selftest_wait_timeout(uint64_t limit_ns, int* returned_device);
 
 /*
  * out_e4m3[i] = e4m3_saturating(in_bf16[i] / scale), i < n.  n % 8 == 0, 16-byte aligned
@@ -160,8 +200,78 @@ int litedsa_dsv4_c128a_bf16(const void* q, const void* kv_comp, const void* kv_r
                             int64_t q_row_stride, int64_t kc_row_stride, int64_t kr_row_stride,
                             void* stream);
 
-/* Status word of the DSv4 kernel; same meaning and use as litedsa_attn_status. */
+/* Status block of the DSv4 kernel; same meaning and use as litedsa_attn_status. */
 int litedsa_dsv4_status(int* out4_host, int reset);
+
+/*
+ * The reference's DSv4 operator with its own argument list:
+ *   dsv4_masked_mla_bf16(q, kv, indices, pref, win_lo, win_hi, counts, sm_scale, h_per_q,
+ *                        out, lse, attn_sink)
+ * (kernels/b200/dsa/litedsa_dsv4.cu:50-121, export litedsa_dsv4_binding.cu:17-18; kernel
+ * litedsa_attention_sm100_dsv4.cuh:1849-2485), tensor shapes/strides passed as integers.
+ *
+ *   q        [ng, 128, d] bf16 (row r of a tile = token r / h_per_q, head r % h_per_q)
+ *   kv       [s_kv, d] bf16 flat workspace; V = the first 512 dims of the same rows
+ *   indices  [ng, topk] int32 rows of kv in ascending rank order (-1 / out of range = skipped)
+ *   pref, win_lo, win_hi [ng, 128/h_per_q] int32: token q of tile g attends the union ranks
+ *            r < pref  or  win_lo <= r < win_hi   (litedsa_attention_sm100_dsv4.cuh:1824-1829,
+ *            2015-2025), and only r < counts[g]
+ *   counts   [ng] int32 live entries of each tile's list
+ *   attn_sink [128] fp32 per packed row or NULL: joins the OUTPUT normaliser only
+ *   out [ng, 128, 512] bf16;  lse [ng, 128] fp32 (natural log, without the sink)
+ *   d = 512 (the reference's only width) or 576; topk % 64 == 0; strides in ELEMENTS
+ *   (q/kv: >= d, multiples of 8; indices: >= topk); q / kv / out 16-byte aligned.
+ * With d = 576 the first call on a device reads a one-thread probe back synchronously
+ * (dynamic shared-memory alignment): make that call outside stream capture.
+ */
+int litedsa_dsv4_masked_mla_bf16(const void* q, const void* kv, const int32_t* indices,
+                                 const int32_t* pref, const int32_t* win_lo,
+                                 const int32_t* win_hi, const int32_t* counts, float sm_scale,
+                                 int h_per_q, void* out, float* lse, const float* attn_sink,
+                                 int ng, int s_kv, int topk, int d, int64_t q_row_stride,
+                                 int64_t kv_row_stride, int64_t indices_row_stride, void* stream);
+
+/*
+ * masked_mla_fp8's bf16 twin for KV caches that have no single-scale all-e4m3 form (per-128
+ * scales that differ, bf16 rope -- the DeepSeek-V3.2 cache row): bf16 q and a bf16 KV
+ * workspace (see litedsa_dequant_kv656), the union list and query-major membership mask of
+ * litedsa_union_qm.  Argument order of masked_mla_fp8 (kernels/b200/dsa/litedsa.cu:77-80)
+ * without out_scale; numerics of the reference's bf16 kernel (64-key blocks, bf16 P,
+ * litedsa_attention_sm100_dsv4.cuh:2072-2083), accurate to bf16 rounding.
+ *
+ *   q [ng, 128, d] bf16, kv [s_kv, d] bf16 (d = 576 or 512; V = first 512 dims), strides in
+ *   ELEMENTS; indices [ng, topk] int32; topk_length [ng] or NULL; memb_qm [ng, G, topk/32];
+ *   out [ng, 128, 512] bf16; max_logits [ng, 128] or NULL; lse [ng, 128]; attn_sink [128] or
+ *   NULL.  topk % 128 == 0.
+ */
+int litedsa_masked_mla_bf16(const void* q, const void* kv, const int32_t* indices, float sm_scale,
+                            const int32_t* topk_length, const uint32_t* memb_qm, int h_per_q,
+                            void* out, float* max_logits, float* lse, int ng, int s_kv, int topk,
+                            int d, int64_t q_row_stride, int64_t kv_row_stride,
+                            int64_t indices_row_stride, const float* attn_sink, void* stream);
+
+/*
+ * Packed 656-byte cache rows (512 e4m3 codes | 4 fp32 per-128 scales | 64 bf16 rope) ->
+ * bf16 rows [s_kv, 576]: latent = code x the scale of its 128-dim chunk, rope copied.
+ * out_pitch = BYTES between output rows (>= 1152, multiple of 16).  The reference's bf16
+ * operator consumes such a "flat dequantised workspace" (litedsa_dsv4.cu:40-48).
+ */
+int litedsa_dequant_kv656(const void* kv656, void* kv_bf16, int s_kv, int64_t out_pitch,
+                          void* stream);
+
+/* Status block of the bf16 gather kernel; same meaning and use as litedsa_attn_status. */
+int litedsa_bf16_status(int* out4_host, int reset);
+
+/*
+ * Measurement aid: the dense tcgen05 tensor-core rate of the current device in TFLOP/s,
+ * measured by a kernel that only issues MMAs from shared memory on every SM pair
+ * (synchronous, a few milliseconds).  kind 0 = FP8 e4m3 (kind::f8f6f4), 1 = bf16
+ * (kind::f16); m_pair = 256 (128 rows per CTA of a pair: the peak shape) or 128 (64 rows
+ * per CTA: the attention kernels' shape); N = 256; iters = MMAs per pair (multiple of 8,
+ * >= 64).  *tflops_out is a HOST double.  The benchmark's FP8 roofline denominator comes
+ * from here.  No counterpart in the reference.
+ */
+int litedsa_probe_mma_tflops(int kind, int m_pair, int iters, double* tflops_out);
 
 /*
  * Masked FP8 MLA prefill from packed 656-byte cache rows WITHOUT any allocation.

@@ -4,10 +4,13 @@ for NVIDIA B200 (sm_100a), behind the reference module's operator API.
 Hand-written CUDA kernels reached through a C ABI (include/litedsa_b200.h); this package
 is the thin Python host side.  There is no CPU fallback.
 """
-from .api import (attn_status, dsv4_c128a_bf16, dsv4_status, masked_mla_fp8,  # noqa: F401
-                  masked_mla_fp8_out, quantize_e4m3,
-                  repack_kv656, sparse_prefill, union_qm, union_qm_out)
+from .api import (attn_status, bf16_status, dequant_kv656, dsv4_c128a_bf16,  # noqa: F401
+                  dsv4_masked_mla_bf16_out, dsv4_status, masked_mla_bf16_out, masked_mla_fp8,
+                  masked_mla_fp8_out, prepare_kv, quantize_e4m3, repack_kv656, sparse_prefill,
+                  sparse_prefill_host, union_qm, union_qm_out)
 from . import synth  # noqa: F401
 
-__all__ = ["union_qm", "union_qm_out", "masked_mla_fp8", "masked_mla_fp8_out", "sparse_prefill",
-           "quantize_e4m3", "repack_kv656", "attn_status", "synth"]
+__all__ = ["union_qm", "union_qm_out", "masked_mla_fp8", "masked_mla_fp8_out", "masked_mla_bf16_out",
+           "dsv4_c128a_bf16", "dsv4_masked_mla_bf16_out", "sparse_prefill", "sparse_prefill_host",
+           "prepare_kv", "quantize_e4m3", "repack_kv656", "dequant_kv656", "attn_status",
+           "bf16_status", "dsv4_status", "synth"]

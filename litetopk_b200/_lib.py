@@ -6,7 +6,7 @@ resolved, importing `lib()` raises.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_int, c_int64, c_float, c_void_p, c_char_p
+from ctypes import c_int, c_int64, c_uint64, c_float, c_void_p, c_char_p
 from pathlib import Path
 
 _PKG = Path(__file__).resolve().parent
@@ -23,13 +23,18 @@ SIGNATURES = {
                                  c_int, c_void_p]),
     "litedsa_masked_mla_fp8": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p,
                                        c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                                       c_int, c_int, c_int64, c_int64, c_int64, c_void_p,
-                                       c_void_p]),
+                                       c_int, c_int, c_int64, c_int64, c_int64, c_void_p]),
+    "litedsa_masked_mla_fp8_ex": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p,
+                                          c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                          c_int, c_int, c_int64, c_int64, c_int64, c_void_p,
+                                          c_void_p, c_int, c_void_p]),
     "litedsa_masked_mla_fp8_multi": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_float,
                                              c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
                                              c_void_p, c_int, c_int, c_int, c_int64, c_int64,
                                              c_int64, c_void_p]),
     "litedsa_attn_status": (c_int, [c_void_p, c_int]),
+    "litedsa_set_wait_limit_ns": (c_int, [c_uint64, c_void_p]),
+    "litedsa_selftest_wait_timeout": (c_int, [c_uint64, c_void_p]),
     "litedsa_quantize_e4m3": (c_int, [c_void_p, c_void_p, c_int64, c_float, c_void_p]),
     "litedsa_repack_kv656": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_float, c_void_p,
                                      c_void_p]),
@@ -41,6 +46,16 @@ SIGNATURES = {
                                         c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int64,
                                         c_int64, c_int64, c_void_p]),
     "litedsa_dsv4_status": (c_int, [c_void_p, c_int]),
+    "litedsa_dsv4_masked_mla_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                             c_void_p, c_float, c_int, c_void_p, c_void_p, c_void_p,
+                                             c_int, c_int, c_int, c_int, c_int64, c_int64, c_int64,
+                                             c_void_p]),
+    "litedsa_masked_mla_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+                                        c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                        c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+    "litedsa_dequant_kv656": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_void_p]),
+    "litedsa_bf16_status": (c_int, [c_void_p, c_int]),
+    "litedsa_probe_mma_tflops": (c_int, [c_int, c_int, c_int, c_void_p]),
 }
 
 _lib = None

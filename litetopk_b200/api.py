@@ -119,26 +119,31 @@ def union_qm(topk_idx: torch.Tensor, tokens_per_tile: int, *, seq_space: Optiona
 # --------------------------------------------------------------------------- FP8 attention
 def masked_mla_fp8_out(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, sm_scale: float,
                        out_scale: float, topk_length: Optional[torch.Tensor],
-                       memb_qm: torch.Tensor, h_per_q: int, out: torch.Tensor,
+                       memb_qm: Optional[torch.Tensor], h_per_q: int, out: torch.Tensor,
                        max_logits: Optional[torch.Tensor], lse: torch.Tensor,
-                       *, peer_outs=None, _debug_dump: Optional[torch.Tensor] = None) -> None:
+                       *, peer_outs=None, attn_sink: Optional[torch.Tensor] = None,
+                       topk_length_per_q: Optional[torch.Tensor] = None,
+                       q_group_div: int = 1) -> None:
     """Reference argument order (kernels/b200/dsa/litedsa.cu:77-80).
-
-    ``peer_outs`` (sharded multi-GPU runs): up to seven peer-mapped device addresses (ints)
-    of [ng,128,512] bf16 buffers on other GPUs that receive a copy of every output box from
-    the kernel's epilogue (see :mod:`litetopk_b200.dist`).
 
     q [ng,128,576] e4m3 (uint8 storage accepted); kv [s_kv,1,576] or [s_kv,576] e4m3, row
     pitch = kv.stride(0); indices [ng,1,topk] or [ng,topk] i32 physical slots; topk_length
     [ng] i32 (None: every tile uses topk); memb_qm [ng,G,topk/32] u32 bits; out
     [ng,128,512] bf16; max_logits [ng,128] f32 or None; lse [ng,128] f32.
     logits = sm_scale * (q . k); out = out_scale * softmax(logits) @ kv[:, :512].
+
+    Keyword extras.  ``peer_outs`` (sharded multi-GPU runs): up to seven peer-mapped device
+    addresses (ints) of [ng,128,512] bf16 buffers on other GPUs that receive a copy of every
+    output box from the kernel's epilogue (see :mod:`litetopk_b200.dist`).  The optional modes
+    of the reference kernel's parameter block (litedsa_attention_sm100.cuh:1340-1393):
+    ``attn_sink`` [128] f32 per packed row joins the output normaliser; ``topk_length_per_q``
+    [ng,G] i32 bounds each token to a causal prefix of the union ranks (memb_qm may then be
+    None); ``q_group_div`` consecutive tiles share one Q tile (q is [ng/q_group_div,128,576]).
     """
     f8 = (torch.float8_e4m3fn, torch.uint8)
     _need(q, "q", f8, 3)
     _need(kv, "kv", f8)
     _need(indices, "indices", torch.int32)
-    _need(memb_qm, "memb_qm", (torch.int32, torch.uint32))
     _need(out, "out", torch.bfloat16, 3)
     _need(lse, "lse", torch.float32)
     if kv.dim() == 3:
@@ -149,17 +154,21 @@ def masked_mla_fp8_out(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor,
         if indices.shape[1] != 1:
             raise ValueError("indices must be [ng, 1, topk]")
         indices = indices[:, 0]
-    ng, rows, d = q.shape
-    if rows != 128 or d != 576 or kv.shape[1] != 576:
-        raise ValueError("q must be [ng,128,576] and kv [s_kv,(1,)576]")
+    ng = indices.shape[0]
+    q_group_div = int(q_group_div)
+    if q_group_div < 1 or ng % q_group_div or tuple(q.shape) != (ng // q_group_div, 128, 576) \
+            or kv.shape[1] != 576:
+        raise ValueError("q must be [ng/q_group_div,128,576] and kv [s_kv,(1,)576]")
     if q.stride(2) != 1 or q.stride(1) * 128 != q.stride(0) or kv.stride(1) != 1 or indices.stride(1) != 1:
         raise ValueError("q rows must be evenly pitched; q/kv/indices need unit inner stride")
     topk = indices.shape[1]
     G = 128 // int(h_per_q)
-    if indices.shape[0] != ng:
-        raise ValueError("indices rows must match q rows")
-    if memb_qm.numel() != ng * G * (topk // 32) or not memb_qm.is_contiguous():
-        raise ValueError("memb_qm must be a contiguous [ng, G, topk/32]")
+    if memb_qm is None and topk_length_per_q is None:
+        raise ValueError("memb_qm or topk_length_per_q is required")
+    if memb_qm is not None:
+        _need(memb_qm, "memb_qm", (torch.int32, torch.uint32))
+        if memb_qm.numel() != ng * G * (topk // 32) or not memb_qm.is_contiguous():
+            raise ValueError("memb_qm must be a contiguous [ng, G, topk/32]")
     if tuple(out.shape) != (ng, 128, 512) or not out.is_contiguous():
         raise ValueError("out must be a contiguous [ng,128,512]")
     if lse.numel() != ng * 128 or not lse.is_contiguous():
@@ -172,8 +181,19 @@ def masked_mla_fp8_out(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor,
         _need(max_logits, "max_logits", torch.float32)
         if max_logits.numel() != ng * 128 or not max_logits.is_contiguous():
             raise ValueError("max_logits must be a contiguous [ng,128]")
+    if attn_sink is not None:
+        _need(attn_sink, "attn_sink", torch.float32, 1)
+        if attn_sink.shape[0] != 128 or not attn_sink.is_contiguous():
+            raise ValueError("attn_sink must be a contiguous [128] (one value per packed row)")
+    if topk_length_per_q is not None:
+        _need(topk_length_per_q, "topk_length_per_q", torch.int32, 2)
+        if tuple(topk_length_per_q.shape) != (ng, G) or not topk_length_per_q.is_contiguous():
+            raise ValueError("topk_length_per_q must be a contiguous [ng, G]")
+    extras = attn_sink is not None or topk_length_per_q is not None or q_group_div != 1
     with torch.cuda.device(q.device):
         if peer_outs:
+            if extras:
+                raise ValueError("peer_outs cannot be combined with attn_sink / topk_length_per_q / q_group_div")
             import ctypes
             ptrs = [_ptr(out)] + [int(a) for a in peer_outs]
             if len(ptrs) > 8:
@@ -184,24 +204,154 @@ def masked_mla_fp8_out(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor,
                 _ptr(topk_length), _ptr(memb_qm), int(h_per_q), arr, len(ptrs), _ptr(max_logits),
                 _ptr(lse), ng, kv.shape[0], topk, q.stride(1), kv.stride(0), indices.stride(0),
                 _stream(q))
+        elif extras:
+            rc = _lib.lib().litedsa_masked_mla_fp8_ex(
+                _ptr(q), _ptr(kv), _ptr(indices), float(sm_scale), float(out_scale),
+                _ptr(topk_length), _ptr(memb_qm), int(h_per_q), _ptr(out), _ptr(max_logits),
+                _ptr(lse), ng, kv.shape[0], topk, q.stride(1), kv.stride(0), indices.stride(0),
+                _ptr(attn_sink), _ptr(topk_length_per_q), q_group_div, _stream(q))
         else:
             rc = _lib.lib().litedsa_masked_mla_fp8(
                 _ptr(q), _ptr(kv), _ptr(indices), float(sm_scale), float(out_scale),
                 _ptr(topk_length), _ptr(memb_qm), int(h_per_q), _ptr(out), _ptr(max_logits),
                 _ptr(lse), ng, kv.shape[0], topk, q.stride(1), kv.stride(0), indices.stride(0),
-                _ptr(_debug_dump), _stream(q))
+                _stream(q))
     check(rc, "masked_mla_fp8")
 
 
-def attn_status(reset: bool = False, device=None) -> Tuple[int, int, int, int]:
-    """Synchronise and read the attention kernels' device status word:
-    (first expired wait site or 0, block, iteration, launches completed)."""
+def _bf16_common(q, kv, indices, out, lse):
+    _need(q, "q", torch.bfloat16, 3)
+    _need(kv, "kv", torch.bfloat16)
+    _need(indices, "indices", torch.int32)
+    _need(out, "out", torch.bfloat16, 3)
+    _need(lse, "lse", torch.float32)
+    if kv.dim() == 3:
+        if kv.shape[1] != 1:
+            raise ValueError("kv must be [s_kv, 1, d]")
+        kv = kv[:, 0]
+    if indices.dim() == 3:
+        if indices.shape[1] != 1:
+            raise ValueError("indices must be [ng, 1, topk]")
+        indices = indices[:, 0]
+    ng, rows, d = q.shape
+    if rows != 128 or d not in (512, 576) or kv.shape[1] != d:
+        raise ValueError("q must be [ng,128,d] and kv [s_kv,(1,)d] with d = 512 or 576")
+    if q.stride(2) != 1 or q.stride(1) * 128 != q.stride(0) or kv.stride(1) != 1 or indices.stride(1) != 1:
+        raise ValueError("q rows must be evenly pitched; q/kv/indices need unit inner stride")
+    if indices.shape[0] != ng:
+        raise ValueError("indices rows must match q tiles")
+    if tuple(out.shape) != (ng, 128, 512) or not out.is_contiguous():
+        raise ValueError("out must be a contiguous [ng,128,512]")
+    if lse.numel() != ng * 128 or not lse.is_contiguous():
+        raise ValueError("lse must be a contiguous [ng,128]")
+    return kv, indices, ng, d
+
+
+def _sink128(attn_sink):
+    if attn_sink is None:
+        return None
+    _need(attn_sink, "attn_sink", torch.float32, 1)
+    if attn_sink.shape[0] != 128 or not attn_sink.is_contiguous():
+        raise ValueError("attn_sink must be a contiguous [128] (one value per packed row)")
+    return attn_sink
+
+
+def masked_mla_bf16_out(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, sm_scale: float,
+                        topk_length: Optional[torch.Tensor], memb_qm: torch.Tensor, h_per_q: int,
+                        out: torch.Tensor, max_logits: Optional[torch.Tensor], lse: torch.Tensor,
+                        *, attn_sink: Optional[torch.Tensor] = None) -> None:
+    """bf16 twin of :func:`masked_mla_fp8_out` (same argument order without ``out_scale``):
+    q [ng,128,d] bf16, kv [s_kv,(1,)d] bf16 workspace (d = 576 or 512, V = first 512 dims),
+    union list + query-major membership mask.  For caches with no single-scale e4m3 form."""
+    kv, indices, ng, d = _bf16_common(q, kv, indices, out, lse)
+    topk = indices.shape[1]
+    G = 128 // int(h_per_q)
+    _need(memb_qm, "memb_qm", (torch.int32, torch.uint32))
+    if memb_qm.numel() != ng * G * (topk // 32) or not memb_qm.is_contiguous():
+        raise ValueError("memb_qm must be a contiguous [ng, G, topk/32]")
+    if topk_length is not None:
+        _need(topk_length, "topk_length", torch.int32, 1)
+        if topk_length.shape[0] != ng or not topk_length.is_contiguous():
+            raise ValueError("topk_length must be a contiguous [ng]")
+    if max_logits is not None:
+        _need(max_logits, "max_logits", torch.float32)
+        if max_logits.numel() != ng * 128 or not max_logits.is_contiguous():
+            raise ValueError("max_logits must be a contiguous [ng,128]")
+    with torch.cuda.device(q.device):
+        rc = _lib.lib().litedsa_masked_mla_bf16(
+            _ptr(q), _ptr(kv), _ptr(indices), float(sm_scale), _ptr(topk_length), _ptr(memb_qm),
+            int(h_per_q), _ptr(out), _ptr(max_logits), _ptr(lse), ng, kv.shape[0], topk, d,
+            q.stride(1), kv.stride(0), indices.stride(0), _ptr(_sink128(attn_sink)), _stream(q))
+    check(rc, "masked_mla_bf16")
+
+
+def dsv4_masked_mla_bf16_out(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor,
+                             pref: torch.Tensor, win_lo: torch.Tensor, win_hi: torch.Tensor,
+                             counts: torch.Tensor, sm_scale: float, h_per_q: int,
+                             out: torch.Tensor, lse: torch.Tensor,
+                             attn_sink: Optional[torch.Tensor]) -> None:
+    """The reference's DSv4 operator, same argument order
+    (kernels/b200/dsa/litedsa_dsv4.cu:50-55): q [ng,128,d] bf16, kv [s_kv,(1,)d] bf16 flat
+    workspace, indices [ng,(1,)topk] i32 ascending union rows (-1 padded, topk % 64 == 0),
+    pref / win_lo / win_hi [ng,G] i32 rank ranges per token, counts [ng] i32, out
+    [ng,128,512] bf16, lse [ng,128] f32, attn_sink [128] f32 or None.  d = 512 (the
+    reference's width) or 576."""
+    kv, indices, ng, d = _bf16_common(q, kv, indices, out, lse)
+    topk = indices.shape[1]
+    G = 128 // int(h_per_q)
+    for name, t in (("pref", pref), ("win_lo", win_lo), ("win_hi", win_hi)):
+        _need(t, name, torch.int32)
+        if t.numel() != ng * G or not t.is_contiguous():
+            raise ValueError(f"{name} must be a contiguous [ng, G]")
+    _need(counts, "counts", torch.int32, 1)
+    if counts.shape[0] != ng or not counts.is_contiguous():
+        raise ValueError("counts must be a contiguous [ng]")
+    with torch.cuda.device(q.device):
+        rc = _lib.lib().litedsa_dsv4_masked_mla_bf16(
+            _ptr(q), _ptr(kv), _ptr(indices), _ptr(pref), _ptr(win_lo), _ptr(win_hi), _ptr(counts),
+            float(sm_scale), int(h_per_q), _ptr(out), _ptr(lse), _ptr(_sink128(attn_sink)), ng,
+            kv.shape[0], topk, d, q.stride(1), kv.stride(0), indices.stride(0), _stream(q))
+    check(rc, "dsv4_masked_mla_bf16")
+
+
+def _status(fn_name: str, reset: bool, device) -> Tuple[int, int, int, int]:
     import ctypes
     buf = (ctypes.c_int * 4)()
     with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
         torch.cuda.synchronize()
-        _lib.lib().litedsa_attn_status(buf, 1 if reset else 0)
+        getattr(_lib.lib(), fn_name)(buf, 1 if reset else 0)
     return tuple(int(x) for x in buf)
+
+
+def attn_status(reset: bool = False, device=None) -> Tuple[int, int, int, int]:
+    """Synchronise and read the FP8 attention kernels' device status block: (first wait site
+    that expired since the last reset or 0, block, iteration, launches completed).  The record
+    is sticky until ``reset``; an expired wait invalidates only the launch it happened in."""
+    return _status("litedsa_attn_status", reset, device)
+
+
+def bf16_status(reset: bool = False, device=None) -> Tuple[int, int, int, int]:
+    """Status block of the bf16 gather kernel (see :func:`attn_status`)."""
+    return _status("litedsa_bf16_status", reset, device)
+
+
+def probe_mma_tflops(kind: str = "fp8", m_pair: int = 256, iters: int = 16384, device=None) -> float:
+    """Dense tcgen05 MMA rate of the device in TFLOP/s (``kind`` "fp8" or "bf16"; ``m_pair``
+    256 = peak shape, 128 = the attention kernels' 64-rows-per-CTA shape).  Synchronous."""
+    import ctypes
+    val = ctypes.c_double(0.0)
+    with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
+        check(_lib.lib().litedsa_probe_mma_tflops({"fp8": 0, "bf16": 1}[kind], int(m_pair), int(iters),
+                                                  ctypes.byref(val)), "probe_mma_tflops")
+    return float(val.value)
+
+
+def set_wait_limit_ns(limit_ns: int) -> int:
+    """Limit of one device-side wait for later launches (0 = default 2 s); returns the old value."""
+    import ctypes
+    old = ctypes.c_uint64(0)
+    check(_lib.lib().litedsa_set_wait_limit_ns(int(limit_ns), ctypes.byref(old)), "set_wait_limit_ns")
+    return int(old.value)
 
 
 # --------------------------------------------------------------------------- operand preparation
@@ -223,11 +373,14 @@ def quantize_e4m3(x: torch.Tensor, scale: float, out: Optional[torch.Tensor] = N
 
 
 def repack_kv656(kv_rows: torch.Tensor, scale: float, out: Optional[torch.Tensor] = None,
-                 *, check_scales: bool = True) -> torch.Tensor:
+                 *, check_scales: bool = False, return_flag: bool = False):
     """Packed 656-byte cache rows -> ``[s_kv, 576]`` e4m3 codes sharing the scalar ``scale``.
 
-    Raises if some per-128 scale of the cache differs from ``scale`` (checked with one
-    device->host read unless ``check_scales`` is False)."""
+    Only caches whose per-128 scales all equal ``scale`` have this form.  The kernel sets a
+    device flag when some scale differs: ``return_flag`` returns ``(out, flag)`` (flag: int32
+    [1] on the device, non-zero = mismatch; no host synchronisation), ``check_scales`` reads
+    it back (one device->host read) and raises.  Caches with differing scales go through
+    :func:`dequant_kv656` and the bf16 kernel instead."""
     _need(kv_rows, "kv_rows", torch.uint8, 2)
     if kv_rows.shape[1] != 656 or not kv_rows.is_contiguous():
         raise ValueError("kv_rows must be a contiguous [s_kv, 656] uint8 tensor")
@@ -241,27 +394,67 @@ def repack_kv656(kv_rows: torch.Tensor, scale: float, out: Optional[torch.Tensor
               "repack_kv656")
     if check_scales and int(flag.item()) != 0:
         raise ValueError("the cache has per-128 scales different from `scale`; it cannot be "
-                         "expressed with one scalar scale (use the bf16 path)")
+                         "expressed with one scalar scale (use dequant_kv656 + the bf16 path)")
+    return (out, flag) if return_flag else out
+
+
+def dequant_kv656(kv_rows: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Packed 656-byte cache rows -> bf16 ``[s_kv, 576]`` (codes x per-128 scales ‖ rope): the
+    flat workspace the bf16 kernel gathers from."""
+    _need(kv_rows, "kv_rows", torch.uint8, 2)
+    if kv_rows.shape[1] != 656 or not kv_rows.is_contiguous():
+        raise ValueError("kv_rows must be a contiguous [s_kv, 656] uint8 tensor")
+    s_kv = kv_rows.shape[0]
+    if out is None:
+        out = torch.empty((s_kv, 576), dtype=torch.bfloat16, device=kv_rows.device)
+    else:
+        _need(out, "out", torch.bfloat16, 2)
+        if tuple(out.shape) != (s_kv, 576) or out.stride(1) != 1:
+            raise ValueError("out must be [s_kv, 576] bf16 with unit inner stride")
+    with torch.cuda.device(kv_rows.device):
+        check(_lib.lib().litedsa_dequant_kv656(_ptr(kv_rows), _ptr(out), s_kv, out.stride(0) * 2,
+                                               _stream(kv_rows)), "dequant_kv656")
     return out
+
+
+def prepare_kv(kv_cache_fp8: torch.Tensor, kv_scale: Optional[float] = None,
+               *, check_scales: bool = False) -> torch.Tensor:
+    """Bring a KV cache into the form one of the attention kernels gathers from.
+
+    * ``[s_kv, 576]`` e4m3 / uint8 codes (one scalar scale) or a bf16 ``[s_kv, 576]``
+      workspace: returned as is.
+    * packed ``[s_kv, 656]`` uint8 rows with ``kv_scale`` given: the caller states that every
+      per-128 scale equals ``kv_scale`` -> repacked to ``[s_kv, 576]`` codes (FP8 kernel).
+    * packed rows with ``kv_scale`` None: per-128 scales may differ (a DeepSeek-V3.2 cache)
+      -> dequantised to a bf16 ``[s_kv, 576]`` workspace (bf16 kernel).
+    Do this once per cache and hand the result to :func:`masked_mla_fp8` / :func:`sparse_prefill`.
+    """
+    kv = kv_cache_fp8
+    if kv.dim() == 2 and kv.shape[1] == 656 and kv.dtype == torch.uint8:
+        return dequant_kv656(kv) if kv_scale is None else repack_kv656(kv, kv_scale, check_scales=check_scales)
+    return kv
 
 
 def masked_mla_fp8(q: torch.Tensor, kv_cache_fp8: torch.Tensor, union_idx: torch.Tensor,
                    mask: torch.Tensor, sm_scale: float, *, counts: Optional[torch.Tensor] = None,
-                   kv_scale: float = 1.0, q_scale: Optional[float] = None,
+                   kv_scale: Optional[float] = None, q_scale: Optional[float] = None,
                    return_max_logits: bool = False, out: Optional[torch.Tensor] = None,
                    lse: Optional[torch.Tensor] = None):
-    """Masked FP8 MLA prefill over the per-tile union; returns ``(out [T,h,512] bf16, lse [T,h] f32)``
-    (written into ``out`` / ``lse`` when given: contiguous, same shapes and dtypes).
+    """Masked MLA prefill over the per-tile union of an FP8 KV cache; returns
+    ``(out [T,h,512] bf16, lse [T,h] f32)`` (written into ``out`` / ``lse`` when given:
+    contiguous, same shapes and dtypes).
 
-    q            [T, h, 576]; bf16 (quantised here to e4m3 with the power-of-two ``q_scale``,
-                 default: the smallest one that avoids saturation) or e4m3/uint8 codes
-                 (``q_scale`` default 1).  G = 128 // h adjacent tokens form one tile.
-    kv_cache_fp8 [s_kv, 576] e4m3/uint8 codes with the scalar ``kv_scale`` (the reference
-                 module's layout), or packed [s_kv, 656] uint8 rows whose per-128 scales all
-                 equal ``kv_scale`` (repacked here).
+    q            [T, h, 576] bf16, or e4m3/uint8 codes (FP8 route only).  G = 128 // h adjacent
+                 tokens form one tile.
+    kv_cache_fp8 any form :func:`prepare_kv` accepts.  Packed 656-byte rows with ``kv_scale``
+                 None, or a bf16 workspace, take the **bf16 route** (per-128 scales may differ;
+                 bf16 tensor-core MMAs, bf16 P: accurate to bf16 rounding).  e4m3 codes, or
+                 packed rows with a stated uniform ``kv_scale``, take the **FP8 route** (the
+                 reference kernel's numerics: q, K, V and P in e4m3, fp32 accumulation).
     union_idx    [T/G, G*k] int32 and mask [T/G, G, G*k/32] from :func:`union_qm`;
-                 counts [T/G] int32 (default: entries before the -1 padding).
-    Numerics are the reference kernel's: logits and P in e4m3, fp32 accumulation.
+                 counts [T/G] int32 (default: entries before the -1 padding, one extra pass).
+    q_scale      FP8 route with bf16 q: the power-of-two quantisation scale.  When omitted it
+                 is derived from max|q| with ONE host synchronisation; pass it on a hot path.
     """
     _need(q, "q", (torch.bfloat16, torch.uint8, torch.float8_e4m3fn), 3)
     T, h, d = q.shape
@@ -271,17 +464,7 @@ def masked_mla_fp8(q: torch.Tensor, kv_cache_fp8: torch.Tensor, union_idx: torch
     if T % G:
         raise ValueError("token count must be a multiple of 128 // heads")
     ng = T // G
-    if q.dtype == torch.bfloat16:
-        if q_scale is None:
-            amax = float(q.abs().amax().item())
-            q_scale = 2.0 ** max(-24, int(torch.tensor(max(amax, 1e-30) / 448.0).log2().ceil().item()))
-        q8 = quantize_e4m3(q.contiguous(), q_scale)
-    else:
-        q8 = q.contiguous()
-        q_scale = 1.0 if q_scale is None else q_scale
-    kv = kv_cache_fp8
-    if kv.dim() == 2 and kv.shape[1] == 656:
-        kv = repack_kv656(kv, kv_scale)
+    kv = prepare_kv(kv_cache_fp8, kv_scale)
     if counts is None:
         counts = (union_idx >= 0).sum(dim=1, dtype=torch.int32)
     if out is None:
@@ -299,21 +482,37 @@ def masked_mla_fp8(q: torch.Tensor, kv_cache_fp8: torch.Tensor, union_idx: torch
             raise ValueError("lse must be a contiguous [T,h] f32 tensor")
         lse = lse.view(ng, 128)
     ml = torch.empty((ng, 128), dtype=torch.float32, device=q.device) if return_max_logits else None
-    masked_mla_fp8_out(q8.view(ng, 128, 576), kv, union_idx, float(sm_scale) * q_scale * kv_scale,
-                       kv_scale, counts, mask, h, out, ml, lse)
+    if kv.dtype == torch.bfloat16:
+        if q.dtype != torch.bfloat16:
+            raise TypeError("the bf16 route (cache with per-128 scales / bf16 workspace) needs bf16 q")
+        masked_mla_bf16_out(q.contiguous().view(ng, 128, 576), kv, union_idx, float(sm_scale), counts,
+                            mask, h, out, ml, lse)
+    else:
+        ks = 1.0 if kv_scale is None else float(kv_scale)
+        if q.dtype == torch.bfloat16:
+            if q_scale is None:      # convenience: one device->host read
+                amax = float(q.abs().amax().item())
+                q_scale = 2.0 ** max(-24, int(torch.tensor(max(amax, 1e-30) / 448.0).log2().ceil().item()))
+            q8 = quantize_e4m3(q.contiguous(), q_scale)
+        else:
+            q8 = q.contiguous()
+            q_scale = 1.0 if q_scale is None else q_scale
+        masked_mla_fp8_out(q8.view(ng, 128, 576), kv, union_idx, float(sm_scale) * q_scale * ks,
+                           ks, counts, mask, h, out, ml, lse)
     res = (out.view(T, h, 512), lse.view(T, h))
     return res + (ml.view(T, h),) if return_max_logits else res
 
 
 def sparse_prefill(q: torch.Tensor, kv_cache_fp8: torch.Tensor, topk_idx: torch.Tensor,
-                   sm_scale: float, *, kv_scale: float = 1.0, q_scale: Optional[float] = None,
-                   seq_space: Optional[int] = None, out: Optional[torch.Tensor] = None,
-                   lse: Optional[torch.Tensor] = None):
-    """The whole hot path for one chunk of query tokens: union_qm + masked_mla_fp8.
+                   sm_scale: float, *, kv_scale: Optional[float] = None,
+                   q_scale: Optional[float] = None, seq_space: Optional[int] = None,
+                   out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None):
+    """The whole hot path for one chunk of query tokens: union_qm + masked attention.
 
     q [T,h,576], topk_idx [T,k] int32, kv_cache_fp8 as in :func:`masked_mla_fp8` (already
-    resident on the device).  Returns ``(out [T,h,512] bf16, lse [T,h] f32)``, written into
-    ``out`` / ``lse`` when given.
+    resident on the device; pass the result of :func:`prepare_kv` when the same cache serves
+    several calls).  Returns ``(out [T,h,512] bf16, lse [T,h] f32)``, written into ``out`` /
+    ``lse`` when given.
     """
     h = q.shape[1]
     u, m, c = union_qm(topk_idx, 128 // h,
@@ -353,7 +552,7 @@ def _host_workspace(device, T: int, h: int, k: int, q_dtype, idx_dtype):
 
 def sparse_prefill_host(q_host: torch.Tensor, kv_cache_fp8: torch.Tensor, topk_host: torch.Tensor,
                         sm_scale: float, *, out_host: Optional[torch.Tensor] = None,
-                        lse_host: Optional[torch.Tensor] = None, kv_scale: float = 1.0,
+                        lse_host: Optional[torch.Tensor] = None, kv_scale: Optional[float] = None,
                         q_scale: Optional[float] = None, seq_space: Optional[int] = None,
                         chunk_tokens: int = 512):
     """:func:`sparse_prefill` for callers whose queries and results live in host memory.
@@ -390,9 +589,10 @@ def sparse_prefill_host(q_host: torch.Tensor, kv_cache_fp8: torch.Tensor, topk_h
         raise ValueError("out_host must be [T,h,512] bf16 and lse_host [T,h] f32")
     space = seq_space if seq_space is not None else kv_cache_fp8.shape[0]
     with torch.cuda.device(dev):
-        kv = kv_cache_fp8
-        if kv.dim() == 2 and kv.shape[1] == 656:
-            kv = repack_kv656(kv, kv_scale)
+        kv = prepare_kv(kv_cache_fp8, kv_scale)       # once per call, not per chunk
+        if kv.dtype != torch.bfloat16 and q_host.dtype == torch.bfloat16 and q_scale is None:
+            raise ValueError("bf16 queries on the FP8 route need q_scale (no host synchronisation "
+                             "happens inside the pipelined chunks)")
         qd, idd, od, ld = _host_workspace(dev, T, h, topk_host.shape[1], q_host.dtype,
                                           topk_host.dtype)
         cur = torch.cuda.current_stream(dev)

@@ -72,12 +72,15 @@ struct Params {
   const float* sink;         // [128] per packed row, or null
   int ng, n_comp, s_raw, G, h_per_q, pos0, window, ratio;
   float scale_log2;
+  int epoch;                          // this launch's epoch for the bounded waits
+  unsigned long long wait_limit_ns;
 };
 
 enum { kSiteQ = 101, kSiteKFull, kSiteVFull, kSiteQkDone, kSitePvDone, kSiteSFree, kSitePReady,
        kSiteKFree, kSiteVFree, kSitePFree, kSiteEpi, kSiteQFree, kSiteOFree, kSiteSmem };
 
-__device__ int g_status[4];
+// status block of the DSv4 kernel (layout: see Waiter in common.cuh)
+__device__ int g_status[8];
 
 // key segments of a tile: compressed blocks first, then window blocks
 struct TilePlan {
@@ -114,11 +117,11 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
   const uint32_t sbase = (raw + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (sbase - raw);
   Misc& ms = *reinterpret_cast<Misc*>(sm + kOffMisc);
-  int* status = g_status;
+  const Waiter wt{g_status, p.epoch, p.wait_limit_ns};
   // the plan leaves less than 1024 bytes for aligning the base: refuse to run (uniformly, in
   // both CTAs, before any barrier exists) if this launch's base needs more
   if ((sbase - raw) + kSmemUsed > kSmem) {
-    if (threadIdx.x == 0 && atomicCAS(status, 0, (int)kSiteSmem) == 0) status[1] = (int)blockIdx.x;
+    if (threadIdx.x == 0) wt.fail(kSiteSmem, 0);
     return;
   }
 
@@ -185,7 +188,7 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
       const int kb = kb0 + k;
       const int s = kb & 1;
       const uint32_t ph = (kb >> 1) & 1;
-      mbar_wait(&ms.qk_done[s], ph, status, kSiteQkDone, k);
+      mbar_wait(&ms.qk_done[s], ph, wt, kSiteQkDone, k);
       tc_fence_after();
       float sv[32];
       tmem_ld32(tmem + lane_base + (s ? kTmemS1 : kTmemS0), sv);
@@ -237,7 +240,7 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
       }
       // the single P buffer was last read by the PV of the previous block (of this or the
       // previous tile)
-      if (kb >= 1) mbar_wait(&ms.pv_done[(kb - 1) & 1], ((kb - 1) >> 1) & 1, status, kSitePFree, k);
+      if (kb >= 1) mbar_wait(&ms.pv_done[(kb - 1) & 1], ((kb - 1) >> 1) & 1, wt, kSitePFree, k);
       // P: [64 rows][64 keys] bf16, K-major core matrices: 8-key group cg at cg*1024 + row*16
       uint8_t* pdst = sm + kOffP + (4 * h) * 1024 + r * 16;
 #pragma unroll
@@ -295,7 +298,7 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
         const TilePlan tp = plan_tile(p, tile);
         const int nb = tp.nb;
         // the previous tile's Q must have been consumed by its last QK^T
-        if (it > 0) mbar_wait(&ms.q_free, (it - 1) & 1, status, kSiteQFree, it);
+        if (it > 0) mbar_wait(&ms.q_free, (it - 1) & 1, wt, kSiteQFree, it);
         if (cta == 0) mbar_arrive_expect_tx(&ms.q_full, 2 * kQBytes);
         for (int j = 0; j < kQChunks; ++j)
           tma_load_2d_pair(sbase + kOffQ + j * kQChunkBytes, &map_q, 64 * j, tile * 128 + (int)cta * 64,
@@ -308,13 +311,13 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
           const int row0 = comp ? k * kBlockKeys : tp.wlo + (k - tp.nbc) * kBlockKeys;
           const CUtensorMap* m32 = comp ? &map_kc32 : &map_kr32;
           const CUtensorMap* m64 = comp ? &map_kc64 : &map_kr64;
-          if (kb >= 2) mbar_wait(&ms.qk_done[s], ph ^ 1, status, kSiteKFree, k);   // K stage free
+          if (kb >= 2) mbar_wait(&ms.qk_done[s], ph ^ 1, wt, kSiteKFree, k);   // K stage free
           if (cta == 0) mbar_arrive_expect_tx(&ms.k_full[s], 2 * kKStage);
           for (int j = 0; j < kQChunks; ++j)
             tma_load_2d_pair(sbase + kOffK + s * kKStage + j * kKChunkBytes, m32, 64 * j,
                              row0 + 32 * (int)cta, a_k_full[s]);
           // V stage s was last read by the PV of block kb-2
-          if (kb >= 2) mbar_wait(&ms.pv_done[s], ph ^ 1, status, kSiteVFree, k);
+          if (kb >= 2) mbar_wait(&ms.pv_done[s], ph ^ 1, wt, kSiteVFree, k);
           if (cta == 0) mbar_arrive_expect_tx(&ms.v_full[s], 2 * kVStage);
           for (int j = 0; j < 4; ++j)
             tma_load_2d_pair(sbase + kOffV + s * kVStage + j * kVChunkBytes, m64,
@@ -341,8 +344,8 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
     for (int tile = cid; tile < p.ng; tile += ncl, ++it) {
       const int nb = plan_tile(p, tile).nb;
       const int kbl = kb0 + nb - 1;                 // last block of the tile
-      mbar_wait(&ms.epi_ready, it & 1, status, kSiteEpi, it);
-      mbar_wait(&ms.pv_done[kbl & 1], (kbl >> 1) & 1, status, kSiteEpi, nb);
+      mbar_wait(&ms.epi_ready, it & 1, wt, kSiteEpi, it);
+      mbar_wait(&ms.pv_done[kbl & 1], (kbl >> 1) & 1, wt, kSiteEpi, nb);
       tc_fence_after();
       const float oscale = ms.oscale[it & 1][r];
       const uint32_t emask = oscale != 0.f ? 0xffffffffu : 0u;
@@ -395,15 +398,15 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
     int kb0 = 0, it = 0;
     for (int tile = cid; tile < p.ng; tile += ncl, ++it) {
       const int nb = plan_tile(p, tile).nb;
-      mbar_wait(&ms.q_full, it & 1, status, kSiteQ, it);
+      mbar_wait(&ms.q_full, it & 1, wt, kSiteQ, it);
       __syncwarp();
       for (int k = 0; k <= nb; ++k) {
         if (k < nb) {
           const int kb = kb0 + k;
           const int s = kb & 1;
           const uint32_t ph = (kb >> 1) & 1;
-          mbar_wait(&ms.k_full[s], ph, status, kSiteKFull, k);
-          if (kb >= 2) mbar_wait(&ms.s_free[s], ph ^ 1, status, kSiteSFree, k);
+          mbar_wait(&ms.k_full[s], ph, wt, kSiteKFull, k);
+          if (kb >= 2) mbar_wait(&ms.s_free[s], ph ^ 1, wt, kSiteSFree, k);
           __syncwarp();
           tc_fence_after();
           const uint32_t d = tmem + (s ? kTmemS1 : kTmemS0);
@@ -427,10 +430,10 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
         if (k > 0) {
           const int kl = k - 1, kb = kb0 + kl;
           const int s = kb & 1;
-          mbar_wait(&ms.p_ready, kb & 1, status, kSitePReady, kl);
-          mbar_wait(&ms.v_full[s], (kb >> 1) & 1, status, kSiteVFull, kl);
+          mbar_wait(&ms.p_ready, kb & 1, wt, kSitePReady, kl);
+          mbar_wait(&ms.v_full[s], (kb >> 1) & 1, wt, kSiteVFull, kl);
           // the tile's first PV overwrites O: the previous tile must have read it out
-          if (kl == 0 && it > 0) mbar_wait(&ms.o_free, (it - 1) & 1, status, kSiteOFree, it);
+          if (kl == 0 && it > 0) mbar_wait(&ms.o_free, (it - 1) & 1, wt, kSiteOFree, it);
           __syncwarp();
           tc_fence_after();
           const uint64_t ad0 = umma_desc(sbase + kOffP, 1024, 128, kSwzNone);
@@ -455,7 +458,7 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
   __syncwarp();
   cluster_sync_all();
   if (warp == 5) tmem_dealloc_pair(tmem, kTmemCols);
-  if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&status[3], 1);
+  if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&g_status[3], 1);
 }
 
 // The kernel's shared-memory plan leaves 768 bytes for aligning its tiles to 1024 bytes.
@@ -559,6 +562,7 @@ extern "C" int litedsa_dsv4_c128a_bf16(const void* q, const void* kv_comp, const
   p.out = reinterpret_cast<__nv_bfloat16*>(out); p.lse = lse; p.sink = attn_sink;
   p.ng = ng; p.n_comp = n_comp; p.s_raw = s_raw; p.G = G; p.h_per_q = h_per_q; p.pos0 = pos0;
   p.window = window; p.ratio = ratio; p.scale_log2 = sm_scale * kLog2e;
+  p.epoch = next_launch_epoch(); p.wait_limit_ns = wait_limit_ns();
   if (!smem_alignment_ok()) return LITEDSA_ERR_UNSUPPORTED;   // first call per device: synchronous probe
   if (cudaFuncSetAttribute(dsv4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) !=
       cudaSuccess)
@@ -574,7 +578,7 @@ extern "C" int litedsa_dsv4_status(int* out4_host, int reset) {
   if (out4_host && cudaMemcpyFromSymbol(out4_host, g_status, sizeof(int) * 4) != cudaSuccess)
     return LITEDSA_ERR_CUDA;
   if (reset) {
-    const int z[4] = {0, 0, 0, 0};
+    const int z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if (cudaMemcpyToSymbol(g_status, z, sizeof(z)) != cudaSuccess) return LITEDSA_ERR_CUDA;
   }
   return (out4_host && out4_host[0] != 0) ? LITEDSA_ERR_TIMEOUT : LITEDSA_OK;

@@ -101,7 +101,10 @@ constexpr int kMaxOutputs = 8;
 struct OutMaps { CUtensorMap m[kMaxOutputs]; };
 
 struct AttnParams {
-  const uint32_t* memb;      // [ng, G, cap/32]
+  const uint32_t* memb;      // [ng, G, cap/32], or null when len_per_q replaces it
+  const int32_t* len_per_q;  // [ng, G] per-token causal prefix bound on the union ranks, or null
+  const float* sink;         // [128] per packed row (natural-log units), or null
+  int q_group_div;           // this many consecutive tiles share one Q tile (KV split)
   const uint8_t* kv;         // [s_kv, kv_pitch] e4m3 rows (576 bytes used)
   long long kv_pitch;        // bytes between KV rows
   const int32_t* indices;    // [ng, idx_stride]
@@ -109,30 +112,22 @@ struct AttnParams {
   __nv_bfloat16* out;        // [ng, 128, 512]
   float* lse;                // [ng, 128]
   float* max_logits;         // [ng, 128] or null
-  float* dbg;                // debug dump or null
   int ng, s_kv, cap, h_per_q, G;
   int n_out;                 // destinations of every output box (1 + peers that hold a copy)
   long long idx_stride;
   float scale_log2, out_scale;
+  int epoch;                          // this launch's epoch for the bounded waits
+  unsigned long long wait_limit_ns;
 };
 
 // wait sites reported in the status word
 enum { kSiteQ = 1, kSiteKLand, kSiteKPeer, kSiteVLand, kSiteVPeer, kSiteQkDone, kSitePvDone,
        kSiteSFree, kSitePReady, kSiteValidReady, kSiteValidFree, kSiteKFree, kSiteKCopied,
-       kSiteVFree, kSitePFree, kSiteEpi, kSiteRelayK, kSiteRelayV, kSiteMPub, kSiteMmaIdle, kSiteQFree, kSiteOFree };
+       kSiteVFree, kSitePFree, kSiteEpi, kSiteRelayK, kSiteRelayV, kSiteMPub, kSiteMmaIdle, kSiteQFree, kSiteOFree, kSiteSelfTest };
 
-// status[0] first failing wait site, [1] block, [2] iteration, [3] launches completed
-__device__ int g_attn_status[4];
+// status block of the FP8 attention kernels (layout: see Waiter in common.cuh)
+__device__ int g_attn_status[8];
 
-// bring-up aid: time stamps of one tile's roles (role 0 softmax thread 0, 1 gather warp 0,
-// 2 MMA warp, 3 tile hand-over and epilogue rounds), 8 slots per block, written after the S/O dump
-#define LT_TS(role, k, slot)                                                              \
-  do {                                                                                    \
-    if (kDebug && ts_on && (k) < 64)                                                      \
-      ts[((((role) + 5 * (int)cta) * 64 + (k)) << 3) + (slot)] = (long long)globaltimer_ns(); \
-  } while (0)
-
-template <bool kDebug>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kAttnThreads, 1)
 masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
                       const __grid_constant__ OutMaps omaps, const AttnParams p) {
@@ -141,7 +136,7 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
   const uint32_t sbase = (raw + 1023u) & ~1023u;       // 128B-swizzle tiles need 1024-byte alignment
   uint8_t* sm = smem_raw + (sbase - raw);
   Misc& ms = *reinterpret_cast<Misc*>(sm + kOffMisc);
-  int* status = g_attn_status;
+  const Waiter wt{g_attn_status, p.epoch, p.wait_limit_ns};
 
   // Persistent: each cluster walks tiles cid, cid + #clusters, ...  Every role runs the same
   // tile loop; stages, buffers and barrier phases are indexed by the cluster-wide running
@@ -151,14 +146,14 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
   const int cid = blockIdx.x >> 1, ncl = gridDim.x >> 1;
   // broadcast so the compiler knows the role index is warp-uniform
   const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
+  // live union entries of a tile; with per-token prefix bounds the block loop runs to the LAST
+  // token's bound (litedsa_attention_sm100.cuh:1846-1851)
   auto tile_count = [&](int tile) -> int {
-    const int c = p.counts ? p.counts[tile] : p.cap;
+    const int c = p.len_per_q ? p.len_per_q[(size_t)tile * p.G + (p.G - 1)]
+                              : (p.counts ? p.counts[tile] : p.cap);
     return min(max(c, 0), p.cap);
   };
   auto blocks_of = [&](int count) -> int { return max((count + kBlockKeys - 1) / kBlockKeys, 1); };
-  long long* ts = nullptr;
-  bool ts_on = false;
-  if (kDebug && p.dbg) ts = reinterpret_cast<long long*>(p.dbg + (size_t)p.cap * 128 + 128 * 512 + 256);
 
   if (threadIdx.x == 0) {
     mbar_init(&ms.q_full, 1);
@@ -216,23 +211,23 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
 
     for (int tile = cid; tile < p.ng; tile += ncl) {
       const int nb = blocks_of(tile_count(tile));
-      if (kDebug) ts_on = ts != nullptr && (tile == p.ng / 2) && lane == 0;
-      const uint32_t* mrow = p.memb + ((size_t)tile * p.G + row / p.h_per_q) * capw + 2 * h;
+      const size_t trow = (size_t)tile * p.G + row / p.h_per_q;     // (tile, token) of this row
+      const uint32_t* mrow = p.memb ? p.memb + trow * capw + 2 * h : nullptr;
+      // per-token causal prefix: this row may attend union ranks < row_bound
+      const int row_bound = p.len_per_q ? __ldg(p.len_per_q + trow) : 0x7fffffff;
       float m_mine = kMInit;      // the running max my row sum is relative to
       float li = 0.f, real_m = -INFINITY;
       const int k_first = (g - kb0) & 1;          // first local block with (kb0 + k) % 2 == g
-      uint2 mk = make_uint2(0u, 0u);
-      if (k_first < nb) mk = __ldg(reinterpret_cast<const uint2*>(mrow + (size_t)k_first * 4));
+      uint2 mk = make_uint2(~0u, ~0u);
+      if (mrow && k_first < nb) mk = __ldg(reinterpret_cast<const uint2*>(mrow + (size_t)k_first * 4));
 
       for (int k = k_first; k < nb; k += 2) {
         const int kb = kb0 + k;
         const uint32_t ph = (kb >> 1) & 1;
         uint2 mk_next = mk;
-        if (k + 2 < nb) mk_next = __ldg(reinterpret_cast<const uint2*>(mrow + (size_t)(k + 2) * 4));
+        if (mrow && k + 2 < nb) mk_next = __ldg(reinterpret_cast<const uint2*>(mrow + (size_t)(k + 2) * 4));
 
-        if ((warp & 3) == 0) LT_TS(0, k, 0);
-        mbar_wait(&ms.qk_done[g], ph, status, kSiteQkDone, k);
-        if ((warp & 3) == 0) LT_TS(0, k, 1);
+        mbar_wait(&ms.qk_done[g], ph, wt, kSiteQkDone, k);
         tc_fence_after();
         float sv[64];
         tmem_ld32(scol, sv);
@@ -242,18 +237,17 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(a_s_free);
 
-        if (kDebug && p.dbg && tile == 0) {
-          float* d = p.dbg + ((size_t)k * 128 + row) * 128 + 64 * h;
-#pragma unroll
-          for (int j = 0; j < 64; ++j) d[j] = sv[j];
+        mbar_wait(&ms.valid_ready[g], ph, wt, kSiteValidReady, k);
+        uint32_t v0 = ms.valid[g][2 * h] & mk.x, v1 = ms.valid[g][2 * h + 1] & mk.y;
+        if (p.len_per_q) {     // ranks of my 64 columns: [128k + 64h, +64)
+          const int n = min(max(row_bound - (k * kBlockKeys + 64 * h), 0), 64);
+          const unsigned long long pm = n >= 64 ? ~0ull : ((1ull << n) - 1ull);
+          v0 &= (uint32_t)pm;
+          v1 &= (uint32_t)(pm >> 32);
         }
-
-        mbar_wait(&ms.valid_ready[g], ph, status, kSiteValidReady, k);
-        const uint32_t v0 = ms.valid[g][2 * h] & mk.x, v1 = ms.valid[g][2 * h + 1] & mk.y;
         __syncwarp();
         if (lane == 0) mbar_arrive(&ms.valid_free[g]);
         mk = mk_next;
-        if ((warp & 3) == 0) LT_TS(0, k, 2);
 
         float cur = -INFINITY;
 #pragma unroll
@@ -268,12 +262,11 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         if (g == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
         else asm volatile("bar.sync 2, 128;" ::: "memory");
         cur = fmaxf(cur, xb[tl ^ 64]);
-        if ((warp & 3) == 0) LT_TS(0, k, 3);
         real_m = fmaxf(real_m, cur);
         // running max after block k-1 of this tile comes from the other group
         float m_prev = kMInit;
         if (k > 0) {
-          mbar_wait(&ms.m_pub[g ^ 1], ((kb - 1) >> 1) & 1, status, kSiteMPub, k);
+          mbar_wait(&ms.m_pub[g ^ 1], ((kb - 1) >> 1) & 1, wt, kSiteMPub, k);
           m_prev = ms.mshare[g ^ 1][tl];
         }
         const bool rescale = __any_sync(0xffffffffu, cur - m_prev > kRescaleThreshold);
@@ -283,7 +276,6 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         if (lane == 0) mbar_arrive(&ms.m_pub[g]);
         li *= fast_exp2(m_mine - new_m);
         m_mine = new_m;
-        if ((warp & 3) == 0) LT_TS(0, k, 4);
 
         const float nm = -new_m + kPScaleLog2;
         uint32_t pk[16];
@@ -300,9 +292,8 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
           const uint32_t hi = __nv_cvt_float2_to_fp8x2(d1, __NV_SATFINITE, __NV_E4M3);
           pk[j >> 2] = lo | (hi << 16);
         }
-        if ((warp & 3) == 0) LT_TS(0, k, 5);
         // P buffer g was last read by the PV of block kb-2
-        if (kb >= 2) mbar_wait(&ms.pv_done[g], ph ^ 1, status, kSitePFree, k);
+        if (kb >= 2) mbar_wait(&ms.pv_done[g], ph ^ 1, wt, kSitePFree, k);
         uint8_t* pdst = sm + kOffP + g * kPBytes + (4 * h) * 1024 + r * 16;
 #pragma unroll
         for (int i = 0; i < 4; ++i)
@@ -311,7 +302,7 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
 
         if (rescale && k > 0) {
           // O holds blocks [0, k) relative to m_prev: bring it to new_m once PV(k-1) is complete
-          mbar_wait(&ms.pv_done[g ^ 1], ((kb - 1) >> 1) & 1, status, kSitePvDone, k);
+          mbar_wait(&ms.pv_done[g ^ 1], ((kb - 1) >> 1) & 1, wt, kSitePvDone, k);
           tc_fence_after();
           const float f = fast_exp2(m_prev - new_m);
           float o[32];
@@ -327,16 +318,13 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
           tmem_wait_st();
           tc_fence_before();
         }
-        if ((warp & 3) == 0) LT_TS(0, k, 6);
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(a_p_ready);
-        if ((warp & 3) == 0) LT_TS(0, k, 7);
       }
 
       // end of tile: merge the two groups' row sums (each relative to its own latest running max)
       const int t = threadIdx.x;                    // 0..255 = g*128 + tl
-      if (warp == 0) LT_TS(3, 0, 0);
       ms.fin[0][t] = li;
       ms.fin[1][t] = real_m;
       ms.fin[2][t] = m_mine;
@@ -370,15 +358,14 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
       }
       // Hand the tile over to the gather warps, which read O out of TMEM, scale it and store
       // it while these warps already work on the next tile: all they need is 1 / l per row.
-      if (g == 0 && h == 0) ms.oscale[it & 1][r] = (li > 0.f) ? __fdividef(p.out_scale, li) : 0.f;
+      if (g == 0 && h == 0) {
+        // the sink joins the OUTPUT normaliser only (in l's units: x 7, relative to m)
+        float denom = li;
+        if (p.sink != nullptr && li > 0.f) denom += fast_exp2(__ldg(p.sink + row) * kLog2e - m + kPScaleLog2);
+        ms.oscale[it & 1][r] = (li > 0.f) ? __fdividef(p.out_scale, denom) : 0.f;
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(&ms.epi_ready);
-      if (warp == 0) LT_TS(3, 0, 1);
-      if (kDebug && p.dbg && tile == 0 && g == 0 && h == 0) {
-        float* d = p.dbg + (size_t)p.cap * 128 + 128 * 512;
-        d[row] = m;
-        d[128 + row] = li;
-      }
       kb0 += nb;
       ++it;
     }
@@ -446,7 +433,7 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
             if (cta == 0) mbar_arrive_expect_tx(&ms.q_full, 2 * kQBytes);
             for (int j = 0; j < kChunks; ++j)
               tma_load_2d_pair_hint(sbase + kOffQ + j * kChunkBytes, &map_q, 128 * j,
-                                    q_tile * 128 + (int)cta * 64, a_q_full, pol_stream);
+                                    (q_tile / p.q_group_div) * 128 + (int)cta * 64, a_q_full, pol_stream);
           }
           __syncwarp();
           q_tile += ncl;
@@ -455,14 +442,12 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         }
       }
       if (ck.tile < p.ng) {
-        if (kDebug) ts_on = ts != nullptr && (ck.tile == p.ng / 2) && lane == 0;
         const int kb = ck.kb0 + ck.k;
         const int s = kb & 1;
         const uint32_t ph = (kb >> 1) & 1;
         // stage s held block kb-2: its QK^T must have read it
         const bool ok = kb < 2 || mbar_test(&ms.qk_done[s], ph ^ 1);
         if (__all_sync(0xffffffffu, ok)) {
-          if (pw == 0) LT_TS(1, ck.k, 1);
           const uint32_t kst = sbase + kOffK + s * kKStage;
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
@@ -478,7 +463,6 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
                        kvb + (size_t)ri * pitch + 512 + 16 * (lane & 3), pol_keep);
           }
           cp_async_mbar_arrive_noinc(&ms.k_land[s]);
-          if (pw == 0) LT_TS(1, ck.k, 2);
           cur_next(ck);
           if (ck.tile < p.ng) kidx = load_idx(ck);
           did = true;
@@ -518,9 +502,9 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         // the (slow) time-limit and abort check runs once per kIdleCheckEvery idle polls
         const unsigned long long now = globaltimer_ns();
         if (idle_since == 0) idle_since = now;
-        bool stop = *reinterpret_cast<volatile int*>(status) != 0;
-        if (now - idle_since > kWaitLimitNs) {
-          if (lane == 0 && atomicCAS(status, 0, (int)kSiteKFree) == 0) { status[1] = (int)blockIdx.x; status[2] = ck.k; }
+        bool stop = wt.aborting();
+        if (now - idle_since > wt.limit_ns) {
+          if (lane == 0) wt.fail(kSiteKFree, ck.k);
           stop = true;
         }
         aborted = __any_sync(0xffffffffu, stop);
@@ -536,9 +520,11 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
       const uint32_t a_pv_done_peer[2] = {mapa(smem_u32(&ms.pv_done[0]), 1), mapa(smem_u32(&ms.pv_done[1]), 1)};
       const uint32_t a_q_free_peer = mapa(smem_u32(&ms.q_free), 1);
       // S = Q K^T of block kb into S buffer kb%2
+      // The K / V tiles were written by cp.async (generic proxy) and are read by the tensor core
+      // through the async proxy: a cross-proxy fence sits between "landed" and the MMA.
       auto issue_qk = [&](int k, int kb) {
         const int s = kb & 1;
-        LT_TS(2, k, 2);
+        fence_proxy_async_smem();
         tc_fence_after();
         const uint32_t d = tmem + (s ? kTmemS1 : kTmemS0);
         const uint64_t ad = umma_desc(sbase + kOffQ, 16, 1024, kSwz128);
@@ -547,11 +533,10 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
                          (uint32_t)(bd >> 32));
         mma_commit_pair_elect(smem_u32(&ms.qk_done[s]));
         mma_commit_pair_elect(a_qk_done_peer[s]);
-        LT_TS(2, k, 3);
       };
       auto issue_pv = [&](int k, int kb) {
         const int s = kb & 1;
-        LT_TS(2, k, 6);
+        fence_proxy_async_smem();
         tc_fence_after();
         const uint64_t ad = umma_desc(sbase + kOffP + s * kPBytes, 1024, 128, kSwzNone);
         const uint64_t bd = umma_desc(sbase + kOffV + s * kVStage, kVChunk, 1024, kSwz128);
@@ -559,14 +544,12 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
                         (uint32_t)(bd >> 32), k ? 1u : 0u);
         mma_commit_pair_elect(smem_u32(&ms.pv_done[s]));
         mma_commit_pair_elect(a_pv_done_peer[s]);
-        LT_TS(2, k, 7);
       };
       int kb0 = 0, it = 0;
       bool aborted = false;
       for (int tile = cid; tile < p.ng && !aborted; tile += ncl, ++it) {
         const int nb = blocks_of(tile_count(tile));
-        if (kDebug) ts_on = ts != nullptr && (tile == p.ng / 2) && lane == 0;
-        mbar_wait(&ms.q_full, it & 1, status, kSiteQ, it);
+        mbar_wait(&ms.q_full, it & 1, wt, kSiteQ, it);
         __syncwarp();
         // Ready-driven issue: whichever of "next QK" (its K stage landed on both CTAs and its S
         // buffer drained) and "next PV" (its P written, its V stage landed on both CTAs, and for
@@ -614,9 +597,9 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
           } else {
             const unsigned long long now = globaltimer_ns();
             if (idle_since == 0) idle_since = now;
-            bool stop = *reinterpret_cast<volatile int*>(status) != 0;
-            if (now - idle_since > kWaitLimitNs) {
-              if (lane == 0 && atomicCAS(status, 0, (int)kSiteMmaIdle) == 0) { status[1] = (int)blockIdx.x; status[2] = pv_i; }
+            bool stop = wt.aborting();
+            if (now - idle_since > wt.limit_ns) {
+              if (lane == 0) wt.fail(kSiteMmaIdle, pv_i);
               stop = true;
             }
             aborted = __any_sync(0xffffffffu, stop);
@@ -642,12 +625,10 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
     for (int tile = cid; tile < p.ng; tile += ncl, ++it) {
       const int nb = blocks_of(tile_count(tile));
       const int kbl = kb0 + nb - 1;                // last block of the tile
-      if (kDebug) ts_on = ts != nullptr && (tile == p.ng / 2) && lane == 0;
       // the row scales are published and the tile's last PV has completed
-      mbar_wait(&ms.epi_ready, it & 1, status, kSiteEpi, it);
-      mbar_wait(&ms.pv_done[kbl & 1], (kbl >> 1) & 1, status, kSiteEpi, nb);
+      mbar_wait(&ms.epi_ready, it & 1, wt, kSiteEpi, it);
+      mbar_wait(&ms.pv_done[kbl & 1], (kbl >> 1) & 1, wt, kSiteEpi, nb);
       tc_fence_after();
-      if (ew == 0) LT_TS(3, 1, 0);
       const float oscale = ms.oscale[it & 1][e_r];
       const uint32_t emask = oscale != 0.f ? 0xffffffffu : 0u;
       const int out_y = tile * 128 + (int)cta * 64 + 32 * (warp & 1);
@@ -664,12 +645,6 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(a_o_free);
-          if (ew == 0) LT_TS(3, 1, 1);
-        }
-        if (kDebug && p.dbg && tile == 0) {
-          float* d = p.dbg + (size_t)p.cap * 128 + (size_t)((int)cta * 64 + e_r) * 512 + 256 * e_h + cc * 32;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) d[j] = o[j];
         }
         uint32_t w[16];
 #pragma unroll
@@ -699,7 +674,6 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
           }
         }
       }
-      if (ew == 0) LT_TS(3, 1, 2);
       kb0 += nb;
     }
     if (lane == 0) bulk_wait_all();   // output boxes written before the CTA retires
@@ -719,7 +693,8 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
           const int kb = kb0 + k;
           const int s = kb & 1;
           const uint32_t ph = (kb >> 1) & 1;
-          mbar_wait(is_k ? &ms.k_land[s] : &ms.v_land[s], ph, status, is_k ? kSiteRelayK : kSiteRelayV, k);
+          mbar_wait(is_k ? &ms.k_land[s] : &ms.v_land[s], ph, wt, is_k ? kSiteRelayK : kSiteRelayV, k);
+          fence_proxy_async_smem();     // this CTA's cp.async writes -> the leader's MMA reads
           if (lane == 0) mbar_arrive_cluster_release(a_peer[s]);
         }
         kb0 += nb;
@@ -745,7 +720,7 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         };
         const uint32_t nib = ok(cur.x, rank0) | (ok(cur.y, rank0 + 1) << 1) |
                              (ok(cur.z, rank0 + 2) << 2) | (ok(cur.w, rank0 + 3) << 3);
-        if (kb >= 2) mbar_wait(&ms.valid_free[s], ph ^ 1, status, kSiteValidFree, k);
+        if (kb >= 2) mbar_wait(&ms.valid_free[s], ph ^ 1, wt, kSiteValidFree, k);
         const uint32_t nib_hi = __shfl_down_sync(0xffffffffu, nib, 1);
         if ((lane & 1) == 0)
           reinterpret_cast<uint8_t*>(&ms.valid[s][0])[lane >> 1] = (uint8_t)(nib | (nib_hi << 4));
@@ -763,7 +738,7 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
   __syncwarp();
   cluster_sync_all();
   if (warp == kWarpMma) tmem_dealloc_pair(tmem, kTmemCols);
-  if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&status[3], 1);
+  if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&g_attn_status[3], 1);
 }
 
 // how many 2-CTA clusters of this kernel the current device can hold at once
@@ -780,43 +755,71 @@ static int max_clusters() {
   cudaLaunchAttribute at; at.id = cudaLaunchAttributeClusterDimension; at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
   cfg.attrs = &at; cfg.numAttrs = 1;
   int q = 0;
-  if (cudaFuncSetAttribute(masked_mla_fp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem) == cudaSuccess &&
-      cudaOccupancyMaxActiveClusters(&q, masked_mla_fp8_kernel<false>, &cfg) == cudaSuccess && q > 0)
+  if (cudaFuncSetAttribute(masked_mla_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem) == cudaSuccess &&
+      cudaOccupancyMaxActiveClusters(&q, masked_mla_fp8_kernel, &cfg) == cudaSuccess && q > 0)
     n = q;
   cudaGetLastError();
   cached_dev = dev; cached = n;
   return n;
 }
 
-static int launch_fp8(const void* q8, const void* kv8, const int32_t* indices, float sm_scale,
-                      float out_scale, const int32_t* counts, const uint32_t* memb, int h_per_q,
-                      void* const* outs, int n_out, float* max_logits, float* lse, int ng, int s_kv, int topk,
-                      long long q_row_stride, long long kv_row_stride, long long idx_row_stride,
-                      float* dbg, cudaStream_t stream) {
+static int launch_fp8(const Fp8Args& a, void* const* outs, int n_out, cudaStream_t stream) {
   CUtensorMap map_q;
   OutMaps omaps;
-  // out is stored as boxes of 32 rows x 64 dims (128 bytes wide, 128-byte swizzle)
-  for (int d = 0; d < kMaxOutputs; ++d)
-    if (!make_map_2d(&omaps.m[d], outs[d < n_out ? d : 0], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, kDV,
-                     (uint64_t)ng * 128, (uint64_t)kDV * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B))
+  // out is stored as boxes of 32 rows x 64 dims (128 bytes wide, 128-byte swizzle); only the
+  // destinations in use are encoded, the unused slots repeat the first map
+  for (int d = 0; d < n_out; ++d)
+    if (!make_map_2d(&omaps.m[d], outs[d], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, kDV,
+                     (uint64_t)a.ng * 128, (uint64_t)kDV * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B))
       return LITEDSA_ERR_CUDA;
-  if (!make_map_2d(&map_q, q8, CU_TENSOR_MAP_DATA_TYPE_UINT8, kDQK, (uint64_t)ng * 128,
-                   (uint64_t)q_row_stride, 128, 64))
+  for (int d = n_out; d < kMaxOutputs; ++d) omaps.m[d] = omaps.m[0];
+  const int qdiv = a.q_group_div > 0 ? a.q_group_div : 1;
+  if (!make_map_2d(&map_q, a.q8, CU_TENSOR_MAP_DATA_TYPE_UINT8, kDQK,
+                   (uint64_t)(a.ng / qdiv) * 128, (uint64_t)a.q_row_stride, 128, 64))
     return LITEDSA_ERR_CUDA;
   AttnParams p;
-  p.memb = memb; p.indices = indices; p.counts = counts;
-  p.kv = reinterpret_cast<const uint8_t*>(kv8); p.kv_pitch = kv_row_stride;
-  p.out = reinterpret_cast<__nv_bfloat16*>(outs[0]); p.n_out = n_out; p.lse = lse; p.max_logits = max_logits;
-  p.dbg = dbg;
-  p.ng = ng; p.s_kv = s_kv; p.cap = topk; p.h_per_q = h_per_q; p.G = 128 / h_per_q;
-  p.idx_stride = idx_row_stride;
-  p.scale_log2 = sm_scale * kLog2e; p.out_scale = out_scale;
-  auto kern = dbg ? masked_mla_fp8_kernel<true> : masked_mla_fp8_kernel<false>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem) !=
-      cudaSuccess)
+  p.memb = a.memb_qm; p.len_per_q = a.topk_length_per_q; p.sink = a.attn_sink; p.q_group_div = qdiv;
+  p.indices = a.indices; p.counts = a.topk_length;
+  p.kv = reinterpret_cast<const uint8_t*>(a.kv8); p.kv_pitch = a.kv_row_stride;
+  p.out = reinterpret_cast<__nv_bfloat16*>(outs[0]); p.n_out = n_out; p.lse = a.lse;
+  p.max_logits = a.max_logits;
+  p.ng = a.ng; p.s_kv = a.s_kv; p.cap = a.topk; p.h_per_q = a.h_per_q; p.G = 128 / a.h_per_q;
+  p.idx_stride = a.indices_row_stride;
+  p.scale_log2 = a.sm_scale * kLog2e; p.out_scale = a.out_scale;
+  p.epoch = next_launch_epoch(); p.wait_limit_ns = wait_limit_ns();
+  if (cudaFuncSetAttribute(masked_mla_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)kAttnSmem) != cudaSuccess)
     return LITEDSA_ERR_CUDA;
-  kern<<<2 * min(ng, max_clusters()), kAttnThreads, kAttnSmem, stream>>>(map_q, omaps, p);
+  masked_mla_fp8_kernel<<<2 * min(a.ng, max_clusters()), kAttnThreads, kAttnSmem, stream>>>(map_q, omaps, p);
   return cudaGetLastError() == cudaSuccess ? LITEDSA_OK : LITEDSA_ERR_CUDA;
+}
+
+// Host-side argument rules shared by every FP8 attention entry point: the reference
+// launcher's shape rules (kernels/b200/dsa/litedsa.cu:82-98) plus the alignment TMA needs.
+// No CUDA call is made here.
+int check_fp8_args(const Fp8Args& a) {
+  if (!a.q8 || !a.kv8 || !a.indices || !a.lse) return LITEDSA_ERR_ARG;
+  if (!a.memb_qm && !a.topk_length_per_q) return LITEDSA_ERR_ARG;   // one of the two masks
+  if (a.ng <= 0 || a.s_kv <= 0 || a.topk <= 0 || a.topk % 128 != 0) return LITEDSA_ERR_SHAPE;
+  if (a.h_per_q <= 0 || 128 % a.h_per_q != 0 || 128 / a.h_per_q > 16) return LITEDSA_ERR_SHAPE;
+  if (a.q_group_div < 1 || a.ng % a.q_group_div != 0) return LITEDSA_ERR_SHAPE;
+  // TMA needs 16-byte aligned bases and row pitches
+  if (a.q_row_stride < kDQK || a.kv_row_stride < kDQK || a.q_row_stride % 16 || a.kv_row_stride % 16)
+    return LITEDSA_ERR_UNSUPPORTED;
+  if (((uintptr_t)a.q8 | (uintptr_t)a.kv8 | (uintptr_t)a.indices) & 15) return LITEDSA_ERR_UNSUPPORTED;
+  if (a.indices_row_stride < a.topk || a.indices_row_stride % 4) return LITEDSA_ERR_UNSUPPORTED;
+  return LITEDSA_OK;
+}
+
+int run_fp8(const Fp8Args& a, void* const* outs, int n_outs, void* stream) {
+  int rc = check_fp8_args(a);
+  if (rc != LITEDSA_OK) return rc;
+  if (!outs || n_outs < 1 || n_outs > kMaxOutputs) return n_outs < 1 || n_outs > kMaxOutputs ? LITEDSA_ERR_SHAPE : LITEDSA_ERR_ARG;
+  for (int d = 0; d < n_outs; ++d) {
+    if (!outs[d]) return LITEDSA_ERR_ARG;
+    if ((uintptr_t)outs[d] & 15) return LITEDSA_ERR_UNSUPPORTED;
+  }
+  return launch_fp8(a, outs, n_outs, reinterpret_cast<cudaStream_t>(stream));
 }
 
 }  // namespace lt
@@ -831,22 +834,35 @@ extern "C" int litedsa_masked_mla_fp8(const void* q8, const void* kv8, const int
                                       int h_per_q, void* out, float* max_logits, float* lse,
                                       int ng, int s_kv, int topk, int64_t q_row_stride,
                                       int64_t kv_row_stride, int64_t indices_row_stride,
-                                      float* debug_dump, void* stream) {
+                                      void* stream) {
   using namespace lt;
-  if (!q8 || !kv8 || !indices || !memb_qm || !out || !lse) return LITEDSA_ERR_ARG;
-  // shape rules of the reference launcher (litedsa.cu:82-98)
-  if (ng <= 0 || s_kv <= 0 || topk <= 0 || topk % 128 != 0) return LITEDSA_ERR_SHAPE;
-  if (h_per_q <= 0 || 128 % h_per_q != 0 || 128 / h_per_q > 16) return LITEDSA_ERR_SHAPE;
-  // TMA needs 16-byte aligned bases and row pitches
-  if (q_row_stride < kDQK || kv_row_stride < kDQK || q_row_stride % 16 || kv_row_stride % 16)
-    return LITEDSA_ERR_UNSUPPORTED;
-  if (((uintptr_t)q8 | (uintptr_t)kv8 | (uintptr_t)indices | (uintptr_t)out) & 15)
-    return LITEDSA_ERR_UNSUPPORTED;
-  if (indices_row_stride < topk || indices_row_stride % 4) return LITEDSA_ERR_UNSUPPORTED;
+  if (!memb_qm || !out) return LITEDSA_ERR_ARG;
+  Fp8Args a{q8, kv8, indices, sm_scale, out_scale, topk_length, memb_qm, h_per_q, max_logits, lse,
+            ng, s_kv, topk, q_row_stride, kv_row_stride, indices_row_stride, nullptr, nullptr, 1};
   void* outs[1] = {out};
-  return launch_fp8(q8, kv8, indices, sm_scale, out_scale, topk_length, memb_qm, h_per_q, outs, 1,
-                    max_logits, lse, ng, s_kv, topk, q_row_stride, kv_row_stride,
-                    indices_row_stride, debug_dump, reinterpret_cast<cudaStream_t>(stream));
+  return run_fp8(a, outs, 1, stream);
+}
+
+// The operator with the optional modes of the reference kernel's parameter block that its
+// binding leaves switched off (litedsa.cu:127-132): attn_sink [128] per packed row joins the
+// output normaliser (litedsa_attention_sm100.cuh:2127-2133); topk_length_per_q [ng, G] bounds
+// each token to a causal prefix of the union ranks and may replace memb_qm (:1378-1385,
+// :1988-1996); q_group_div consecutive tiles share one Q tile (KV split, :1383-1385, :1909).
+extern "C" int litedsa_masked_mla_fp8_ex(const void* q8, const void* kv8, const int32_t* indices,
+                                         float sm_scale, float out_scale,
+                                         const int32_t* topk_length, const uint32_t* memb_qm,
+                                         int h_per_q, void* out, float* max_logits, float* lse,
+                                         int ng, int s_kv, int topk, int64_t q_row_stride,
+                                         int64_t kv_row_stride, int64_t indices_row_stride,
+                                         const float* attn_sink, const int32_t* topk_length_per_q,
+                                         int q_group_div, void* stream) {
+  using namespace lt;
+  if (!out) return LITEDSA_ERR_ARG;
+  Fp8Args a{q8, kv8, indices, sm_scale, out_scale, topk_length, memb_qm, h_per_q, max_logits, lse,
+            ng, s_kv, topk, q_row_stride, kv_row_stride, indices_row_stride, attn_sink,
+            topk_length_per_q, q_group_div};
+  void* outs[1] = {out};
+  return run_fp8(a, outs, 1, stream);
 }
 
 // The same operator with the all-gather of a sharded run folded into its epilogue: every
@@ -861,35 +877,51 @@ extern "C" int litedsa_masked_mla_fp8_multi(const void* q8, const void* kv8, con
                                             int topk, int64_t q_row_stride, int64_t kv_row_stride,
                                             int64_t indices_row_stride, void* stream) {
   using namespace lt;
-  if (!q8 || !kv8 || !indices || !memb_qm || !outs || !lse) return LITEDSA_ERR_ARG;
-  if (n_outs < 1 || n_outs > kMaxOutputs) return LITEDSA_ERR_SHAPE;
-  if (ng <= 0 || s_kv <= 0 || topk <= 0 || topk % 128 != 0) return LITEDSA_ERR_SHAPE;
-  if (h_per_q <= 0 || 128 % h_per_q != 0 || 128 / h_per_q > 16) return LITEDSA_ERR_SHAPE;
-  if (q_row_stride < kDQK || kv_row_stride < kDQK || q_row_stride % 16 || kv_row_stride % 16)
-    return LITEDSA_ERR_UNSUPPORTED;
-  uintptr_t bits = (uintptr_t)q8 | (uintptr_t)kv8 | (uintptr_t)indices;
-  for (int d = 0; d < n_outs; ++d) {
-    if (!outs[d]) return LITEDSA_ERR_ARG;
-    bits |= (uintptr_t)outs[d];
-  }
-  if (bits & 15) return LITEDSA_ERR_UNSUPPORTED;
-  if (indices_row_stride < topk || indices_row_stride % 4) return LITEDSA_ERR_UNSUPPORTED;
-  return launch_fp8(q8, kv8, indices, sm_scale, out_scale, topk_length, memb_qm, h_per_q, outs,
-                    n_outs, max_logits, lse, ng, s_kv, topk, q_row_stride, kv_row_stride,
-                    indices_row_stride, nullptr, reinterpret_cast<cudaStream_t>(stream));
+  if (!memb_qm || !outs) return LITEDSA_ERR_ARG;
+  Fp8Args a{q8, kv8, indices, sm_scale, out_scale, topk_length, memb_qm, h_per_q, max_logits, lse,
+            ng, s_kv, topk, q_row_stride, kv_row_stride, indices_row_stride, nullptr, nullptr, 1};
+  return run_fp8(a, outs, n_outs, stream);
 }
 
-// Synchronous read (and optional reset) of the device status word of the attention
-// kernels on the current device: out[0] = first wait site that expired (0 = none),
-// out[1] = block, out[2] = iteration, out[3] = launches completed since the last reset.
+// Synchronous read (and optional reset) of the device status block of the FP8 attention
+// kernels on the current device: out[0] = first wait site that expired since the last reset
+// (0 = none), out[1] = block, out[2] = iteration, out[3] = launches completed since the reset.
 extern "C" int litedsa_attn_status(int* out4_host, int reset) {
   using namespace lt;
   if (out4_host &&
       cudaMemcpyFromSymbol(out4_host, g_attn_status, sizeof(int) * 4) != cudaSuccess)
     return LITEDSA_ERR_CUDA;
   if (reset) {
-    const int z[4] = {0, 0, 0, 0};
+    const int z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if (cudaMemcpyToSymbol(g_attn_status, z, sizeof(z)) != cudaSuccess) return LITEDSA_ERR_CUDA;
   }
   return (out4_host && out4_host[0] != 0) ? LITEDSA_ERR_TIMEOUT : LITEDSA_OK;
+}
+
+// Self-test of the bounded wait, for test suites: a one-warp kernel waits with the given
+// limit on an mbarrier that nobody arrives on.  The wait must give up, record its site
+// (kSiteSelfTest) in the same status block the attention kernels use, and the kernel must
+// return normally.  Synchronous.  Returns LITEDSA_ERR_TIMEOUT when the wait expired as it
+// should, LITEDSA_OK if it (wrongly) succeeded.  Nothing hangs or faults.
+namespace lt {
+__global__ void wait_selftest_kernel(int epoch, unsigned long long limit_ns, int* returned) {
+  __shared__ uint64_t bar;
+  const Waiter wt{g_attn_status, epoch, limit_ns};
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+  }
+  __syncwarp();
+  const bool ok = mbar_wait(&bar, 0, wt, kSiteSelfTest, 7);
+  if (threadIdx.x == 0) *returned = ok ? 1 : 2;
+}
+}  // namespace lt
+extern "C" int litedsa_selftest_wait_timeout(uint64_t limit_ns, int* returned_device) {
+  using namespace lt;
+  if (!returned_device || limit_ns == 0 || limit_ns > 1000000000ull) return LITEDSA_ERR_ARG;
+  wait_selftest_kernel<<<1, 32>>>(next_launch_epoch(), limit_ns, returned_device);
+  if (cudaGetLastError() != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) return LITEDSA_ERR_CUDA;
+  int st[4] = {0, 0, 0, 0};
+  if (cudaMemcpyFromSymbol(st, g_attn_status, sizeof(st)) != cudaSuccess) return LITEDSA_ERR_CUDA;
+  return st[0] != 0 ? LITEDSA_ERR_TIMEOUT : LITEDSA_OK;
 }

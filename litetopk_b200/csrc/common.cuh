@@ -16,6 +16,33 @@
 
 namespace lt {
 
+// ---------------------------------------------------------------- host-side helpers (abi.cu)
+// A fresh epoch for one kernel launch (never 0; process-wide counter) and the current limit
+// of a single device-side wait (default kWaitLimitNs; litedsa_set_wait_limit_ns changes it).
+int next_launch_epoch();
+unsigned long long wait_limit_ns();
+
+// Arguments of the FP8 attention operator as every entry point of the library passes them
+// to the shared checker / launcher (attn_fp8.cu).
+struct Fp8Args {
+  const void* q8;
+  const void* kv8;
+  const int32_t* indices;
+  float sm_scale, out_scale;
+  const int32_t* topk_length;
+  const uint32_t* memb_qm;
+  int h_per_q;
+  float* max_logits;
+  float* lse;
+  int ng, s_kv, topk;
+  int64_t q_row_stride, kv_row_stride, indices_row_stride;
+  const float* attn_sink;
+  const int32_t* topk_length_per_q;
+  int q_group_div;
+};
+int check_fp8_args(const Fp8Args& a);                                   // no CUDA call
+int run_fp8(const Fp8Args& a, void* const* outs, int n_outs, void* stream);
+
 // ---------------------------------------------------------------- addresses / cluster
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -81,39 +108,56 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait.  Every wait in the library goes through here: it gives up after
-// `kWaitLimitNs` of wall time, or as soon as any other wait of the launch gave up
-// (the launch-wide abort word), records where, and returns false.  Callers then fall
-// through to their normal tear-down, so a lost arrival costs a wrong result and an
-// error status, never a hung GPU.
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
+// Bounded wait.  Every wait in the library goes through here: it gives up after the
+// launch's time limit, or as soon as any other wait of the SAME launch gave up (the abort
+// word carries that launch's epoch), records where, and returns false.  Callers then fall
+// through to their normal tear-down, so a lost arrival costs a wrong result and an error
+// status, never a hung GPU.
+//
+// Status block of a kernel family (ints): [0] first wait site that ever expired since the
+// last reset (sticky; 0 = none), [1] its block, [2] its loop iteration, [3] launches
+// completed, [4] epoch of the launch that is aborting.  Later launches carry another
+// epoch, so one expired wait does not make them give up too.
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // default limit: 2 s
+struct Waiter {
+  int* status;                  // the family's status block (device global)
+  int epoch;                    // this launch's epoch (never 0)
+  unsigned long long limit_ns;  // how long one wait may take
+  __device__ __forceinline__ bool aborting() const {
+    return reinterpret_cast<volatile int*>(status)[4] == epoch;
+  }
+  // record the first failure (sticky) and make every other wait of this launch give up
+  __device__ __forceinline__ void fail(int site, int iter) const {
+    if (atomicCAS(status, 0, site) == 0) {
+      status[1] = (int)blockIdx.x;
+      status[2] = iter;
+    }
+    atomicExch(status + 4, epoch);
+  }
+};
 __device__ __forceinline__ unsigned long long globaltimer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// status[0] = first failing wait site (0 = none), status[1] = blockIdx.x, status[2] = iteration
-static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int* status, int site,
-                                            int iter) {
+static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, const Waiter w,
+                                                   int site, int iter) {
   const unsigned long long t0 = globaltimer_ns();
   for (;;) {
     for (int i = 0; i < 256; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return false;
-    if (globaltimer_ns() - t0 > kWaitLimitNs) {
-      if (status != nullptr && atomicCAS(status, 0, site) == 0) {
-        status[1] = (int)blockIdx.x;
-        status[2] = iter;
-      }
+    if (w.aborting()) return false;
+    if (globaltimer_ns() - t0 > w.limit_ns) {
+      w.fail(site, iter);
       return false;
     }
   }
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int site,
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const Waiter& w, int site,
                                           int iter = 0) {
   for (int i = 0; i < 64; ++i)
     if (mbar_try_wait(bar, parity)) return true;
-  return mbar_wait_slow(bar, parity, status, site, iter);
+  return mbar_wait_slow(bar, parity, w, site, iter);
 }
 
 // release at cluster scope: orders this thread's earlier (distributed) shared-memory stores

@@ -20,12 +20,6 @@
 
 extern "C" int litedsa_repack_kv656(const void* kv656, void* kv576, int s_kv, int64_t out_pitch,
                                     float scale, int* mismatch_flag, void* stream);
-extern "C" int litedsa_masked_mla_fp8(const void* q8, const void* kv8, const int32_t* indices,
-                                      float sm_scale, float out_scale, const int32_t* topk_length,
-                                      const uint32_t* memb_qm, int h_per_q, void* out,
-                                      float* max_logits, float* lse, int ng, int s_kv, int topk,
-                                      int64_t q_row_stride, int64_t kv_row_stride,
-                                      int64_t indices_row_stride, float* debug_dump, void* stream);
 
 namespace {
 
@@ -60,17 +54,24 @@ int scratch_for_current_device(unsigned char** out) {
 
 // See include/litedsa_b200.h.  Calls no cudaMalloc / cudaFree and no allocating library
 // routine: one cudaMemsetAsync (the mismatch word must start at zero), the repack kernel
-// into the built-in scratch, then the attention kernel reading the scratch.
+// into the built-in scratch, then the attention kernel reading the scratch.  Every argument
+// rule is checked before the scratch is touched or anything is enqueued.
 extern "C" int litedsa_masked_mla_fp8_kv656_noalloc(
     const void* q8, const void* kv656, const int32_t* indices, float sm_scale, float kv_scale,
     const int32_t* topk_length, const uint32_t* memb_qm, int h_per_q, void* out, float* max_logits,
     float* lse, int ng, int s_kv, int topk, int64_t q_row_stride, int64_t indices_row_stride,
     int* mismatch_flag, void* stream) {
-  if (!kv656) return LITEDSA_ERR_ARG;
-  if (s_kv <= 0) return LITEDSA_ERR_SHAPE;
+  if (!kv656 || !memb_qm || !out) return LITEDSA_ERR_ARG;
+  if (((uintptr_t)kv656 | (uintptr_t)out) & 15) return LITEDSA_ERR_UNSUPPORTED;
+  if (!(kv_scale > 0.f)) return LITEDSA_ERR_SHAPE;
+  // the operator's own rules, with the scratch rows standing in for kv8 (576-byte pitch)
+  lt::Fp8Args a{q8, kv656, indices, sm_scale, kv_scale, topk_length, memb_qm, h_per_q, max_logits,
+                lse, ng, s_kv, topk, q_row_stride, 576, indices_row_stride, nullptr, nullptr, 1};
+  int rc = lt::check_fp8_args(a);
+  if (rc != LITEDSA_OK) return rc;
   if (s_kv > kNoAllocMaxRows) return LITEDSA_ERR_UNSUPPORTED;   // beyond the built-in scratch
   unsigned char* scratch = nullptr;
-  int rc = scratch_for_current_device(&scratch);
+  rc = scratch_for_current_device(&scratch);
   if (rc != LITEDSA_OK) return rc;
   int* flag = mismatch_flag ? mismatch_flag : reinterpret_cast<int*>(scratch);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
@@ -78,7 +79,7 @@ extern "C" int litedsa_masked_mla_fp8_kv656_noalloc(
   unsigned char* rows = scratch + kFlagBytes;
   rc = litedsa_repack_kv656(kv656, rows, s_kv, 576, kv_scale, flag, stream);
   if (rc != LITEDSA_OK) return rc;
-  return litedsa_masked_mla_fp8(q8, rows, indices, sm_scale, kv_scale, topk_length, memb_qm, h_per_q,
-                                out, max_logits, lse, ng, s_kv, topk, q_row_stride, 576,
-                                indices_row_stride, nullptr, stream);
+  a.kv8 = rows;
+  void* outs[1] = {out};
+  return lt::run_fp8(a, outs, 1, stream);
 }

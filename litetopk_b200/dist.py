@@ -120,6 +120,15 @@ class PeerGatheredOutput:
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
         self.device = torch.device(device)
+        # every rank's slot has the same number of rows: the slot of rank r starts r * slot_bytes
+        # into each buffer.  Ranks that own unequal blocks (dist.tile_range with a remainder)
+        # must pad to the largest block before building this object.
+        rows_t = torch.tensor([rows, -rows], dtype=torch.int64,
+                              device=self.device if self.device.type == "cuda" else "cpu")
+        dist.all_reduce(rows_t, op=dist.ReduceOp.MAX, group=self.group)
+        if int(rows_t[0]) != -int(rows_t[1]):
+            raise ValueError(f"PeerGatheredOutput needs the same number of rows on every rank "
+                             f"(got between {-int(rows_t[1])} and {int(rows_t[0])}); pad the smaller blocks")
         shape = (self.world, rows, *row_shape)
         self.handle = None
         if self.device.type == "cuda":

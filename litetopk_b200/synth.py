@@ -237,6 +237,40 @@ def make_dsv4(w: Workload, seed: int = 0, device="cpu", d: int = D_QK):
     return q, kc, kr
 
 
+def dsv4_rank_space_operands(q: torch.Tensor, kv_comp: torch.Tensor, kv_raw: torch.Tensor, pos0: int,
+                             heads: int, window: int, ratio: int):
+    """The two-range problem in the form the reference's DSv4 operator takes it
+    (kernels/b200/dsa/litedsa_dsv4.cu:40-55): a flat KV workspace [compressed | raw], one
+    ascending union index list per tile (-1 padded to a multiple of 64) and the per-token
+    bounds (prefix, window start, window end) in union-rank space.
+
+    q [T,h,d], kv_comp [Nc,d], kv_raw [S,d] (any width d) -> (q [ng,128,d], kv [Nc+S,1,d],
+    indices [ng,1,topk] i32, pref / win_lo / win_hi [ng,G] i32, counts [ng] i32)."""
+    T, _, d = q.shape
+    G = 128 // heads
+    ng = T // G
+    nc_all = kv_comp.shape[0]
+    dev = q.device
+    p_first = pos0 + torch.arange(ng, device=dev, dtype=torch.int64) * G           # [ng]
+    p_tok = p_first[:, None] + torch.arange(G, device=dev, dtype=torch.int64)       # [ng, G]
+    ncmax = torch.clamp(p_tok[:, -1] // ratio, max=nc_all)                           # [ng]
+    lo = torch.clamp(p_first - window + 1, min=0)                                    # [ng]
+    n_win = p_tok[:, -1] + 1 - lo                                                    # [ng]
+    counts = (ncmax + n_win).to(torch.int32)
+    topk = int((int(counts.max().item()) + 63) // 64 * 64)
+    r = torch.arange(topk, device=dev, dtype=torch.int64)[None, :]                   # rank
+    is_c = r < ncmax[:, None]
+    widx = nc_all + lo[:, None] + (r - ncmax[:, None])
+    indices = torch.where(is_c, r, torch.where(r < counts[:, None].long(), widx, torch.full_like(widx, -1)))
+    pref = torch.clamp(p_tok // ratio, max=nc_all)
+    win_lo = ncmax[:, None] + (torch.clamp(p_tok - window + 1, min=0) - lo[:, None])
+    win_hi = ncmax[:, None] + (p_tok + 1 - lo[:, None])
+    kv = torch.cat([kv_comp, kv_raw], dim=0).contiguous().view(-1, 1, d)
+    return (q.contiguous().view(ng, 128, d), kv, indices.to(torch.int32).view(ng, 1, topk).contiguous(),
+            pref.to(torch.int32).contiguous(), win_lo.to(torch.int32).contiguous(),
+            win_hi.to(torch.int32).contiguous(), counts.contiguous())
+
+
 def attended_pairs(w: Workload, topk_idx: Optional[torch.Tensor] = None) -> int:
     """Attended (query-head, key) pairs: the unit effective FLOPs are counted on."""
     if w.kind == "dsv4":

@@ -27,7 +27,7 @@ def test_library_exports_every_declared_symbol(built_lib):
     assert sorted(_lib.SIGNATURES) == names, "ctypes table and header disagree"
     for n in names:
         assert getattr(built_lib, n) is not None
-    assert built_lib.litedsa_abi_version() >= 1
+    assert built_lib.litedsa_abi_version() >= 2
     assert b"shape" in built_lib.litedsa_error_string(2)
 
 
@@ -79,13 +79,37 @@ def test_entry_points_reject_bad_arguments_before_any_cuda_call(built_lib):
     # attention: null q, topk not a multiple of 128, heads not dividing 128, misaligned base
     ok = dict(sm=0.1, os=1.0)
     assert L.litedsa_masked_mla_fp8(None, P, P, ok["sm"], ok["os"], None, P, 64, P, None, P,
-                                    2, 128, 128, 576, 576, 128, None, None) == ARG
+                                    2, 128, 128, 576, 576, 128, None) == ARG
     assert L.litedsa_masked_mla_fp8(P, P, P, ok["sm"], ok["os"], None, P, 64, P, None, P,
-                                    2, 128, 100, 576, 576, 128, None, None) == SHAPE
+                                    2, 128, 100, 576, 576, 128, None) == SHAPE
     assert L.litedsa_masked_mla_fp8(P, P, P, ok["sm"], ok["os"], None, P, 48, P, None, P,
-                                    2, 128, 128, 576, 576, 128, None, None) == SHAPE
+                                    2, 128, 128, 576, 576, 128, None) == SHAPE
     assert L.litedsa_masked_mla_fp8(P + 8, P, P, ok["sm"], ok["os"], None, P, 64, P, None, P,
-                                    2, 128, 128, 576, 576, 128, None, None) == UNSUP
+                                    2, 128, 128, 576, 576, 128, None) == UNSUP
+    # extended form: neither mask given, q_group_div not dividing the tile count
+    assert L.litedsa_masked_mla_fp8_ex(P, P, P, ok["sm"], ok["os"], None, None, 64, P, None, P,
+                                       2, 128, 128, 576, 576, 128, None, None, 1, None) == ARG
+    assert L.litedsa_masked_mla_fp8_ex(P, P, P, ok["sm"], ok["os"], None, P, 64, P, None, P,
+                                       3, 128, 128, 576, 576, 128, None, None, 2, None) == SHAPE
+    # allocation-free form: every rule is checked before its scratch is touched
+    na = L.litedsa_masked_mla_fp8_kv656_noalloc
+    assert na(P, P, P, ok["sm"], ok["os"], None, P, 64, None, None, P, 2, 128, 128, 576, 128, None, None) == ARG
+    assert na(P, P, P, ok["sm"], ok["os"], None, P, 64, P, None, P, 2, 128, 100, 576, 128, None, None) == SHAPE
+    assert na(P, P, P, ok["sm"], ok["os"], None, P, 48, P, None, P, 2, 128, 128, 576, 128, None, None) == SHAPE
+    assert na(P + 8, P, P, ok["sm"], ok["os"], None, P, 64, P, None, P, 2, 128, 128, 576, 128, None, None) == UNSUP
+    assert na(P, P, P, ok["sm"], ok["os"], None, P, 64, P, None, P, 2, 65537, 128, 576, 128, None, None) == UNSUP
+    # bf16 operators: missing range arrays, width other than 512 / 576, list not in 64-key blocks
+    assert L.litedsa_dsv4_masked_mla_bf16(P, P, P, None, P, P, P, 0.1, 64, P, P, None,
+                                          2, 128, 128, 512, 512, 512, 128, None) == ARG
+    assert L.litedsa_dsv4_masked_mla_bf16(P, P, P, P, P, P, P, 0.1, 64, P, P, None,
+                                          2, 128, 128, 500, 512, 512, 128, None) == SHAPE
+    assert L.litedsa_dsv4_masked_mla_bf16(P, P, P, P, P, P, P, 0.1, 64, P, P, None,
+                                          2, 128, 96, 512, 512, 512, 96, None) == SHAPE
+    assert L.litedsa_masked_mla_bf16(P, P, P, 0.1, None, None, 64, P, None, P,
+                                     2, 128, 128, 576, 576, 576, 128, None, None) == ARG
+    assert L.litedsa_masked_mla_bf16(P, P, P, 0.1, None, P, 64, P, None, P,
+                                     2, 128, 64, 576, 576, 576, 64, None, None) == SHAPE
+    assert L.litedsa_dequant_kv656(P, P, 16, 1000, None) == SHAPE
     # multi-destination form: destination count out of range, null destination
     outs = (ctypes.c_void_p * 9)(*([P] * 9))
     assert L.litedsa_masked_mla_fp8_multi(P, P, P, ok["sm"], ok["os"], None, P, 64, outs, 9, None, P,

@@ -155,7 +155,9 @@ def test_argument_validation():
         api.masked_mla_fp8_out(q.float(), kv, idx, 1.0, 1.0, None, m, 64, out, None, lse)
     kv656 = synth.make_kv_cache(256, seed=1, mode="native").to(DEV)       # varying per-128 scales
     with pytest.raises(ValueError):
-        api.repack_kv656(kv656, 2.0 ** -6)
+        api.repack_kv656(kv656, 2.0 ** -6, check_scales=True)
+    _, flag = api.repack_kv656(kv656, 2.0 ** -6, return_flag=True)       # no host synchronisation
+    assert int(flag.item()) != 0
 
 
 def test_full_size_tile_sample_linearity_in_v_scale():
@@ -178,3 +180,115 @@ def test_full_size_tile_sample_linearity_in_v_scale():
     assert torch.equal(outs[1][0].float(), 2 * outs[0][0].float())
     assert bool(torch.isfinite(outs[0][0].float()).all())
     assert api.attn_status()[0] == 0
+
+
+# --------------------------------------------------------------------------- optional operator modes
+def _run_ex(w, u, c, m, q8, kv8, qs, ks, **kw):
+    ng = u.shape[0]
+    out = torch.full((ng, 128, 512), float("nan"), dtype=torch.bfloat16, device=DEV)
+    lse = torch.full((ng, 128), float("nan"), dtype=torch.float32, device=DEV)
+    ml = torch.full((ng, 128), float("nan"), dtype=torch.float32, device=DEV)
+    api.attn_status(reset=True)
+    api.masked_mla_fp8_out(q8.to(DEV), kv8.to(DEV), torch.from_numpy(u).to(DEV), synth.SM_SCALE * qs * ks, ks,
+                           None if c is None else torch.from_numpy(c).to(DEV),
+                           None if m is None else torch.from_numpy(m.view(np.int32)).to(DEV),
+                           w.heads, out, ml, lse, **kw)
+    torch.cuda.synchronize()
+    return out, lse, ml
+
+
+def test_attn_sink_joins_the_output_normaliser_only():
+    w, idx, kv, q = _case(64, 32, 256, 4096, (0.5, 0.9), seed=8)
+    (u, c, m), ref, (q8, kv8, qs, ks) = _oracle(w, idx, kv, q)
+    sink = torch.randn((128,), generator=torch.Generator().manual_seed(1)) * 2.0
+    q8t = q8.view(w.tiles, 128, 576)
+    out, lse, ml = _run_ex(w, u, c, m, q8t, kv8, qs, ks, attn_sink=sink.to(DEV))
+    ref_s = ao.masked_mla_refnum(q8t.view(torch.float8_e4m3fn).float(), kv8.view(torch.float8_e4m3fn).float(),
+                                 torch.from_numpy(u), torch.from_numpy(c), torch.from_numpy(m.astype(np.int64)),
+                                 synth.SM_SCALE * qs * ks, ks, w.heads, attn_sink=sink)
+    _check(out, lse, ml, ref_s)
+    assert float((ref_s[1] - ref[1]).abs().max()) == 0.0          # lse is the sink-free one
+    assert float((ref_s[0].float() - ref[0].float()).abs().max()) > 1e-3   # ... and the output is not
+
+
+def test_per_query_prefix_lengths_replace_the_membership_mask():
+    # causal-prefix mode: token t of a tile attends the union ranks below its own bound
+    w, idx, kv, q = _case(64, 16, 128, 2048, (0.6, 0.6), seed=9)
+    (u, c, m), _, (q8, kv8, qs, ks) = _oracle(w, idx, kv, q)
+    G = w.group
+    g = torch.Generator().manual_seed(2)
+    frac = torch.sort(torch.rand((w.tiles, G), generator=g), dim=1).values      # non-decreasing bounds
+    frac[:, -1] = 1.0
+    lens = (frac * torch.from_numpy(c).float()[:, None]).round().to(torch.int32)
+    lens[1, 0] = 0                                                               # a token with no key
+    q8t = q8.view(w.tiles, 128, 576)
+    q8f, kv8f = q8t.view(torch.float8_e4m3fn).float(), kv8.view(torch.float8_e4m3fn).float()
+    for use_mask in (False, True):
+        out, lse, ml = _run_ex(w, u, c, m if use_mask else None, q8t, kv8, qs, ks,
+                               topk_length_per_q=lens.to(DEV))
+        ref = ao.masked_mla_refnum(q8f, kv8f, torch.from_numpy(u), None,
+                                   torch.from_numpy(m.astype(np.int64)) if use_mask else None,
+                                   synth.SM_SCALE * qs * ks, ks, w.heads, topk_length_per_q=lens)
+        _check(out, lse, ml, ref)
+
+
+def test_q_group_div_kv_split_merges_to_the_unsplit_result():
+    # one long union list cut into two slices that share the Q tile; merging the slices' outputs
+    # with their lse gives the unsplit attention
+    w, idx, kv, q = _case(16, 64, 512, 4096, (0.8, 0.8), seed=10)
+    (u, c, m), ref, (q8, kv8, qs, ks) = _oracle(w, idx, kv, q)
+    ng, cap, G = w.tiles, w.cap, w.group
+    half = cap // 2                                          # 512: a multiple of 128
+    u2 = np.ascontiguousarray(u.reshape(ng, 2, half).reshape(ng * 2, half))
+    c2 = np.stack([np.minimum(c, half), np.maximum(c - half, 0)], axis=1).reshape(-1).astype(np.int32)
+    capw = cap // 32
+    m2 = np.ascontiguousarray(m.reshape(ng, G, 2, capw // 2).transpose(0, 2, 1, 3).reshape(ng * 2, G, capw // 2))
+    q8t = q8.view(ng, 128, 576)
+    out, lse, ml = _run_ex(w, u2, c2, m2, q8t, kv8, qs, ks, q_group_div=2)
+    ref2 = ao.masked_mla_refnum(q8t.view(torch.float8_e4m3fn).float(), kv8.view(torch.float8_e4m3fn).float(),
+                                torch.from_numpy(u2), torch.from_numpy(c2), torch.from_numpy(m2.astype(np.int64)),
+                                synth.SM_SCALE * qs * ks, ks, w.heads, q_group_div=2)
+    _check(out, lse, ml, ref2)
+    # LSE merge of the two slices == the unsplit reference
+    o = out.float().cpu().view(ng, 2, 128, 512)
+    l = lse.cpu().view(ng, 2, 128)
+    wgt = torch.softmax(torch.where(torch.isinf(l), torch.full_like(l, -float("inf")), l), dim=1)
+    wgt = torch.nan_to_num(wgt, nan=0.0)
+    merged = (o * wgt[..., None]).sum(dim=1)
+    mad, cos = ao.compare(merged, ref[0])
+    assert mad <= 2e-2 and cos >= 0.9995, (mad, cos)
+
+
+def test_bounded_wait_gives_up_reports_and_later_launches_are_unaffected():
+    # a wait nobody satisfies must expire (about a millisecond here), record its site in the
+    # status block and return; nothing hangs or faults.  The record is sticky until reset, but
+    # the next launch carries another epoch and runs normally.
+    from litetopk_b200 import _lib
+    w, idx, kv, q = _case(32, 64, 256, 2048, (0.8, 0.8), seed=12)
+    (u, c, m), ref, (q8, kv8, qs, ks) = _oracle(w, idx, kv, q)
+    api.attn_status(reset=True)
+    flag = torch.zeros((1,), dtype=torch.int32, device=DEV)
+    with torch.cuda.device(DEV):
+        rc = _lib.lib().litedsa_selftest_wait_timeout(1_000_000, flag.data_ptr())
+    assert rc == _lib.ERR_TIMEOUT
+    assert int(flag.item()) == 2                         # the wait returned false and the kernel ended
+    st = api.attn_status()
+    assert st[0] != 0 and st[2] == 7                     # site recorded with the test's iteration tag
+    import ctypes
+    buf = (ctypes.c_int * 4)()
+    with torch.cuda.device(DEV):
+        assert _lib.lib().litedsa_attn_status(buf, 0) == _lib.ERR_TIMEOUT
+    # without a reset: a normal launch still runs and is correct (its epoch differs)
+    ng = w.tiles
+    out = torch.empty((ng, 128, 512), dtype=torch.bfloat16, device=DEV)
+    lse = torch.empty((ng, 128), dtype=torch.float32, device=DEV)
+    api.masked_mla_fp8_out(q8.view(ng, 128, 576).to(DEV), kv8.to(DEV), torch.from_numpy(u).to(DEV),
+                           synth.SM_SCALE * qs * ks, ks, torch.from_numpy(c).to(DEV),
+                           torch.from_numpy(m.view(np.int32)).to(DEV), w.heads, out, None, lse)
+    torch.cuda.synchronize()
+    mad, cos = ao.compare(out.cpu(), ref[0])
+    assert mad <= TOL_ABS and cos >= TOL_COS
+    assert api.attn_status(reset=True)[0] != 0           # still the sticky record; now cleared
+    assert api.attn_status()[0] == 0
+    old = api.set_wait_limit_ns(5_000_000)               # the limit is a run-time setting
+    assert api.set_wait_limit_ns(0) == 5_000_000 and old > 0

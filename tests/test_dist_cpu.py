@@ -92,3 +92,18 @@ def _peer_worker(rank, world, port, rows):
 def test_peer_gathered_output_two_ranks():
     port = _free_port()
     mp.spawn(_peer_worker, args=(2, port, 5), nprocs=2, join=True)
+
+
+def _unequal_worker(rank, world, port):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        lo, hi = ldist.tile_range(5, world, rank)          # 3 + 2 tiles: unequal blocks
+        with pytest.raises(ValueError, match="same number of rows"):
+            ldist.PeerGatheredOutput(hi - lo, (4,), torch.float32, "cpu")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_gathered_output_rejects_unequal_slots():
+    mp.spawn(_unequal_worker, args=(2, _free_port()), nprocs=2, join=True)

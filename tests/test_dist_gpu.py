@@ -1,6 +1,6 @@
-"""Two ranks on two GPUs: the attention kernel's epilogue writes each rank's outputs into
-both ranks' gathered buffers (peer-mapped symmetric memory), and the copy-engine form pushes
-chunks to the peer; either way the gathered result must be bit-identical with one GPU
+"""Two to four ranks, one per GPU: the attention kernel's epilogue writes each rank's outputs
+into every rank's gathered buffer (peer-mapped symmetric memory), and the copy-engine form
+pushes chunks to the peers; either way the gathered result must be bit-identical with one GPU
 computing every tile.  Skipped with fewer than two GPUs."""
 import os
 import socket
@@ -43,7 +43,7 @@ def _worker(rank, world, port):
         want = torch.empty((ng, 128, 512), dtype=torch.bfloat16, device=dev)
         lse_all = torch.empty((ng, 128), dtype=torch.float32, device=dev)
         api.masked_mla_fp8_out(q8t, kv8, u, sm, ks, c, m, w.heads, want, None, lse_all)
-        # two ranks, half of the tiles each, gathered by the epilogue
+        # `world` ranks, an equal share of the tiles each, gathered by the epilogue
         lo, hi = ldist.tile_range(ng, world, rank)
         assert hi - lo == ng // world
         pg = ldist.PeerGatheredOutput(hi - lo, (128, 512), torch.bfloat16, dev)
@@ -77,7 +77,10 @@ def _worker(rank, world, port):
         dist.destroy_process_group()
 
 
-def test_epilogue_gather_two_gpus():
-    if torch.cuda.device_count() < 2:
+def test_epilogue_gather_across_gpus():
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
         pytest.skip("needs two GPUs")
-    mp.spawn(_worker, args=(2, _free_port()), nprocs=2, join=True)
+    if world == 3:
+        world = 2                      # 128 tiles split evenly over 2 or 4 ranks
+    mp.spawn(_worker, args=(world, _free_port()), nprocs=world, join=True)

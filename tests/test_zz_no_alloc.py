@@ -53,6 +53,40 @@ def test_noalloc_entry_matches_regular_route_twice():
         # same kernels on the same bytes: identical; the suite's tolerance is the bound
         assert float((out.float() - out_r.float()).abs().max()) <= 1e-2
         assert torch.equal(out, out_r) and torch.equal(lse, lse_r) and torch.equal(ml, ml_r)
+        # without a caller flag the mismatch word lives in the library's own scratch
+        rc, out_n, lse_n, _ = _call_noalloc(q8, kv656, u, c, m, heads, sm, ks, None)
+        torch.cuda.synchronize()
+        assert rc == 0 and torch.equal(out_n, out_r) and torch.equal(lse_n, lse_r)
+
+
+def test_noalloc_entry_leaves_device_memory_unchanged():
+    # the point of the entry: nothing is allocated, by the library or through torch
+    ks = qs = synth.REFCOMPAT_SCALE
+    w = synth.Workload("t", tokens=64, heads=64, topk=512, s_kv=4096, overlap=(0.7, 0.7))
+    idx = synth.make_topk(w, seed=23).to(DEV)
+    kv656 = synth.make_kv_cache(w.s_kv, seed=23, mode="refcompat").to(DEV)
+    q8 = api.quantize_e4m3(synth.make_q(w.tokens, w.heads, seed=23, mode="refcompat").to(DEV), qs)
+    q8 = q8.view(w.tiles, 128, 576)
+    u, m, c = api.union_qm(idx, w.group, seq_space=w.s_kv, return_counts=True)
+    ng, cap = u.shape
+    out = torch.empty((ng, 128, 512), dtype=torch.bfloat16, device=DEV)
+    lse = torch.empty((ng, 128), dtype=torch.float32, device=DEV)
+
+    def call():
+        with torch.cuda.device(DEV):
+            return _lib.lib().litedsa_masked_mla_fp8_kv656_noalloc(
+                q8.data_ptr(), kv656.data_ptr(), u.data_ptr(), float(synth.SM_SCALE * qs * ks), float(ks),
+                c.data_ptr(), m.data_ptr(), w.heads, out.data_ptr(), None, lse.data_ptr(), ng, w.s_kv, cap,
+                q8.stride(1), u.stride(0), None, torch.cuda.current_stream().cuda_stream)
+
+    assert call() == 0                                   # warm-up: set-up happens on the first call
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info(DEV)
+    alloc0 = torch.cuda.memory_allocated(DEV)
+    assert call() == 0 and call() == 0
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info(DEV)
+    assert torch.cuda.memory_allocated(DEV) == alloc0 and free1 == free0
 
 
 def test_noalloc_entry_rejects_oversized_cache_and_flags_bad_scales():
