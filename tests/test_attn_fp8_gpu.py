@@ -255,8 +255,10 @@ def test_q_group_div_kv_split_merges_to_the_unsplit_result():
     wgt = torch.softmax(torch.where(torch.isinf(l), torch.full_like(l, -float("inf")), l), dim=1)
     wgt = torch.nan_to_num(wgt, nan=0.0)
     merged = (o * wgt[..., None]).sum(dim=1)
+    # two e4m3-P evaluations with different running-max histories differ by the P rounding
+    # (relative 2^-4 per element), so this semantic check is looser than the parity check above
     mad, cos = ao.compare(merged, ref[0])
-    assert mad <= 2e-2 and cos >= 0.9995, (mad, cos)
+    assert mad <= 0.1 and cos >= 0.9995, (mad, cos)
 
 
 def test_bounded_wait_gives_up_reports_and_later_launches_are_unaffected():
