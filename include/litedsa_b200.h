@@ -97,6 +97,14 @@ int litedsa_masked_mla_fp8(const void* q8, const void* kv8, const int32_t* indic
  *   q_group_div >= 1: that many consecutive tiles (slices of one long union list) share ONE
  *            Q tile, so q8 is [ng / q_group_div, 128, 576]; the outputs stay per tile and the
  *            caller merges them with their lse (litedsa_attention_sm100.cuh:1383-1385, 1909).
+ *   q_token_stride, q_head_stride, out_token_stride, out_head_stride (ELEMENTS; 0 = the dense
+ *            packed layout): in-place addressing of q and out inside [T, H_padded, d] tensors
+ *            that hold h_per_q real heads per token.  Row r of tile g is then read at
+ *            q8 + (g*G + r / h_per_q) * q_token_stride + (r % h_per_q) * q_head_stride and
+ *            written likewise into out, so a tensor-parallel caller needs neither the pack
+ *            copy of q nor the unpack copy of out that the reference's packed path pays
+ *            (kernels/b200/dsa/DSV4_ZEROCOPY_PLAN.md:12-22, 50-76: planned there, not built).
+ *            Pitches must be multiples of 16 bytes; lse / max_logits stay packed [ng, 128].
  */
 int litedsa_masked_mla_fp8_ex(const void* q8, const void* kv8, const int32_t* indices,
                               float sm_scale, float out_scale, const int32_t* topk_length,
@@ -104,7 +112,8 @@ int litedsa_masked_mla_fp8_ex(const void* q8, const void* kv8, const int32_t* in
                               float* lse, int ng, int s_kv, int topk, int64_t q_row_stride,
                               int64_t kv_row_stride, int64_t indices_row_stride,
                               const float* attn_sink, const int32_t* topk_length_per_q,
-                              int q_group_div, void* stream);
+                              int q_group_div, int64_t q_token_stride, int64_t q_head_stride,
+                              int64_t out_token_stride, int64_t out_head_stride, void* stream);
 
 /*
  * litedsa_masked_mla_fp8 with the all-gather of a query-sharded multi-GPU run folded into
@@ -189,6 +198,9 @@ int litedsa_repack_kv656(const void* kv656, void* kv576, int s_kv, int64_t out_p
  *   attn_sink [128] fp32 per packed row or NULL: adds exp(sink) to the OUTPUT normaliser only
  *   out [ng, 128, 512] bf16;  lse [ng, 128] fp32 (natural log, without the sink)
  * Requires pos0 + ng * (128 / h_per_q) <= s_raw.
+ * q_token_stride, q_head_stride, out_token_stride, out_head_stride (ELEMENTS; 0 = the dense
+ * packed layout) address q and out in place inside [T, H_padded, d] tensors with h_per_q real
+ * heads per token (see litedsa_masked_mla_fp8_ex; kernels/b200/dsa/DSV4_ZEROCOPY_PLAN.md:50-76).
  * The kernel uses all 227 KB of shared memory and needs its dynamic base within 768 bytes of
  * a 1024-byte boundary: the first call on each device launches a one-thread probe and reads
  * its answer back synchronously (make that call outside stream capture); when the base
@@ -198,7 +210,8 @@ int litedsa_dsv4_c128a_bf16(const void* q, const void* kv_comp, const void* kv_r
                             int h_per_q, int n_comp, int s_raw, int pos0, int window, int ratio,
                             float sm_scale, const float* attn_sink, void* out, float* lse,
                             int64_t q_row_stride, int64_t kc_row_stride, int64_t kr_row_stride,
-                            void* stream);
+                            int64_t q_token_stride, int64_t q_head_stride, int64_t out_token_stride,
+                            int64_t out_head_stride, void* stream);
 
 /* Status block of the DSv4 kernel; same meaning and use as litedsa_attn_status. */
 int litedsa_dsv4_status(int* out4_host, int reset);
@@ -221,6 +234,10 @@ int litedsa_dsv4_status(int* out4_host, int reset);
  *   out [ng, 128, 512] bf16;  lse [ng, 128] fp32 (natural log, without the sink)
  *   d = 512 (the reference's only width) or 576; topk % 64 == 0; strides in ELEMENTS
  *   (q/kv: >= d, multiples of 8; indices: >= topk); q / kv / out 16-byte aligned.
+ *   q_token_stride, q_head_stride, out_token_stride, out_head_stride (ELEMENTS; 0 = the dense
+ *   packed layout): q and out addressed in place inside [T, H_padded, d] tensors with
+ *   h_per_q real heads per token, as in litedsa_masked_mla_fp8_ex -- the zero-copy form the
+ *   reference planned for this operator (kernels/b200/dsa/DSV4_ZEROCOPY_PLAN.md:50-76).
  * With d = 576 the first call on a device reads a one-thread probe back synchronously
  * (dynamic shared-memory alignment): make that call outside stream capture.
  */
@@ -229,7 +246,9 @@ int litedsa_dsv4_masked_mla_bf16(const void* q, const void* kv, const int32_t* i
                                  const int32_t* win_hi, const int32_t* counts, float sm_scale,
                                  int h_per_q, void* out, float* lse, const float* attn_sink,
                                  int ng, int s_kv, int topk, int d, int64_t q_row_stride,
-                                 int64_t kv_row_stride, int64_t indices_row_stride, void* stream);
+                                 int64_t kv_row_stride, int64_t indices_row_stride,
+                                 int64_t q_token_stride, int64_t q_head_stride,
+                                 int64_t out_token_stride, int64_t out_head_stride, void* stream);
 
 /*
  * masked_mla_fp8's bf16 twin for KV caches that have no single-scale all-e4m3 form (per-128

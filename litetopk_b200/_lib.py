@@ -27,7 +27,8 @@ SIGNATURES = {
     "litedsa_masked_mla_fp8_ex": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p,
                                           c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                           c_int, c_int, c_int64, c_int64, c_int64, c_void_p,
-                                          c_void_p, c_int, c_void_p]),
+                                          c_void_p, c_int, c_int64, c_int64, c_int64, c_int64,
+                                          c_void_p]),
     "litedsa_masked_mla_fp8_multi": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_float,
                                              c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
                                              c_void_p, c_int, c_int, c_int, c_int64, c_int64,
@@ -44,12 +45,12 @@ SIGNATURES = {
                                                      c_void_p, c_void_p]),
     "litedsa_dsv4_c128a_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                         c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int64,
-                                        c_int64, c_int64, c_void_p]),
+                                        c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p]),
     "litedsa_dsv4_status": (c_int, [c_void_p, c_int]),
     "litedsa_dsv4_masked_mla_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                              c_void_p, c_float, c_int, c_void_p, c_void_p, c_void_p,
                                              c_int, c_int, c_int, c_int, c_int64, c_int64, c_int64,
-                                             c_void_p]),
+                                             c_int64, c_int64, c_int64, c_int64, c_void_p]),
     "litedsa_masked_mla_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
                                         c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                         c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p]),

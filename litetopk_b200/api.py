@@ -123,7 +123,7 @@ def masked_mla_fp8_out(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor,
                        max_logits: Optional[torch.Tensor], lse: torch.Tensor,
                        *, peer_outs=None, attn_sink: Optional[torch.Tensor] = None,
                        topk_length_per_q: Optional[torch.Tensor] = None,
-                       q_group_div: int = 1) -> None:
+                       q_group_div: int = 1, in_place_heads: bool = False) -> None:
     """Reference argument order (kernels/b200/dsa/litedsa.cu:77-80).
 
     q [ng,128,576] e4m3 (uint8 storage accepted); kv [s_kv,1,576] or [s_kv,576] e4m3, row
@@ -139,6 +139,14 @@ def masked_mla_fp8_out(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor,
     ``attn_sink`` [128] f32 per packed row joins the output normaliser; ``topk_length_per_q``
     [ng,G] i32 bounds each token to a causal prefix of the union ranks (memb_qm may then be
     None); ``q_group_div`` consecutive tiles share one Q tile (q is [ng/q_group_div,128,576]).
+
+    ``in_place_heads`` (zero-copy for tensor-parallel callers): q is the model's own
+    ``[T, H_padded, 576]`` tensor and out its ``[T, H_padded, 512]`` tensor, of which only the
+    first ``h_per_q`` head slots of every token are read / written (G = 128 // h_per_q
+    consecutive tokens form a tile); any token / head strides with unit inner stride and
+    16-byte-multiple pitches.  This removes the pack and unpack copies the reference's packed
+    path performs around its kernel (kernels/b200/dsa/DSV4_ZEROCOPY_PLAN.md:12-22).
+    lse / max_logits stay packed ``[ng,128]``.
     """
     f8 = (torch.float8_e4m3fn, torch.uint8)
     _need(q, "q", f8, 3)
@@ -156,20 +164,32 @@ def masked_mla_fp8_out(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor,
         indices = indices[:, 0]
     ng = indices.shape[0]
     q_group_div = int(q_group_div)
-    if q_group_div < 1 or ng % q_group_div or tuple(q.shape) != (ng // q_group_div, 128, 576) \
-            or kv.shape[1] != 576:
-        raise ValueError("q must be [ng/q_group_div,128,576] and kv [s_kv,(1,)576]")
-    if q.stride(2) != 1 or q.stride(1) * 128 != q.stride(0) or kv.stride(1) != 1 or indices.stride(1) != 1:
-        raise ValueError("q rows must be evenly pitched; q/kv/indices need unit inner stride")
-    topk = indices.shape[1]
     G = 128 // int(h_per_q)
+    q_strides = out_strides = (0, 0)
+    if in_place_heads:
+        if q_group_div < 1 or ng % q_group_div or q.dim() != 3 or q.shape[0] != ng // q_group_div * G \
+                or q.shape[1] < h_per_q or q.shape[2] != 576 or kv.shape[1] != 576:
+            raise ValueError("in_place_heads: q must be [ng*G/q_group_div, H_padded >= h_per_q, 576]")
+        if tuple(out.shape[:1]) != (ng * G,) or out.shape[1] < h_per_q or out.shape[2] != 512:
+            raise ValueError("in_place_heads: out must be [ng*G, H_padded >= h_per_q, 512]")
+        if q.stride(2) != 1 or out.stride(2) != 1 or kv.stride(1) != 1 or indices.stride(1) != 1:
+            raise ValueError("q / out / kv / indices need unit inner stride")
+        q_strides = (q.stride(0), q.stride(1))
+        out_strides = (out.stride(0), out.stride(1))
+    else:
+        if q_group_div < 1 or ng % q_group_div or tuple(q.shape) != (ng // q_group_div, 128, 576) \
+                or kv.shape[1] != 576:
+            raise ValueError("q must be [ng/q_group_div,128,576] and kv [s_kv,(1,)576]")
+        if q.stride(2) != 1 or q.stride(1) * 128 != q.stride(0) or kv.stride(1) != 1 or indices.stride(1) != 1:
+            raise ValueError("q rows must be evenly pitched; q/kv/indices need unit inner stride")
+    topk = indices.shape[1]
     if memb_qm is None and topk_length_per_q is None:
         raise ValueError("memb_qm or topk_length_per_q is required")
     if memb_qm is not None:
         _need(memb_qm, "memb_qm", (torch.int32, torch.uint32))
         if memb_qm.numel() != ng * G * (topk // 32) or not memb_qm.is_contiguous():
             raise ValueError("memb_qm must be a contiguous [ng, G, topk/32]")
-    if tuple(out.shape) != (ng, 128, 512) or not out.is_contiguous():
+    if not in_place_heads and (tuple(out.shape) != (ng, 128, 512) or not out.is_contiguous()):
         raise ValueError("out must be a contiguous [ng,128,512]")
     if lse.numel() != ng * 128 or not lse.is_contiguous():
         raise ValueError("lse must be a contiguous [ng,128]")
@@ -189,7 +209,8 @@ def masked_mla_fp8_out(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor,
         _need(topk_length_per_q, "topk_length_per_q", torch.int32, 2)
         if tuple(topk_length_per_q.shape) != (ng, G) or not topk_length_per_q.is_contiguous():
             raise ValueError("topk_length_per_q must be a contiguous [ng, G]")
-    extras = attn_sink is not None or topk_length_per_q is not None or q_group_div != 1
+    extras = attn_sink is not None or topk_length_per_q is not None or q_group_div != 1 or in_place_heads
+    q_row_stride = q.stride(1)
     with torch.cuda.device(q.device):
         if peer_outs:
             if extras:
@@ -208,8 +229,9 @@ def masked_mla_fp8_out(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor,
             rc = _lib.lib().litedsa_masked_mla_fp8_ex(
                 _ptr(q), _ptr(kv), _ptr(indices), float(sm_scale), float(out_scale),
                 _ptr(topk_length), _ptr(memb_qm), int(h_per_q), _ptr(out), _ptr(max_logits),
-                _ptr(lse), ng, kv.shape[0], topk, q.stride(1), kv.stride(0), indices.stride(0),
-                _ptr(attn_sink), _ptr(topk_length_per_q), q_group_div, _stream(q))
+                _ptr(lse), ng, kv.shape[0], topk, q_row_stride, kv.stride(0), indices.stride(0),
+                _ptr(attn_sink), _ptr(topk_length_per_q), q_group_div, q_strides[0], q_strides[1],
+                out_strides[0], out_strides[1], _stream(q))
         else:
             rc = _lib.lib().litedsa_masked_mla_fp8(
                 _ptr(q), _ptr(kv), _ptr(indices), float(sm_scale), float(out_scale),
@@ -289,16 +311,47 @@ def dsv4_masked_mla_bf16_out(q: torch.Tensor, kv: torch.Tensor, indices: torch.T
                              pref: torch.Tensor, win_lo: torch.Tensor, win_hi: torch.Tensor,
                              counts: torch.Tensor, sm_scale: float, h_per_q: int,
                              out: torch.Tensor, lse: torch.Tensor,
-                             attn_sink: Optional[torch.Tensor]) -> None:
+                             attn_sink: Optional[torch.Tensor], *, in_place_heads: bool = False) -> None:
     """The reference's DSv4 operator, same argument order
     (kernels/b200/dsa/litedsa_dsv4.cu:50-55): q [ng,128,d] bf16, kv [s_kv,(1,)d] bf16 flat
     workspace, indices [ng,(1,)topk] i32 ascending union rows (-1 padded, topk % 64 == 0),
     pref / win_lo / win_hi [ng,G] i32 rank ranges per token, counts [ng] i32, out
     [ng,128,512] bf16, lse [ng,128] f32, attn_sink [128] f32 or None.  d = 512 (the
-    reference's width) or 576."""
-    kv, indices, ng, d = _bf16_common(q, kv, indices, out, lse)
-    topk = indices.shape[1]
+    reference's width) or 576.
+
+    ``in_place_heads``: q is the model's own ``[T, H_padded, d]`` tensor and out its
+    ``[T, H_padded, 512]`` tensor with ``h_per_q`` real heads per token (unit inner stride);
+    the kernel reads and writes them in place, so the pack copy of q and the unpack copy of out
+    that the reference's packed path makes (kernels/b200/dsa/DSV4_ZEROCOPY_PLAN.md:12-22) go
+    away.  lse stays packed ``[ng,128]``."""
     G = 128 // int(h_per_q)
+    strides = (0, 0, 0, 0)
+    if in_place_heads:
+        _need(q, "q", torch.bfloat16, 3)
+        _need(out, "out", torch.bfloat16, 3)
+        if indices.dim() == 3:
+            indices = indices[:, 0]
+        ng = indices.shape[0]
+        d = q.shape[2]
+        if q.shape[0] != ng * G or q.shape[1] < h_per_q or d not in (512, 576) or q.stride(2) != 1:
+            raise ValueError("in_place_heads: q must be [ng*G, H_padded >= h_per_q, d] with unit inner stride")
+        if out.shape[0] != ng * G or out.shape[1] < h_per_q or out.shape[2] != 512 or out.stride(2) != 1:
+            raise ValueError("in_place_heads: out must be [ng*G, H_padded >= h_per_q, 512] with unit inner stride")
+        strides = (q.stride(0), q.stride(1), out.stride(0), out.stride(1))
+        q_row_stride = q.stride(1)
+        _need(kv, "kv", torch.bfloat16)
+        _need(indices, "indices", torch.int32)
+        _need(lse, "lse", torch.float32)
+        if kv.dim() == 3:
+            kv = kv[:, 0]
+        if kv.shape[1] != d or kv.stride(1) != 1 or indices.stride(1) != 1:
+            raise ValueError("kv must be [s_kv,(1,)d] and indices [ng,(1,)topk] with unit inner stride")
+        if lse.numel() != ng * 128 or not lse.is_contiguous():
+            raise ValueError("lse must be a contiguous [ng,128]")
+    else:
+        kv, indices, ng, d = _bf16_common(q, kv, indices, out, lse)
+        q_row_stride = q.stride(1)
+    topk = indices.shape[1]
     for name, t in (("pref", pref), ("win_lo", win_lo), ("win_hi", win_hi)):
         _need(t, name, torch.int32)
         if t.numel() != ng * G or not t.is_contiguous():
@@ -310,7 +363,8 @@ def dsv4_masked_mla_bf16_out(q: torch.Tensor, kv: torch.Tensor, indices: torch.T
         rc = _lib.lib().litedsa_dsv4_masked_mla_bf16(
             _ptr(q), _ptr(kv), _ptr(indices), _ptr(pref), _ptr(win_lo), _ptr(win_hi), _ptr(counts),
             float(sm_scale), int(h_per_q), _ptr(out), _ptr(lse), _ptr(_sink128(attn_sink)), ng,
-            kv.shape[0], topk, d, q.stride(1), kv.stride(0), indices.stride(0), _stream(q))
+            kv.shape[0], topk, d, q_row_stride, kv.stride(0), indices.stride(0), strides[0], strides[1],
+            strides[2], strides[3], _stream(q))
     check(rc, "dsv4_masked_mla_bf16")
 
 
@@ -622,7 +676,8 @@ def sparse_prefill_host(q_host: torch.Tensor, kv_cache_fp8: torch.Tensor, topk_h
 # --------------------------------------------------------------------------- DSv4 BF16 two-range attention
 def dsv4_c128a_bf16(q: torch.Tensor, kv_compressed: Optional[torch.Tensor], kv_raw: torch.Tensor,
                     q_pos0: int, sm_scale: float, *, window: int = 128, ratio: int = 128,
-                    attn_sink: Optional[torch.Tensor] = None):
+                    attn_sink: Optional[torch.Tensor] = None, heads: Optional[int] = None,
+                    out: Optional[torch.Tensor] = None):
     """Packed BF16 attention over (compressed prefix, sliding window).
 
     q [T,h,576] bf16 for T consecutive tokens starting at position ``q_pos0``; token at
@@ -631,16 +686,25 @@ def dsv4_c128a_bf16(q: torch.Tensor, kv_compressed: Optional[torch.Tensor], kv_r
     exp(sink) to the output normaliser.  Returns ``(out [T,h,512] bf16, lse [T,h] f32)``.
     The reference's counterpart takes a gathered index list plus rank ranges
     (kernels/b200/dsa/litedsa_dsv4.cu:50-55); here the ranges are contiguous memory.
+
+    ``heads`` (zero-copy for tensor-parallel callers): q is ``[T, H_padded, 576]`` of which only
+    the first ``heads`` head slots per token are real; it is read in place (any strides with unit
+    inner stride), and the result is written in place into ``out`` ``[T, H_padded, 512]`` when
+    given (else a dense ``[T, heads, 512]`` is returned).  lse is ``[T, heads]``.
     """
     _need(q, "q", torch.bfloat16, 3)
     _need(kv_raw, "kv_raw", torch.bfloat16, 2)
-    T, h, d = q.shape
-    if d != 576 or 128 % h or 128 // h > 16 or kv_raw.shape[1] != 576:
+    T, hq, d = q.shape
+    h = hq if heads is None else int(heads)
+    if d != 576 or h > hq or 128 % h or 128 // h > 16 or kv_raw.shape[1] != 576:
         raise ValueError("q must be [T,h,576] (h | 128, 128/h <= 16) and kv_raw [S,576]")
     G = 128 // h
     if T % G:
         raise ValueError("token count must be a multiple of 128 // heads")
-    q = q.contiguous()
+    if heads is None:
+        q = q.contiguous()
+    elif q.stride(2) != 1:
+        raise ValueError("q needs unit inner stride")
     n_comp = 0
     if kv_compressed is not None and kv_compressed.shape[0] > 0:
         _need(kv_compressed, "kv_compressed", torch.bfloat16, 2)
@@ -656,16 +720,22 @@ def dsv4_c128a_bf16(q: torch.Tensor, kv_compressed: Optional[torch.Tensor], kv_r
             raise ValueError("attn_sink must be [heads]")
         sink = attn_sink.repeat(G).contiguous()            # per packed row
     ng = T // G
-    out = torch.empty((ng, 128, 512), dtype=torch.bfloat16, device=q.device)
+    in_place_out = out is not None
+    if in_place_out:
+        _need(out, "out", torch.bfloat16, 3)
+        if out.shape[0] != T or out.shape[1] < h or out.shape[2] != 512 or out.stride(2) != 1:
+            raise ValueError("out must be [T, H_padded >= heads, 512] with unit inner stride")
+    else:
+        out = torch.empty((T, h, 512), dtype=torch.bfloat16, device=q.device)
     lse = torch.empty((ng, 128), dtype=torch.float32, device=q.device)
     with torch.cuda.device(q.device):
         rc = _lib.lib().litedsa_dsv4_c128a_bf16(
             _ptr(q), _ptr(kv_compressed) if n_comp else None, _ptr(kv_raw), ng, h, n_comp,
             kv_raw.shape[0], int(q_pos0), int(window), int(ratio), float(sm_scale), _ptr(sink),
-            _ptr(out), _ptr(lse), 576, kv_compressed.stride(0) if n_comp else 576, kv_raw.stride(0),
-            _stream(q))
+            _ptr(out), _ptr(lse), q.stride(1), kv_compressed.stride(0) if n_comp else 576, kv_raw.stride(0),
+            q.stride(0), q.stride(1), out.stride(0), out.stride(1), _stream(q))
     check(rc, "dsv4_c128a_bf16")
-    return out.view(T, h, 512), lse.view(T, h)
+    return out, lse.view(T, h)
 
 
 def dsv4_status(reset: bool = False, device=None) -> Tuple[int, int, int, int]:

@@ -377,8 +377,10 @@ masked_mla_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
           if (lane == 0) {
             if (cta == 0) mbar_arrive_expect_tx(&ms.q_full, 2 * PL::kQBytes);
             for (int j = 0; j < kChunks; ++j)
-              tma_load_2d_pair_hint(sbase + PL::kOffQ + j * kQChunkBytes, &map_q, 64 * j,
-                                    q_tile * 128 + (int)cta * 64, a_q_full, pol_stream);
+              // this CTA's 64 rows of the tile = (token, head) pairs starting at row 64 cta
+              tma_load_3d_pair_hint(sbase + PL::kOffQ + j * kQChunkBytes, &map_q, 64 * j,
+                                    (64 * (int)cta) % p.h_per_q, q_tile * p.G + (64 * (int)cta) / p.h_per_q,
+                                    a_q_full, pol_stream);
           }
           __syncwarp();
           q_tile += ncl;
@@ -597,7 +599,9 @@ masked_mla_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
       tc_fence_after();
       const float oscale = ms.oscale[it & 1][r];
       const uint32_t emask = oscale != 0.f ? 0xffffffffu : 0u;
-      const int out_y = tile * 128 + (int)cta * 64 + 32 * (warp & 1);
+      // this warp's 32 rows of the tile = (token, head) pairs starting at row r0
+      const int r0 = (int)cta * 64 + 32 * (warp & 1);
+      const int out_head = r0 % p.h_per_q, out_tok = tile * p.G + r0 / p.h_per_q;
       float ob[2][32];
       tmem_ld32(ocol, ob[0]);
 #pragma unroll
@@ -628,7 +632,7 @@ masked_mla_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          tma_store_2d(&map_out, sbase + stage_off, 256 * h + 32 * cc, out_y);
+          tma_store_3d(&map_out, sbase + stage_off, 256 * h + 32 * cc, out_head, out_tok);
           bulk_commit_group();
         }
       }
@@ -710,6 +714,8 @@ struct Args {
   int ng, s_kv, topk, d, h_per_q;
   int64_t q_row_stride, kv_row_stride, idx_row_stride;     // ELEMENTS
   float sm_scale;
+  // in-place addressing of q / out inside [T, H_padded, d] tensors (ELEMENTS, 0 = dense packed)
+  int64_t q_token_stride, q_head_stride, out_token_stride, out_head_stride;
 };
 
 // argument rules shared by both entry points (no CUDA call)
@@ -725,6 +731,11 @@ static int check(const Args& a) {
     return LITEDSA_ERR_UNSUPPORTED;
   if (((uintptr_t)a.q | (uintptr_t)a.kv | (uintptr_t)a.out) & 15) return LITEDSA_ERR_UNSUPPORTED;
   if (a.idx_row_stride < a.topk) return LITEDSA_ERR_UNSUPPORTED;
+  if (a.q_token_stride < 0 || a.q_head_stride < 0 || a.out_token_stride < 0 || a.out_head_stride < 0)
+    return LITEDSA_ERR_SHAPE;
+  if ((a.q_head_stride && (a.q_head_stride < a.d || a.q_head_stride % 8)) || a.q_token_stride % 8 ||
+      (a.out_head_stride && (a.out_head_stride < kDV || a.out_head_stride % 8)) || a.out_token_stride % 8)
+    return LITEDSA_ERR_UNSUPPORTED;
   return LITEDSA_OK;
 }
 
@@ -733,9 +744,17 @@ static int launch(const Args& a, cudaStream_t stream) {
   using PL = Plan<kD>;
   CUtensorMap mq, mout;
   const auto BF = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  if (!make_map_2d(&mq, a.q, BF, kD, (uint64_t)a.ng * 128, (uint64_t)a.q_row_stride * 2, 64, 64) ||
+  // q and out are addressed as (dim, head, token): row r of a tile is (token r / h, head r % h),
+  // which covers the dense packed layout and the in-place layout with padded head slots alike
+  const int h = a.h_per_q, G = 128 / h;
+  const uint64_t q_hs = (a.q_head_stride ? (uint64_t)a.q_head_stride : (uint64_t)a.q_row_stride) * 2;
+  const uint64_t q_ts = a.q_token_stride ? (uint64_t)a.q_token_stride * 2 : (uint64_t)h * q_hs;
+  const uint64_t o_hs = (a.out_head_stride ? (uint64_t)a.out_head_stride : (uint64_t)kDV) * 2;
+  const uint64_t o_ts = a.out_token_stride ? (uint64_t)a.out_token_stride * 2 : (uint64_t)h * o_hs;
+  const uint32_t qb_h = (uint32_t)min(h, 64), ob_h = (uint32_t)min(h, 32);
+  if (!make_map_3d(&mq, a.q, BF, kD, (uint64_t)h, (uint64_t)a.ng * G, q_hs, q_ts, 64, qb_h, 64 / qb_h) ||
       // out leaves as boxes of 32 rows x 32 dims (64 bytes wide, 64-byte swizzle)
-      !make_map_2d(&mout, a.out, BF, kDV, (uint64_t)a.ng * 128, (uint64_t)kDV * 2, 32, 32,
+      !make_map_3d(&mout, a.out, BF, kDV, (uint64_t)h, (uint64_t)a.ng * G, o_hs, o_ts, 32, ob_h, 32 / ob_h,
                    CU_TENSOR_MAP_SWIZZLE_64B))
     return LITEDSA_ERR_CUDA;
   Params p;
@@ -803,18 +822,24 @@ __global__ void __launch_bounds__(256) dequant_kv656_kernel(const uint8_t* __res
 // The reference's DSv4 operator with its own argument list
 //   dsv4_masked_mla_bf16(q, kv, indices, pref, win_lo, win_hi, counts, sm_scale, h_per_q,
 //                        out, lse, attn_sink)        (kernels/b200/dsa/litedsa_dsv4.cu:50-121)
-// tensor shapes and strides passed as integers.  d = 512 as in the reference, or 576.
+// tensor shapes and strides passed as integers.  d = 512 as in the reference, or 576.  The four
+// trailing strides (ELEMENTS, 0 = dense packed) address q and out in place inside
+// [T, H_padded, d] tensors with h_per_q real heads per token: the zero-copy form the reference
+// planned for this operator (kernels/b200/dsa/DSV4_ZEROCOPY_PLAN.md:50-76).
 extern "C" int litedsa_dsv4_masked_mla_bf16(const void* q, const void* kv, const int32_t* indices,
                                             const int32_t* pref, const int32_t* win_lo,
                                             const int32_t* win_hi, const int32_t* counts,
                                             float sm_scale, int h_per_q, void* out, float* lse,
                                             const float* attn_sink, int ng, int s_kv, int topk,
                                             int d, int64_t q_row_stride, int64_t kv_row_stride,
-                                            int64_t indices_row_stride, void* stream) {
+                                            int64_t indices_row_stride, int64_t q_token_stride,
+                                            int64_t q_head_stride, int64_t out_token_stride,
+                                            int64_t out_head_stride, void* stream) {
   using namespace lt::b16;
   if (!pref || !win_lo || !win_hi || !counts) return LITEDSA_ERR_ARG;
   Args a{q, kv, indices, counts, nullptr, pref, win_lo, win_hi, attn_sink, out, nullptr, lse,
-         ng, s_kv, topk, d, h_per_q, q_row_stride, kv_row_stride, indices_row_stride, sm_scale};
+         ng, s_kv, topk, d, h_per_q, q_row_stride, kv_row_stride, indices_row_stride, sm_scale,
+         q_token_stride, q_head_stride, out_token_stride, out_head_stride};
   return run(a, stream);
 }
 
@@ -831,7 +856,8 @@ extern "C" int litedsa_masked_mla_bf16(const void* q, const void* kv, const int3
   using namespace lt::b16;
   if (!memb_qm) return LITEDSA_ERR_ARG;
   Args a{q, kv, indices, topk_length, memb_qm, nullptr, nullptr, nullptr, attn_sink, out, max_logits,
-         lse, ng, s_kv, topk, d, h_per_q, q_row_stride, kv_row_stride, indices_row_stride, sm_scale};
+         lse, ng, s_kv, topk, d, h_per_q, q_row_stride, kv_row_stride, indices_row_stride, sm_scale,
+         0, 0, 0, 0};
   return run(a, stream);
 }
 

@@ -293,6 +293,7 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
       const uint32_t a_q_full = mapa(smem_u32(&ms.q_full), 0);
       const uint32_t a_k_full[2] = {mapa(smem_u32(&ms.k_full[0]), 0), mapa(smem_u32(&ms.k_full[1]), 0)};
       const uint32_t a_v_full[2] = {mapa(smem_u32(&ms.v_full[0]), 0), mapa(smem_u32(&ms.v_full[1]), 0)};
+      const uint64_t pol_stream = l2_policy_evict_first();     // q streams through once
       int kb0 = 0, it = 0;
       for (int tile = cid; tile < p.ng; tile += ncl, ++it) {
         const TilePlan tp = plan_tile(p, tile);
@@ -300,9 +301,11 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
         // the previous tile's Q must have been consumed by its last QK^T
         if (it > 0) mbar_wait(&ms.q_free, (it - 1) & 1, wt, kSiteQFree, it);
         if (cta == 0) mbar_arrive_expect_tx(&ms.q_full, 2 * kQBytes);
+        // this CTA's 64 rows of the tile = (token, head) pairs starting at row 64 cta
         for (int j = 0; j < kQChunks; ++j)
-          tma_load_2d_pair(sbase + kOffQ + j * kQChunkBytes, &map_q, 64 * j, tile * 128 + (int)cta * 64,
-                           a_q_full);
+          tma_load_3d_pair_hint(sbase + kOffQ + j * kQChunkBytes, &map_q, 64 * j,
+                                (64 * (int)cta) % p.h_per_q, tile * p.G + (64 * (int)cta) / p.h_per_q,
+                                a_q_full, pol_stream);
         for (int k = 0; k < nb; ++k) {
           const int kb = kb0 + k;
           const int s = kb & 1;
@@ -349,7 +352,9 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
       tc_fence_after();
       const float oscale = ms.oscale[it & 1][r];
       const uint32_t emask = oscale != 0.f ? 0xffffffffu : 0u;
-      const int out_y = tile * 128 + (int)cta * 64 + 32 * (warp & 1);
+      // this warp's 32 rows of the tile = (token, head) pairs starting at row r0
+      const int r0 = (int)cta * 64 + 32 * (warp & 1);
+      const int out_head = r0 % p.h_per_q, out_tok = tile * p.G + r0 / p.h_per_q;
       float ob[2][32];
       tmem_ld32(ocol, ob[0]);
 #pragma unroll
@@ -380,7 +385,7 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          tma_store_2d(&map_out, sbase + stage_off, 256 * h + 32 * cc, out_y);
+          tma_store_3d(&map_out, sbase + stage_off, 256 * h + 32 * cc, out_head, out_tok);
           bulk_commit_group();
         }
       }
@@ -527,7 +532,9 @@ extern "C" int litedsa_dsv4_c128a_bf16(const void* q, const void* kv_comp, const
                                        int window, int ratio, float sm_scale,
                                        const float* attn_sink, void* out, float* lse,
                                        int64_t q_row_stride, int64_t kc_row_stride,
-                                       int64_t kr_row_stride, void* stream) {
+                                       int64_t kr_row_stride, int64_t q_token_stride,
+                                       int64_t q_head_stride, int64_t out_token_stride,
+                                       int64_t out_head_stride, void* stream) {
   using namespace lt;
   using namespace lt::dsv4;
   if (!q || !kv_raw || !out || !lse) return LITEDSA_ERR_ARG;
@@ -544,18 +551,30 @@ extern "C" int litedsa_dsv4_c128a_bf16(const void* q, const void* kv_comp, const
     return LITEDSA_ERR_UNSUPPORTED;
   if (((uintptr_t)q | (uintptr_t)kv_raw | (uintptr_t)kv_comp | (uintptr_t)out) & 15)
     return LITEDSA_ERR_UNSUPPORTED;
+  if (q_token_stride < 0 || q_head_stride < 0 || out_token_stride < 0 || out_head_stride < 0)
+    return LITEDSA_ERR_SHAPE;
+  if ((q_head_stride && (q_head_stride < kD || q_head_stride % 8)) || q_token_stride % 8 ||
+      (out_head_stride && (out_head_stride < kDV || out_head_stride % 8)) || out_token_stride % 8)
+    return LITEDSA_ERR_UNSUPPORTED;
   const void* kc = n_comp > 0 ? kv_comp : kv_raw;      // never dereferenced when n_comp == 0
   const uint64_t kc_rows = n_comp > 0 ? (uint64_t)n_comp : 1;
   const int64_t kc_pitch = n_comp > 0 ? kc_row_stride : kr_row_stride;
   CUtensorMap mq, mkc32, mkr32, mkc64, mkr64, mout;
   const auto BF = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  if (!make_map_2d(&mq, q, BF, kD, (uint64_t)ng * 128, (uint64_t)q_row_stride * 2, 64, 64) ||
+  // q and out are addressed as (dim, head, token): row r of a tile is (token r / h, head r % h),
+  // which covers the dense packed layout and the in-place layout with padded head slots alike
+  const uint64_t q_hs = (q_head_stride ? (uint64_t)q_head_stride : (uint64_t)q_row_stride) * 2;
+  const uint64_t q_ts = q_token_stride ? (uint64_t)q_token_stride * 2 : (uint64_t)h_per_q * q_hs;
+  const uint64_t o_hs = (out_head_stride ? (uint64_t)out_head_stride : (uint64_t)kDV) * 2;
+  const uint64_t o_ts = out_token_stride ? (uint64_t)out_token_stride * 2 : (uint64_t)h_per_q * o_hs;
+  const uint32_t qb_h = (uint32_t)min(h_per_q, 64), ob_h = (uint32_t)min(h_per_q, 32);
+  if (!make_map_3d(&mq, q, BF, kD, (uint64_t)h_per_q, (uint64_t)ng * G, q_hs, q_ts, 64, qb_h, 64 / qb_h) ||
       !make_map_2d(&mkc32, kc, BF, kD, kc_rows, (uint64_t)kc_pitch * 2, 64, 32) ||
       !make_map_2d(&mkr32, kv_raw, BF, kD, (uint64_t)s_raw, (uint64_t)kr_row_stride * 2, 64, 32) ||
       !make_map_2d(&mkc64, kc, BF, kD, kc_rows, (uint64_t)kc_pitch * 2, 64, 64) ||
       !make_map_2d(&mkr64, kv_raw, BF, kD, (uint64_t)s_raw, (uint64_t)kr_row_stride * 2, 64, 64) ||
       // out leaves as boxes of 32 rows x 32 dims (64 bytes wide, 64-byte swizzle)
-      !make_map_2d(&mout, out, BF, kDV, (uint64_t)ng * 128, (uint64_t)kDV * 2, 32, 32,
+      !make_map_3d(&mout, out, BF, kDV, (uint64_t)h_per_q, (uint64_t)ng * G, o_hs, o_ts, 32, ob_h, 32 / ob_h,
                    CU_TENSOR_MAP_SWIZZLE_64B))
     return LITEDSA_ERR_CUDA;
   Params p;

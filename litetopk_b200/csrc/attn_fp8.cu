@@ -432,8 +432,11 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
           if (lane == 0) {
             if (cta == 0) mbar_arrive_expect_tx(&ms.q_full, 2 * kQBytes);
             for (int j = 0; j < kChunks; ++j)
-              tma_load_2d_pair_hint(sbase + kOffQ + j * kChunkBytes, &map_q, 128 * j,
-                                    (q_tile / p.q_group_div) * 128 + (int)cta * 64, a_q_full, pol_stream);
+              // this CTA's 64 rows of the tile = (token, head) pairs starting at row 64 cta
+              tma_load_3d_pair_hint(sbase + kOffQ + j * kChunkBytes, &map_q, 128 * j,
+                                    (64 * (int)cta) % p.h_per_q,
+                                    (q_tile / p.q_group_div) * p.G + (64 * (int)cta) / p.h_per_q,
+                                    a_q_full, pol_stream);
           }
           __syncwarp();
           q_tile += ncl;
@@ -631,7 +634,9 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
       tc_fence_after();
       const float oscale = ms.oscale[it & 1][e_r];
       const uint32_t emask = oscale != 0.f ? 0xffffffffu : 0u;
-      const int out_y = tile * 128 + (int)cta * 64 + 32 * (warp & 1);
+      // this warp's 32 rows of the tile = (token, head) pairs starting at row r0
+      const int r0 = (int)cta * 64 + 32 * (warp & 1);
+      const int out_head = r0 % p.h_per_q, out_tok = tile * p.G + r0 / p.h_per_q;
       float ob[2][32];
       tmem_ld32(e_ocol, ob[0]);
 #pragma unroll
@@ -669,7 +674,7 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
           __syncwarp();
           if (lane == 0) {
             for (int d = 0; d < p.n_out; ++d)
-              tma_store_2d_hint(&omaps.m[d], sbase + slice, 256 * e_h + 64 * (cc >> 1), out_y, pol_stream);
+              tma_store_3d_hint(&omaps.m[d], sbase + slice, 256 * e_h + 64 * (cc >> 1), out_head, out_tok, pol_stream);
             bulk_commit_group();
           }
         }
@@ -768,14 +773,23 @@ static int launch_fp8(const Fp8Args& a, void* const* outs, int n_out, cudaStream
   OutMaps omaps;
   // out is stored as boxes of 32 rows x 64 dims (128 bytes wide, 128-byte swizzle); only the
   // destinations in use are encoded, the unused slots repeat the first map
+  // q and out are addressed as (dim, head, token): row r of a tile is (token r / h, head r % h),
+  // which covers the dense packed layout and the in-place layout with padded head slots alike
+  const int h = a.h_per_q, G = 128 / h;
+  const int qdiv = a.q_group_div > 0 ? a.q_group_div : 1;
+  const uint64_t q_hs = a.q_head_stride ? (uint64_t)a.q_head_stride : (uint64_t)a.q_row_stride;
+  const uint64_t q_ts = a.q_token_stride ? (uint64_t)a.q_token_stride : (uint64_t)h * q_hs;
+  const uint64_t o_hs = (a.out_head_stride ? (uint64_t)a.out_head_stride : (uint64_t)kDV) * 2;
+  const uint64_t o_ts = a.out_token_stride ? (uint64_t)a.out_token_stride * 2 : (uint64_t)h * o_hs;
+  const uint32_t ob_h = (uint32_t)min(h, 32);
   for (int d = 0; d < n_out; ++d)
-    if (!make_map_2d(&omaps.m[d], outs[d], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, kDV,
-                     (uint64_t)a.ng * 128, (uint64_t)kDV * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B))
+    if (!make_map_3d(&omaps.m[d], outs[d], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, kDV, (uint64_t)h,
+                     (uint64_t)a.ng * G, o_hs, o_ts, 64, ob_h, 32 / ob_h, CU_TENSOR_MAP_SWIZZLE_128B))
       return LITEDSA_ERR_CUDA;
   for (int d = n_out; d < kMaxOutputs; ++d) omaps.m[d] = omaps.m[0];
-  const int qdiv = a.q_group_div > 0 ? a.q_group_div : 1;
-  if (!make_map_2d(&map_q, a.q8, CU_TENSOR_MAP_DATA_TYPE_UINT8, kDQK,
-                   (uint64_t)(a.ng / qdiv) * 128, (uint64_t)a.q_row_stride, 128, 64))
+  const uint32_t qb_h = (uint32_t)min(h, 64);
+  if (!make_map_3d(&map_q, a.q8, CU_TENSOR_MAP_DATA_TYPE_UINT8, kDQK, (uint64_t)h,
+                   (uint64_t)(a.ng / qdiv) * G, q_hs, q_ts, 128, qb_h, 64 / qb_h))
     return LITEDSA_ERR_CUDA;
   AttnParams p;
   p.memb = a.memb_qm; p.len_per_q = a.topk_length_per_q; p.sink = a.attn_sink; p.q_group_div = qdiv;
@@ -808,6 +822,12 @@ int check_fp8_args(const Fp8Args& a) {
     return LITEDSA_ERR_UNSUPPORTED;
   if (((uintptr_t)a.q8 | (uintptr_t)a.kv8 | (uintptr_t)a.indices) & 15) return LITEDSA_ERR_UNSUPPORTED;
   if (a.indices_row_stride < a.topk || a.indices_row_stride % 4) return LITEDSA_ERR_UNSUPPORTED;
+  // in-place addressing: TMA wants 16-byte multiples for every pitch
+  if (a.q_token_stride < 0 || a.q_head_stride < 0 || a.out_token_stride < 0 || a.out_head_stride < 0)
+    return LITEDSA_ERR_SHAPE;
+  if ((a.q_head_stride && (a.q_head_stride < kDQK || a.q_head_stride % 16)) || a.q_token_stride % 16 ||
+      (a.out_head_stride && (a.out_head_stride < kDV || a.out_head_stride % 8)) || a.out_token_stride % 8)
+    return LITEDSA_ERR_UNSUPPORTED;
   return LITEDSA_OK;
 }
 
@@ -848,6 +868,10 @@ extern "C" int litedsa_masked_mla_fp8(const void* q8, const void* kv8, const int
 // output normaliser (litedsa_attention_sm100.cuh:2127-2133); topk_length_per_q [ng, G] bounds
 // each token to a causal prefix of the union ranks and may replace memb_qm (:1378-1385,
 // :1988-1996); q_group_div consecutive tiles share one Q tile (KV split, :1383-1385, :1909).
+// q_token_stride / q_head_stride / out_token_stride / out_head_stride (ELEMENTS, 0 = dense packed)
+// address q and out in place inside [T, H_padded, d] tensors that hold h_per_q real heads per
+// token, which removes the pack / unpack copies around the kernel
+// (kernels/b200/dsa/DSV4_ZEROCOPY_PLAN.md:12-22, 50-76).
 extern "C" int litedsa_masked_mla_fp8_ex(const void* q8, const void* kv8, const int32_t* indices,
                                          float sm_scale, float out_scale,
                                          const int32_t* topk_length, const uint32_t* memb_qm,
@@ -855,12 +879,15 @@ extern "C" int litedsa_masked_mla_fp8_ex(const void* q8, const void* kv8, const 
                                          int ng, int s_kv, int topk, int64_t q_row_stride,
                                          int64_t kv_row_stride, int64_t indices_row_stride,
                                          const float* attn_sink, const int32_t* topk_length_per_q,
-                                         int q_group_div, void* stream) {
+                                         int q_group_div, int64_t q_token_stride,
+                                         int64_t q_head_stride, int64_t out_token_stride,
+                                         int64_t out_head_stride, void* stream) {
   using namespace lt;
   if (!out) return LITEDSA_ERR_ARG;
   Fp8Args a{q8, kv8, indices, sm_scale, out_scale, topk_length, memb_qm, h_per_q, max_logits, lse,
             ng, s_kv, topk, q_row_stride, kv_row_stride, indices_row_stride, attn_sink,
-            topk_length_per_q, q_group_div};
+            topk_length_per_q, q_group_div, q_token_stride, q_head_stride, out_token_stride,
+            out_head_stride};
   void* outs[1] = {out};
   return run_fp8(a, outs, 1, stream);
 }

@@ -39,6 +39,9 @@ struct Fp8Args {
   const float* attn_sink;
   const int32_t* topk_length_per_q;
   int q_group_div;
+  // in-place ("zero-copy") addressing of q and out inside [T, H_padded, d] tensors that hold
+  // h_per_q real heads per token: strides in ELEMENTS, 0 = the dense packed layout
+  int64_t q_token_stride, q_head_stride, out_token_stride, out_head_stride;
 };
 int check_fp8_args(const Fp8Args& a);                                   // no CUDA call
 int run_fp8(const Fp8Args& a, void* const* outs, int n_outs, void* stream);
@@ -189,6 +192,29 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_smem, const CUtens
       " [%0], [%1, {%2, %3}], [%4];"
       ::"r"(dst_smem), "l"(map), "r"(x), "r"(y), "r"(mbar_cluster_addr)
       : "memory");
+}
+
+// tiled 3-D load (x, y, z) into this CTA's smem, completion bytes to a barrier that may be the
+// pair leader's (.cta_group::2 form).  Used for Q tiles addressed as (dim, head, token).
+__device__ __forceinline__ void tma_load_3d_pair_hint(uint32_t dst_smem, const CUtensorMap* map,
+                                                      int x, int y, int z, uint32_t mbar_cluster_addr,
+                                                      uint64_t pol) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cta.global.tile.mbarrier::complete_tx::bytes.cta_group::2"
+      ".L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], %6;"
+      ::"r"(dst_smem), "l"(map), "r"(x), "r"(y), "r"(z), "r"(mbar_cluster_addr), "l"(pol)
+      : "memory");
+}
+// TMA 3-D tile store shared -> global (bulk async-group completion)
+__device__ __forceinline__ void tma_store_3d_hint(const void* map, uint32_t src_smem, int x, int y,
+                                                  int z, uint64_t pol) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group.L2::cache_hint"
+               " [%0, {%2, %3, %4}], [%1], %5;"
+               :: "l"(map), "r"(src_smem), "r"(x), "r"(y), "r"(z), "l"(pol) : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const void* map, uint32_t src_smem, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               :: "l"(map), "r"(src_smem), "r"(x), "r"(y), "r"(z) : "memory");
 }
 
 // TMA tile store shared -> global (bulk async-group completion)

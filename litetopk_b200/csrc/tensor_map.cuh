@@ -44,4 +44,26 @@ inline bool make_map_2d(CUtensorMap* map, const void* base, CUtensorMapDataType 
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// 3-D tensor [tokens, heads, cols] (cols innermost, unit stride) of `elem_bytes`-wide elements:
+// heads `head_pitch_bytes` apart, tokens `token_pitch_bytes` apart; box = box_cols x box_heads x
+// box_tokens.  This is how a 128-row attention tile is addressed in place: its row r is
+// (token r / h, head r % h) of a [T, H_padded, d] tensor that holds only h real heads per
+// token -- the layout a tensor-parallel model hands over
+// (kernels/b200/dsa/DSV4_ZEROCOPY_PLAN.md:12-22) -- and equally of the dense packed layout.
+inline bool make_map_3d(CUtensorMap* map, const void* base, CUtensorMapDataType dtype,
+                        uint64_t cols, uint64_t heads, uint64_t tokens, uint64_t head_pitch_bytes,
+                        uint64_t token_pitch_bytes, uint32_t box_cols, uint32_t box_heads,
+                        uint32_t box_tokens,
+                        CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  cuuint64_t size[3] = {cols, heads, tokens};
+  cuuint64_t stride[2] = {head_pitch_bytes, token_pitch_bytes};
+  cuuint32_t box[3] = {box_cols, box_heads, box_tokens};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, dtype, 3, const_cast<void*>(base), size, stride, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace lt

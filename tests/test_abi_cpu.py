@@ -88,9 +88,13 @@ def test_entry_points_reject_bad_arguments_before_any_cuda_call(built_lib):
                                     2, 128, 128, 576, 576, 128, None) == UNSUP
     # extended form: neither mask given, q_group_div not dividing the tile count
     assert L.litedsa_masked_mla_fp8_ex(P, P, P, ok["sm"], ok["os"], None, None, 64, P, None, P,
-                                       2, 128, 128, 576, 576, 128, None, None, 1, None) == ARG
+                                       2, 128, 128, 576, 576, 128, None, None, 1, 0, 0, 0, 0, None) == ARG
     assert L.litedsa_masked_mla_fp8_ex(P, P, P, ok["sm"], ok["os"], None, P, 64, P, None, P,
-                                       3, 128, 128, 576, 576, 128, None, None, 2, None) == SHAPE
+                                       3, 128, 128, 576, 576, 128, None, None, 2, 0, 0, 0, 0, None) == SHAPE
+    # in-place addressing: a head pitch that is not a multiple of 16 bytes
+    assert L.litedsa_masked_mla_fp8_ex(P, P, P, ok["sm"], ok["os"], None, P, 64, P, None, P,
+                                       2, 128, 128, 576, 576, 128, None, None, 1, 64 * 584, 584, 0, 0,
+                                       None) == UNSUP
     # allocation-free form: every rule is checked before its scratch is touched
     na = L.litedsa_masked_mla_fp8_kv656_noalloc
     assert na(P, P, P, ok["sm"], ok["os"], None, P, 64, None, None, P, 2, 128, 128, 576, 128, None, None) == ARG
@@ -100,11 +104,11 @@ def test_entry_points_reject_bad_arguments_before_any_cuda_call(built_lib):
     assert na(P, P, P, ok["sm"], ok["os"], None, P, 64, P, None, P, 2, 65537, 128, 576, 128, None, None) == UNSUP
     # bf16 operators: missing range arrays, width other than 512 / 576, list not in 64-key blocks
     assert L.litedsa_dsv4_masked_mla_bf16(P, P, P, None, P, P, P, 0.1, 64, P, P, None,
-                                          2, 128, 128, 512, 512, 512, 128, None) == ARG
+                                          2, 128, 128, 512, 512, 512, 128, 0, 0, 0, 0, None) == ARG
     assert L.litedsa_dsv4_masked_mla_bf16(P, P, P, P, P, P, P, 0.1, 64, P, P, None,
-                                          2, 128, 128, 500, 512, 512, 128, None) == SHAPE
+                                          2, 128, 128, 500, 512, 512, 128, 0, 0, 0, 0, None) == SHAPE
     assert L.litedsa_dsv4_masked_mla_bf16(P, P, P, P, P, P, P, 0.1, 64, P, P, None,
-                                          2, 128, 96, 512, 512, 512, 96, None) == SHAPE
+                                          2, 128, 96, 512, 512, 512, 96, 0, 0, 0, 0, None) == SHAPE
     assert L.litedsa_masked_mla_bf16(P, P, P, 0.1, None, None, 64, P, None, P,
                                      2, 128, 128, 576, 576, 576, 128, None, None) == ARG
     assert L.litedsa_masked_mla_bf16(P, P, P, 0.1, None, P, 64, P, None, P,
@@ -119,6 +123,6 @@ def test_entry_points_reject_bad_arguments_before_any_cuda_call(built_lib):
                                           2, 128, 128, 576, 576, 128, None) == ARG
     # DSv4: queries outside the cache, heads not dividing 128
     assert L.litedsa_dsv4_c128a_bf16(P, None, P, 4, 64, 0, 4, 0, 128, 128, 0.1, None, P, P,
-                                     576, 576, 576, None) == SHAPE
+                                     576, 576, 576, 0, 0, 0, 0, None) == SHAPE
     assert L.litedsa_dsv4_c128a_bf16(P, None, P, 1, 48, 0, 64, 0, 128, 128, 0.1, None, P, P,
-                                     576, 576, 576, None) == SHAPE
+                                     576, 576, 576, 0, 0, 0, 0, None) == SHAPE

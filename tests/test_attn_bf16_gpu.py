@@ -223,3 +223,26 @@ def test_dsv4_reference_signature_equals_range_kernel_on_contiguous_ranges():
     # few keys per row: |out| reaches several units, where one bf16 ulp exceeds 1e-2 absolute
     assert mad <= TOL_ABS * max(1.0, float(want_o.float().abs().max())) and cos >= 0.99999, (mad, cos)
     assert float((lse - want_l.reshape(ng, 128)).abs().max()) <= TOL_LSE
+
+
+@pytest.mark.parametrize("heads,hpad,d", [(16, 64, 512), (32, 64, 576), (8, 64, 512)])
+def test_dsv4_signature_in_place_padded_heads(heads, hpad, d):
+    # the zero-copy form the reference planned for this operator: q as [T, 64, d] with `heads`
+    # real head slots, out scattered straight into [T, 64, 512]
+    ng, topk, s_kv = 6, 256, 4096
+    q, kv, idx, pref, wlo, whi, counts, sk = _random_union_case(ng, heads, topk, s_kv, d, seed=17, sink=True)
+    G = 128 // heads
+    args = (kv.to(DEV), idx.to(DEV), pref.to(DEV), wlo.to(DEV), whi.to(DEV), counts.to(DEV), synth.SM_SCALE, heads)
+    out_p = torch.empty((ng, 128, 512), dtype=torch.bfloat16, device=DEV)
+    lse_p = torch.empty((ng, 128), dtype=torch.float32, device=DEV)
+    api.bf16_status(reset=True)
+    api.dsv4_masked_mla_bf16_out(q.to(DEV), *args, out_p, lse_p, sk.to(DEV))
+    q_pad = torch.randn((ng * G, hpad, d), dtype=torch.bfloat16, device=DEV)
+    q_pad[:, :heads] = q.view(ng * G, heads, d).to(DEV)
+    out_pad = torch.full((ng * G, hpad, 512), 7.0, dtype=torch.bfloat16, device=DEV)
+    lse_i = torch.empty((ng, 128), dtype=torch.float32, device=DEV)
+    api.dsv4_masked_mla_bf16_out(q_pad, *args, out_pad, lse_i, sk.to(DEV), in_place_heads=True)
+    torch.cuda.synchronize()
+    assert api.bf16_status()[0] == 0
+    assert torch.equal(out_pad[:, :heads].reshape(ng, 128, 512), out_p) and torch.equal(lse_i, lse_p)
+    assert bool((out_pad[:, heads:] == 7.0).all())

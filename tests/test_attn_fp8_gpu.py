@@ -294,3 +294,31 @@ def test_bounded_wait_gives_up_reports_and_later_launches_are_unaffected():
     assert api.attn_status()[0] == 0
     old = api.set_wait_limit_ns(5_000_000)               # the limit is a run-time setting
     assert api.set_wait_limit_ns(0) == 5_000_000 and old > 0
+
+
+@pytest.mark.parametrize("heads,hpad", [(16, 64), (32, 64), (8, 24), (64, 64)])
+def test_in_place_padded_heads_equal_the_packed_path_bit_for_bit(heads, hpad):
+    # zero-copy for tensor-parallel callers: q / out live in [T, H_padded, d] tensors with `heads`
+    # real head slots per token; no pack / unpack copies around the kernel
+    w, idx, kv, q = _case(128, heads, 256, 4096, (0.6, 0.8), seed=14)
+    (u, c, m), ref, (q8, kv8, qs, ks) = _oracle(w, idx, kv, q)
+    ng, G = w.tiles, w.group
+    u_d, c_d = torch.from_numpy(u).to(DEV), torch.from_numpy(c).to(DEV)
+    m_d, kv_d = torch.from_numpy(m.view(np.int32)).to(DEV), kv8.to(DEV)
+    sm = synth.SM_SCALE * qs * ks
+    # packed path
+    out_p = torch.empty((ng, 128, 512), dtype=torch.bfloat16, device=DEV)
+    lse_p = torch.empty((ng, 128), dtype=torch.float32, device=DEV)
+    api.attn_status(reset=True)
+    api.masked_mla_fp8_out(q8.view(ng, 128, 576).to(DEV), kv_d, u_d, sm, ks, c_d, m_d, heads, out_p, None, lse_p)
+    # in place: the same queries inside a padded tensor, outputs into a padded tensor of canaries
+    q_pad = torch.randint(0, 255, (w.tokens, hpad, 576), dtype=torch.uint8, device=DEV)
+    q_pad[:, :heads] = q8.view(w.tokens, heads, 576).to(DEV)
+    out_pad = torch.full((w.tokens, hpad, 512), 7.0, dtype=torch.bfloat16, device=DEV)
+    lse_i = torch.empty((ng, 128), dtype=torch.float32, device=DEV)
+    api.masked_mla_fp8_out(q_pad, kv_d, u_d, sm, ks, c_d, m_d, heads, out_pad, None, lse_i, in_place_heads=True)
+    torch.cuda.synchronize()
+    assert api.attn_status()[0] == 0
+    assert torch.equal(out_pad[:, :heads].reshape(ng, 128, 512), out_p) and torch.equal(lse_i, lse_p)
+    assert bool((out_pad[:, heads:] == 7.0).all())            # the padding slots are never written
+    _check(out_p, lse_p, None, ref)

@@ -72,3 +72,24 @@ def test_dsv4_config3_tile_sample_is_finite_and_normalised():
     assert api.dsv4_status()[0] == 0
     assert bool(torch.isfinite(lse).all())
     assert float((out.float() - 0.5).abs().max()) <= 4e-3
+
+
+@pytest.mark.parametrize("h,hpad", [(16, 64), (32, 64), (64, 64)])
+def test_dsv4_in_place_padded_heads(h, hpad):
+    # q read in place from [T, H_padded, 576] with h real head slots, out written in place
+    T, S, Nc = 128, 4096, 32
+    g = torch.Generator().manual_seed(7)
+    q = torch.randn((T, h, 576), generator=g).to(torch.bfloat16).to(DEV)
+    kc = torch.randn((Nc, 576), generator=g).to(torch.bfloat16).to(DEV)
+    kr = torch.randn((S, 576), generator=g).to(torch.bfloat16).to(DEV)
+    want_o, want_l = api.dsv4_c128a_bf16(q, kc, kr, S - T, synth.SM_SCALE)
+    q_pad = torch.randn((T, hpad, 576), dtype=torch.bfloat16, device=DEV)
+    q_pad[:, :h] = q
+    out_pad = torch.full((T, hpad, 512), 7.0, dtype=torch.bfloat16, device=DEV)
+    api.dsv4_status(reset=True)
+    got_o, got_l = api.dsv4_c128a_bf16(q_pad, kc, kr, S - T, synth.SM_SCALE, heads=h, out=out_pad)
+    torch.cuda.synchronize()
+    assert api.dsv4_status()[0] == 0
+    assert got_o.data_ptr() == out_pad.data_ptr()
+    assert torch.equal(out_pad[:, :h], want_o) and torch.equal(got_l, want_l)
+    assert bool((out_pad[:, h:] == 7.0).all())
