@@ -27,13 +27,17 @@
 //       warps 20-23 tile epilogue: O out of TMEM, x out_scale / l, bf16, staged per warp and
 //                   written with TMA tile stores while the softmax warps already work on the
 //                   next tile.
-//   * K tiles are five 128-byte-swizzled column chunks per 64 keys (the fifth holds the 64
-//     rope bytes, its other half kept zero), V tiles two MN-major chunks per 128 keys.
+//   * Q and K tiles are four 128-byte-swizzled column chunks per 64 rows plus a compact
+//     64-byte-swizzled chunk for the 64 rope bytes; V tiles two MN-major chunks per 128 keys.
+//   * the 512 latent dims of every Q tile are moved from shared memory into TENSOR MEMORY once
+//     per tile (by the epilogue warps) and the QK^T MMAs read them from there (A operand in
+//     TMEM); only the rope chunk of Q stays in shared memory.
 //   * completion is tracked with mbarriers only; every wait is bounded (common.cuh) and
 //     reports through a status word instead of trapping.
 //   * no TMA multicast of any kind; the pair is signalled with two plain commits.
 #include "common.cuh"
 #include "tensor_map.cuh"
+
 
 namespace lt {
 constexpr unsigned kIdleCheckEvery = 64;   // idle polls between two time-limit checks (power of two)
@@ -46,27 +50,37 @@ constexpr int kEpiWarps = 4;
 constexpr int kAttnThreads = 768;
 constexpr int kBlockKeys = 128;                      // keys per softmax block (whole pair)
 constexpr int kDQK = 576, kDV = 512;
-constexpr int kChunks = 5;                           // 128-byte column chunks per row
-constexpr int kChunkBytes = 64 * 128;                // 64 rows x 128 B
-constexpr uint32_t kQBytes = kChunks * kChunkBytes;  // 40960 (per CTA)
-constexpr uint32_t kKStage = kChunks * kChunkBytes;  // 64 keys x 640 B
+constexpr int kChunkBytes = 64 * 128;                // 64 rows x 128 B (dims 128j .. 128j+127)
+constexpr int kRopeChunkBytes = 64 * 64;             // 64 rows x 64 B (dims 512 .. 575), 64-byte swizzle
+constexpr uint32_t kQBytes = 4 * kChunkBytes + kRopeChunkBytes;  // 36864 (per CTA)
+constexpr uint32_t kKStage = kQBytes;                // 64 keys x 576 B
 constexpr uint32_t kVChunk = 128 * 128;              // 128 keys x 128 B
 constexpr uint32_t kVStage = 2 * kVChunk;            // 128 keys x 256 dims
 constexpr uint32_t kPBytes = 64 * 128;               // 64 rows x 128 keys e4m3
-constexpr uint32_t kOffQ = 0;
-constexpr uint32_t kOffK = kOffQ + kQBytes;
-constexpr uint32_t kOffV = kOffK + 2 * kKStage;
-constexpr uint32_t kOffP = kOffV + 2 * kVStage;
-constexpr uint32_t kOffMisc = kOffP + 2 * kPBytes;   // 204800
 constexpr uint32_t kMiscBytes = 7168;
-constexpr uint32_t kOffStage = kOffMisc + kMiscBytes;  // 4 x 4 KB output staging slices (epilogue warps)
-constexpr uint32_t kStageBytes = 8 * 2048;
-constexpr uint32_t kAttnSmem = kOffStage + kStageBytes + 1024;  // + alignment slack
-static_assert(kAttnSmem <= 232448, "shared-memory plan exceeds the 227 KB per-CTA limit");
+constexpr uint32_t kStageBytes = 4 * 4096;           // staged epilogue: one 4 KB slice per epilogue warp
+
+// Shared-memory plan: two K stages, two V stages, two P buffers, own output staging.  (A third
+// K stage fits only with a single P buffer and staging aliased onto the Q tile; measured
+// slower: the single P buffer then waits for PVs whose V tile landed late.)
+constexpr int kKStages = 2;
+struct Plan {
+  static constexpr int kPBufs = 2;
+  static constexpr uint32_t kOffQ = 0;
+  static constexpr uint32_t kOffK = kOffQ + kQBytes;
+  static constexpr uint32_t kOffV = kOffK + kKStages * kKStage;
+  static constexpr uint32_t kOffP = kOffV + 2 * kVStage;
+  static constexpr uint32_t kOffMisc = kOffP + kPBufs * kPBytes;
+  static constexpr uint32_t kOffStage = kOffMisc + kMiscBytes;
+  static constexpr uint32_t kSmem = kOffStage + kStageBytes + 1024;   // + alignment slack
+  static_assert(kOffV % 1024 == 0 && kOffP % 1024 == 0, "swizzled tiles need 1024-byte alignment");
+  static_assert(kSmem <= 232448, "shared-memory plan exceeds the 227 KB per-CTA limit");
+};
 
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTmemO = 0;                        // 256 columns: O (64 rows x 512 dims per CTA)
 constexpr uint32_t kTmemS0 = 256, kTmemS1 = 320;      // 64 columns each: S double buffer
+constexpr uint32_t kTmemQ = 384;                      // 128 columns: the 512 latent dims of Q (e4m3, 4 per column)
 
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
@@ -76,12 +90,16 @@ constexpr float kMInit = -1e30f;
 constexpr float kRescaleThreshold = 6.0f;
 
 struct Misc {
-  // in the leader CTA only: q_full (both CTAs' Q tiles), k_peer / v_peer (peer's K / V landed),
-  // s_free / p_ready (softmax warps of both CTAs)
-  uint64_t q_full, k_peer[2], v_peer[2], s_free[2], p_ready[2];
-  // in every CTA
-  uint64_t k_land[2], v_land[2], qk_done[2], pv_done[2], valid_ready[2], valid_free[2];
+  // in the leader CTA only: k_peer / v_peer (peer's K / V landed), s_free / p_ready (softmax
+  // warps of both CTAs)
+  uint64_t k_peer[3], v_peer[2], s_free[2], p_ready[2];
+  // in every CTA.  qk_done is indexed by the running block number modulo 6: one barrier tells
+  // the softmax group of block kb (S buffer kb % 2) and the gather warps (K stage kb % 2 or
+  // kb % 3) that QK^T(kb) is complete, and none is reused before both have looked at it.
+  uint64_t k_land[3], v_land[2], qk_done[6], pv_done[2], valid_ready[2], valid_free[2];
   uint64_t m_pub[2];                // running max of block k published by softmax group k%2
+  uint64_t q_land;                  // every CTA: this CTA's Q tile has landed in shared memory
+  uint64_t qt_ready;                // leader CTA: Q's latent part is in tensor memory in both CTAs
   uint64_t q_free;                  // all QK^T of the current tile are complete (Q tile reusable)
   uint64_t o_free;                  // leader CTA: the tile's O has been read out of TMEM
   uint64_t epi_ready;               // the tile's row scales are published (softmax warps)
@@ -128,10 +146,24 @@ enum { kSiteQ = 1, kSiteKLand, kSiteKPeer, kSiteVLand, kSiteVPeer, kSiteQkDone, 
 // status block of the FP8 attention kernels (layout: see Waiter in common.cuh)
 __device__ int g_attn_status[8];
 
+// a running block number's K stage / phase and its qk_done barrier / phase
+struct BlockIdx {
+  int ks, kph, b6, b6ph;
+  __device__ __forceinline__ explicit BlockIdx(int kb) {
+    ks = kb % kKStages; kph = (kb / kKStages) & 1;
+    b6 = kb % 6; b6ph = (kb / 6) & 1;
+  }
+};
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kAttnThreads, 1)
 masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
+                      const __grid_constant__ CUtensorMap map_q_rope,
                       const __grid_constant__ OutMaps omaps, const AttnParams p) {
-  extern __shared__ uint8_t smem_raw[];
+  using PL = Plan;
+  constexpr uint32_t kOffQ = PL::kOffQ, kOffK = PL::kOffK, kOffV = PL::kOffV, kOffP = PL::kOffP,
+                     kOffMisc = PL::kOffMisc, kOffStage = PL::kOffStage;
+  constexpr int kPBufs = PL::kPBufs;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t sbase = (raw + 1023u) & ~1023u;       // 128B-swizzle tiles need 1024-byte alignment
   uint8_t* sm = smem_raw + (sbase - raw);
@@ -156,18 +188,21 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
   auto blocks_of = [&](int count) -> int { return max((count + kBlockKeys - 1) / kBlockKeys, 1); };
 
   if (threadIdx.x == 0) {
-    mbar_init(&ms.q_full, 1);
+    mbar_init(&ms.q_land, 1);
+    mbar_init(&ms.qt_ready, 2 * kEpiWarps);
     mbar_init(&ms.q_free, 1);
     mbar_init(&ms.o_free, 2 * kEpiWarps);
     mbar_init(&ms.epi_ready, kSoftmaxWarps);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < 3; ++i) {
       mbar_init(&ms.k_peer[i], 1);
+      mbar_init(&ms.k_land[i], kProducerWarps * 32);        // one async arrival per gather thread
+    }
+    for (int i = 0; i < 6; ++i) mbar_init(&ms.qk_done[i], 1);
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&ms.v_peer[i], 1);
       mbar_init(&ms.s_free[i], 8);        // 4 warps of one softmax group x 2 CTAs
       mbar_init(&ms.p_ready[i], 8);
-      mbar_init(&ms.k_land[i], kProducerWarps * 32);        // one async arrival per gather thread
       mbar_init(&ms.v_land[i], kProducerWarps * 32);        // one async arrival per gather thread
-      mbar_init(&ms.qk_done[i], 1);
       mbar_init(&ms.pv_done[i], 1);
       mbar_init(&ms.valid_ready[i], 1);
       mbar_init(&ms.valid_free[i], 4);
@@ -175,6 +210,7 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
     }
     fence_mbar_init();
     tma_prefetch_desc(&map_q);
+    tma_prefetch_desc(&map_q_rope);
     for (int d = 0; d < p.n_out; ++d) tma_prefetch_desc(&omaps.m[d]);
   }
   __syncthreads();
@@ -227,7 +263,11 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         uint2 mk_next = mk;
         if (mrow && k + 2 < nb) mk_next = __ldg(reinterpret_cast<const uint2*>(mrow + (size_t)(k + 2) * 4));
 
-        mbar_wait(&ms.qk_done[g], ph, wt, kSiteQkDone, k);
+        {
+          const BlockIdx bi(kb);
+          mbar_wait(&ms.qk_done[bi.b6], bi.b6ph, wt, kSiteQkDone, k);
+        }
+        __syncwarp();      // lanes leave the wait loop one by one: re-converge before .aligned ops
         tc_fence_after();
         float sv[64];
         tmem_ld32(scol, sv);
@@ -292,9 +332,13 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
           const uint32_t hi = __nv_cvt_float2_to_fp8x2(d1, __NV_SATFINITE, __NV_E4M3);
           pk[j >> 2] = lo | (hi << 16);
         }
-        // P buffer g was last read by the PV of block kb-2
-        if (kb >= 2) mbar_wait(&ms.pv_done[g], ph ^ 1, wt, kSitePFree, k);
-        uint8_t* pdst = sm + kOffP + g * kPBytes + (4 * h) * 1024 + r * 16;
+        // the P buffer was last read by the PV of block kb-2 (two buffers) or kb-1 (one)
+        if (kPBufs == 2) {
+          if (kb >= 2) mbar_wait(&ms.pv_done[g], ph ^ 1, wt, kSitePFree, k);
+        } else {
+          if (kb >= 1) mbar_wait(&ms.pv_done[g ^ 1], ((kb - 1) >> 1) & 1, wt, kSitePFree, k);
+        }
+        uint8_t* pdst = sm + kOffP + (kPBufs == 2 ? g : 0) * kPBytes + (4 * h) * 1024 + r * 16;
 #pragma unroll
         for (int i = 0; i < 4; ++i)
           *reinterpret_cast<uint4*>(pdst + i * 1024) =
@@ -303,6 +347,7 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         if (rescale && k > 0) {
           // O holds blocks [0, k) relative to m_prev: bring it to new_m once PV(k-1) is complete
           mbar_wait(&ms.pv_done[g ^ 1], ((kb - 1) >> 1) & 1, wt, kSitePvDone, k);
+          __syncwarp();      // lanes leave the wait loop one by one: re-converge before .aligned ops
           tc_fence_after();
           const float f = fast_exp2(m_prev - new_m);
           float o[32];
@@ -382,15 +427,6 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
     // (QK^T done vs PV done), so each warp advances two independent cursors and issues
     // whichever is ready; neither tile is derived from the other, so no stage waits on a copy.
     const int pw = warp - kSoftmaxWarps;
-    const uint32_t a_q_full = mapa(smem_u32(&ms.q_full), 0);
-    // the unused half of the fifth (rope) chunk of both K stages must read as zero
-    for (int i = pw * 32 + lane; i < 2 * 64 * 8; i += kProducerWarps * 32) {
-      const int st = i >> 9, rowp = (i >> 3) & 63, c8 = i & 7;
-      *reinterpret_cast<uint4*>(sm + kOffK + st * kKStage + 4 * kChunkBytes + rowp * 128 + c8 * 16) =
-          make_uint4(0u, 0u, 0u, 0u);
-    }
-    fence_proxy_async_smem();
-    asm volatile("bar.sync 4, 256;" ::: "memory");   // zeros are in place before any copy lands
     struct Cursor { int tile, it, k, nb, kb0; };
     auto cur_init = [&](Cursor& c) {
       c.tile = cid; c.it = 0; c.k = 0; c.kb0 = 0;
@@ -414,6 +450,9 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
       const int v = __ldg(p.indices + (size_t)c.tile * p.idx_stride + (size_t)c.k * kBlockKeys + my_key);
       return ((unsigned)v < (unsigned)p.s_kv) ? v : 0;     // out-of-range rows are masked later
     };
+    // The indices of a block are loaded three blocks before its gather is issued (a cold index
+    // line comes from HBM): look-ahead cursors run ahead of the issue cursors and feed two
+    // three-deep register pipelines.
     int kidx = 0, vidx = 0;
     if (ck.tile < p.ng) { kidx = load_idx(ck); vidx = load_idx(cv); }
     const uint8_t* kvb = p.kv;
@@ -430,13 +469,13 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
         const bool okq = q_it == 0 || mbar_test(&ms.q_free, (q_it - 1) & 1);
         if (__all_sync(0xffffffffu, okq)) {
           if (lane == 0) {
-            if (cta == 0) mbar_arrive_expect_tx(&ms.q_full, 2 * kQBytes);
-            for (int j = 0; j < kChunks; ++j)
-              // this CTA's 64 rows of the tile = (token, head) pairs starting at row 64 cta
-              tma_load_3d_pair_hint(sbase + kOffQ + j * kChunkBytes, &map_q, 128 * j,
-                                    (64 * (int)cta) % p.h_per_q,
-                                    (q_tile / p.q_group_div) * p.G + (64 * (int)cta) / p.h_per_q,
-                                    a_q_full, pol_stream);
+            mbar_arrive_expect_tx(&ms.q_land, kQBytes);
+            // this CTA's 64 rows of the tile = (token, head) pairs starting at row 64 cta
+            const int qh = (64 * (int)cta) % p.h_per_q;
+            const int qt = (q_tile / p.q_group_div) * p.G + (64 * (int)cta) / p.h_per_q;
+            for (int j = 0; j < 4; ++j)
+              tma_load_3d_hint(sbase + kOffQ + j * kChunkBytes, &map_q, 128 * j, qh, qt, &ms.q_land, pol_stream);
+            tma_load_3d_hint(sbase + kOffQ + 4 * kChunkBytes, &map_q_rope, 512, qh, qt, &ms.q_land, pol_stream);
           }
           __syncwarp();
           q_tile += ncl;
@@ -446,10 +485,14 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
       }
       if (ck.tile < p.ng) {
         const int kb = ck.kb0 + ck.k;
-        const int s = kb & 1;
-        const uint32_t ph = (kb >> 1) & 1;
-        // stage s held block kb-2: its QK^T must have read it
-        const bool ok = kb < 2 || mbar_test(&ms.qk_done[s], ph ^ 1);
+        const BlockIdx bi(kb);
+        const int s = bi.ks;
+        // stage s held block kb - kKStages: its QK^T must have read it
+        bool ok = true;
+        if (kb >= kKStages) {
+          const BlockIdx prev(kb - kKStages);
+          ok = mbar_test(&ms.qk_done[prev.b6], prev.b6ph);
+        }
         if (__all_sync(0xffffffffu, ok)) {
           const uint32_t kst = sbase + kOffK + s * kKStage;
 #pragma unroll
@@ -462,7 +505,8 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
           {
             const int ri = __shfl_sync(0xffffffffu, kidx, lane >> 2);
             const int row = 8 * pw + (lane >> 2);
-            cp_async16_hint(kst + 4 * kChunkBytes + row * 128 + (((lane & 3) ^ (row & 7)) << 4),
+            // rope bytes: compact 64-byte rows, 64-byte swizzle (16-byte unit ^ ((row / 2) % 4))
+            cp_async16_hint(kst + 4 * kChunkBytes + row * 64 + (((lane & 3) ^ ((row >> 1) & 3)) << 4),
                        kvb + (size_t)ri * pitch + 512 + 16 * (lane & 3), pol_keep);
           }
           cp_async_mbar_arrive_noinc(&ms.k_land[s]);
@@ -519,29 +563,31 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
     if (cta == 0) {   // the whole warp runs this loop; one elected lane issues
       constexpr uint32_t idesc_qk = umma_idesc(0, 0, false, false, 128, 128);
       constexpr uint32_t idesc_pv = umma_idesc(0, 0, false, true, 128, 256);
-      const uint32_t a_qk_done_peer[2] = {mapa(smem_u32(&ms.qk_done[0]), 1), mapa(smem_u32(&ms.qk_done[1]), 1)};
+      const uint32_t a_qk_done0 = smem_u32(&ms.qk_done[0]), a_qk_done0_peer = mapa(a_qk_done0, 1);
       const uint32_t a_pv_done_peer[2] = {mapa(smem_u32(&ms.pv_done[0]), 1), mapa(smem_u32(&ms.pv_done[1]), 1)};
       const uint32_t a_q_free_peer = mapa(smem_u32(&ms.q_free), 1);
       // S = Q K^T of block kb into S buffer kb%2
       // The K / V tiles were written by cp.async (generic proxy) and are read by the tensor core
       // through the async proxy: a cross-proxy fence sits between "landed" and the MMA.
-      auto issue_qk = [&](int k, int kb) {
-        const int s = kb & 1;
+      // descriptor high words: 128-byte swizzle (8-row groups 1024 B apart) for the four latent
+      // chunks, 64-byte swizzle (8-row groups 512 B apart) for the compact rope chunk
+      const uint32_t hi128 = (uint32_t)(umma_desc(0, 16, 1024, kSwz128) >> 32);
+      const uint32_t hi64 = (uint32_t)(umma_desc(0, 16, 512, kSwz64) >> 32);
+      auto issue_qk = [&](int k, int kb, const BlockIdx& bi) {
         fence_proxy_async_smem();
         tc_fence_after();
-        const uint32_t d = tmem + (s ? kTmemS1 : kTmemS0);
-        const uint64_t ad = umma_desc(sbase + kOffQ, 16, 1024, kSwz128);
-        const uint64_t bd = umma_desc(sbase + kOffK + s * kKStage, 16, 1024, kSwz128);
-        mma_f8_pair_qk18(d, idesc_qk, (uint32_t)ad, (uint32_t)bd, (uint32_t)(ad >> 32),
-                         (uint32_t)(bd >> 32));
-        mma_commit_pair_elect(smem_u32(&ms.qk_done[s]));
-        mma_commit_pair_elect(a_qk_done_peer[s]);
+        const uint32_t d = tmem + ((kb & 1) ? kTmemS1 : kTmemS0);
+        const uint32_t a_rope_lo = (uint32_t)umma_desc(sbase + kOffQ + 4 * kChunkBytes, 16, 512, kSwz64);
+        const uint32_t b_lo = (uint32_t)umma_desc(sbase + kOffK + bi.ks * kKStage, 16, 1024, kSwz128);
+        mma_f8_pair_qk18(d, idesc_qk, tmem + kTmemQ, b_lo, hi128, hi64, a_rope_lo);
+        mma_commit_pair_elect(a_qk_done0 + 8u * (uint32_t)bi.b6);
+        mma_commit_pair_elect(a_qk_done0_peer + 8u * (uint32_t)bi.b6);
       };
       auto issue_pv = [&](int k, int kb) {
         const int s = kb & 1;
         fence_proxy_async_smem();
         tc_fence_after();
-        const uint64_t ad = umma_desc(sbase + kOffP + s * kPBytes, 1024, 128, kSwzNone);
+        const uint64_t ad = umma_desc(sbase + kOffP + (kPBufs == 2 ? s : 0) * kPBytes, 1024, 128, kSwzNone);
         const uint64_t bd = umma_desc(sbase + kOffV + s * kVStage, kVChunk, 1024, kSwz128);
         mma_f8_pair_pv8(tmem + kTmemO, idesc_pv, (uint32_t)ad, (uint32_t)bd, (uint32_t)(ad >> 32),
                         (uint32_t)(bd >> 32), k ? 1u : 0u);
@@ -552,7 +598,7 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
       bool aborted = false;
       for (int tile = cid; tile < p.ng && !aborted; tile += ncl, ++it) {
         const int nb = blocks_of(tile_count(tile));
-        mbar_wait(&ms.q_full, it & 1, wt, kSiteQ, it);
+        mbar_wait(&ms.qt_ready, it & 1, wt, kSiteQ, it);
         __syncwarp();
         // Ready-driven issue: whichever of "next QK" (its K stage landed on both CTAs and its S
         // buffer drained) and "next PV" (its P written, its V stage landed on both CTAs, and for
@@ -578,12 +624,13 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
           }
           if (qk_i < nb) {
             const int kb = kb0 + qk_i;
+            const BlockIdx bi(kb);
             const int s = kb & 1;
             const uint32_t ph = (kb >> 1) & 1;
-            const bool ok = mbar_test(&ms.k_land[s], ph) && mbar_test(&ms.k_peer[s], ph) &&
+            const bool ok = mbar_test(&ms.k_land[bi.ks], bi.kph) && mbar_test(&ms.k_peer[bi.ks], bi.kph) &&
                             (kb < 2 || mbar_test(&ms.s_free[s], ph ^ 1));
             if (__all_sync(0xffffffffu, ok)) {
-              issue_qk(qk_i, kb);
+              issue_qk(qk_i, kb, bi);
               ++qk_i;
               if (qk_i == nb) {      // the Q tile is no longer needed once these MMAs complete
                 mma_commit_pair_elect(smem_u32(&ms.q_free));
@@ -623,14 +670,43 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
     const int e_tl = ((warp & 3) << 5) | lane, e_r = e_tl & 63, e_h = e_tl >> 6;
     const uint32_t e_ocol = tmem + ((uint32_t)((warp & 3) * 32) << 16) + kTmemO;
     const uint32_t a_o_free = mapa(smem_u32(&ms.o_free), 0);
+    const uint32_t a_qt_ready = mapa(smem_u32(&ms.qt_ready), 0);
     const uint64_t pol_stream = l2_policy_evict_first();
+    // These warps also move the latent part of every Q tile from shared memory (where TMA put
+    // it) into tensor memory, where the QK^T MMAs read it: lane = row (e_r, duplicated in lanes
+    // 64-127 as the 64-rows-per-CTA form of the instruction wants), chunk j -> 32 columns.  The
+    // tile's Q lands when the previous tile's last QK^T has completed, i.e. shortly before that
+    // tile's epilogue starts: transfer Q(t + 1), then write out O(t).
+    auto transfer_q = [&](int q_it) {
+      mbar_wait(&ms.q_land, q_it & 1, wt, kSiteQ, q_it);
+      __syncwarp();      // lanes leave the wait loop one by one: re-converge before .aligned ops
+      const uint8_t* qrow = sm + kOffQ + e_r * 128;
+#pragma unroll 1
+      for (int j = 0; j < 4; ++j) {
+        uint32_t v[32];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const uint4 t = *reinterpret_cast<const uint4*>(qrow + j * kChunkBytes + ((u ^ (e_r & 7)) << 4));
+          v[4 * u] = t.x; v[4 * u + 1] = t.y; v[4 * u + 2] = t.z; v[4 * u + 3] = t.w;
+        }
+        tmem_st32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + kTmemQ + 32 * j, reinterpret_cast<const float*>(v));
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      fence_proxy_async_smem();      // these reads are ordered before the next TMA write of the tile
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(a_qt_ready);
+    };
     int kb0 = 0, it = 0;
+    if (cid < p.ng) transfer_q(0);
     for (int tile = cid; tile < p.ng; tile += ncl, ++it) {
       const int nb = blocks_of(tile_count(tile));
       const int kbl = kb0 + nb - 1;                // last block of the tile
+      if (tile + ncl < p.ng) transfer_q(it + 1);
       // the row scales are published and the tile's last PV has completed
       mbar_wait(&ms.epi_ready, it & 1, wt, kSiteEpi, it);
       mbar_wait(&ms.pv_done[kbl & 1], (kbl >> 1) & 1, wt, kSiteEpi, nb);
+      __syncwarp();      // lanes leave the wait loop one by one: re-converge before .aligned ops
       tc_fence_after();
       const float oscale = ms.oscale[it & 1][e_r];
       const uint32_t emask = oscale != 0.f ? 0xffffffffu : 0u;
@@ -657,25 +733,27 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
           __nv_bfloat162 v2 = __floats2bfloat162_rn(o[2 * j] * oscale, o[2 * j + 1] * oscale);
           w[j] = *reinterpret_cast<uint32_t*>(&v2) & emask;    // rows without a valid key: zeros
         }
-        // two rounds make one box of 32 rows x 128 bytes (128-byte swizzle) in the warp's 4 KB
-        // slice; before the first of them the previous box must have been read out
-        if ((cc & 1) == 0) {
-          if (lane == 0) bulk_wait_read_all();
-          __syncwarp();
-        }
-        const uint32_t slice = kOffStage + (uint32_t)ew * 4096;
-        uint8_t* st_row = sm + slice + (e_r & 31) * 128;
+        {
+          // two rounds make one box of 32 rows x 128 bytes (128-byte swizzle) in the warp's 4 KB
+          // slice; before the first of them the previous box must have been read out
+          if ((cc & 1) == 0) {
+            if (lane == 0) bulk_wait_read_all();
+            __syncwarp();
+          }
+          const uint32_t slice = kOffStage + (uint32_t)ew * 4096;
+          uint8_t* st_row = sm + slice + (e_r & 31) * 128;
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          *reinterpret_cast<uint4*>(st_row + (((4 * (cc & 1) + j) ^ (e_r & 7)) << 4)) =
-              make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
-        if (cc & 1) {
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            for (int d = 0; d < p.n_out; ++d)
-              tma_store_3d_hint(&omaps.m[d], sbase + slice, 256 * e_h + 64 * (cc >> 1), out_head, out_tok, pol_stream);
-            bulk_commit_group();
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(st_row + (((4 * (cc & 1) + j) ^ (e_r & 7)) << 4)) =
+                make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+          if (cc & 1) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              for (int d = 0; d < p.n_out; ++d)
+                tma_store_3d_hint(&omaps.m[d], sbase + slice, 256 * e_h + 64 * (cc >> 1), out_head, out_tok, pol_stream);
+              bulk_commit_group();
+            }
           }
         }
       }
@@ -689,18 +767,18 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
     // peer CTA warp 17 forwards "K tile landed" and warp 18 "V tile landed".
     if (cta == 1) {
       const bool is_k = warp == kWarpCopy;
-      const uint32_t a_peer[2] = {mapa(smem_u32(is_k ? &ms.k_peer[0] : &ms.v_peer[0]), 0),
-                                  mapa(smem_u32(is_k ? &ms.k_peer[1] : &ms.v_peer[1]), 0)};
+      const uint32_t a_peer0 = mapa(smem_u32(is_k ? &ms.k_peer[0] : &ms.v_peer[0]), 0);
       int kb0 = 0;
       for (int tile = cid; tile < p.ng; tile += ncl) {
         const int nb = blocks_of(tile_count(tile));
         for (int k = 0; k < nb; ++k) {
           const int kb = kb0 + k;
-          const int s = kb & 1;
-          const uint32_t ph = (kb >> 1) & 1;
+          const BlockIdx bi(kb);
+          const int s = is_k ? bi.ks : (kb & 1);
+          const uint32_t ph = is_k ? (uint32_t)bi.kph : (uint32_t)((kb >> 1) & 1);
           mbar_wait(is_k ? &ms.k_land[s] : &ms.v_land[s], ph, wt, is_k ? kSiteRelayK : kSiteRelayV, k);
           fence_proxy_async_smem();     // this CTA's cp.async writes -> the leader's MMA reads
-          if (lane == 0) mbar_arrive_cluster_release(a_peer[s]);
+          if (lane == 0) mbar_arrive_cluster_release(a_peer0 + 8u * (uint32_t)s);
         }
         kb0 += nb;
       }
@@ -756,11 +834,12 @@ static int max_clusters() {
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   int n = sms / 2;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(sms, 1, 1); cfg.blockDim = dim3(kAttnThreads, 1, 1); cfg.dynamicSmemBytes = kAttnSmem;
+  cfg.gridDim = dim3(sms, 1, 1); cfg.blockDim = dim3(kAttnThreads, 1, 1); cfg.dynamicSmemBytes = Plan::kSmem;
   cudaLaunchAttribute at; at.id = cudaLaunchAttributeClusterDimension; at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
   cfg.attrs = &at; cfg.numAttrs = 1;
   int q = 0;
-  if (cudaFuncSetAttribute(masked_mla_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem) == cudaSuccess &&
+  if (cudaFuncSetAttribute(masked_mla_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)Plan::kSmem) == cudaSuccess &&
       cudaOccupancyMaxActiveClusters(&q, masked_mla_fp8_kernel, &cfg) == cudaSuccess && q > 0)
     n = q;
   cudaGetLastError();
@@ -768,13 +847,24 @@ static int max_clusters() {
   return n;
 }
 
+static int launch_fp8_t(const CUtensorMap& map_q, const CUtensorMap& map_q_rope, const OutMaps& omaps,
+                        const AttnParams& p, cudaStream_t stream) {
+  using PL = Plan;
+  auto kern = masked_mla_fp8_kernel;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PL::kSmem) != cudaSuccess)
+    return LITEDSA_ERR_CUDA;
+  kern<<<2 * min(p.ng, max_clusters()), kAttnThreads, PL::kSmem, stream>>>(
+      map_q, map_q_rope, omaps, p);
+  return cudaGetLastError() == cudaSuccess ? LITEDSA_OK : LITEDSA_ERR_CUDA;
+}
+
 static int launch_fp8(const Fp8Args& a, void* const* outs, int n_out, cudaStream_t stream) {
-  CUtensorMap map_q;
+  CUtensorMap map_q, map_q_rope;
   OutMaps omaps;
+  // q and out are addressed as (dim, head, token): row r of a tile is (token r / h, head r % h),
+  // which covers the dense packed layout and the in-place layout with padded head slots alike.
   // out is stored as boxes of 32 rows x 64 dims (128 bytes wide, 128-byte swizzle); only the
   // destinations in use are encoded, the unused slots repeat the first map
-  // q and out are addressed as (dim, head, token): row r of a tile is (token r / h, head r % h),
-  // which covers the dense packed layout and the in-place layout with padded head slots alike
   const int h = a.h_per_q, G = 128 / h;
   const int qdiv = a.q_group_div > 0 ? a.q_group_div : 1;
   const uint64_t q_hs = a.q_head_stride ? (uint64_t)a.q_head_stride : (uint64_t)a.q_row_stride;
@@ -787,9 +877,13 @@ static int launch_fp8(const Fp8Args& a, void* const* outs, int n_out, cudaStream
                      (uint64_t)a.ng * G, o_hs, o_ts, 64, ob_h, 32 / ob_h, CU_TENSOR_MAP_SWIZZLE_128B))
       return LITEDSA_ERR_CUDA;
   for (int d = n_out; d < kMaxOutputs; ++d) omaps.m[d] = omaps.m[0];
+  // Q per CTA: four boxes of 128 bytes x 64 rows (128-byte swizzle) and the rope box of 64 bytes
+  // x 64 rows (64-byte swizzle)
   const uint32_t qb_h = (uint32_t)min(h, 64);
   if (!make_map_3d(&map_q, a.q8, CU_TENSOR_MAP_DATA_TYPE_UINT8, kDQK, (uint64_t)h,
-                   (uint64_t)(a.ng / qdiv) * G, q_hs, q_ts, 128, qb_h, 64 / qb_h))
+                   (uint64_t)(a.ng / qdiv) * G, q_hs, q_ts, 128, qb_h, 64 / qb_h) ||
+      !make_map_3d(&map_q_rope, a.q8, CU_TENSOR_MAP_DATA_TYPE_UINT8, kDQK, (uint64_t)h,
+                   (uint64_t)(a.ng / qdiv) * G, q_hs, q_ts, 64, qb_h, 64 / qb_h, CU_TENSOR_MAP_SWIZZLE_64B))
     return LITEDSA_ERR_CUDA;
   AttnParams p;
   p.memb = a.memb_qm; p.len_per_q = a.topk_length_per_q; p.sink = a.attn_sink; p.q_group_div = qdiv;
@@ -801,11 +895,7 @@ static int launch_fp8(const Fp8Args& a, void* const* outs, int n_out, cudaStream
   p.idx_stride = a.indices_row_stride;
   p.scale_log2 = a.sm_scale * kLog2e; p.out_scale = a.out_scale;
   p.epoch = next_launch_epoch(); p.wait_limit_ns = wait_limit_ns();
-  if (cudaFuncSetAttribute(masked_mla_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           (int)kAttnSmem) != cudaSuccess)
-    return LITEDSA_ERR_CUDA;
-  masked_mla_fp8_kernel<<<2 * min(a.ng, max_clusters()), kAttnThreads, kAttnSmem, stream>>>(map_q, omaps, p);
-  return cudaGetLastError() == cudaSuccess ? LITEDSA_OK : LITEDSA_ERR_CUDA;
+  return launch_fp8_t(map_q, map_q_rope, omaps, p, stream);
 }
 
 // Host-side argument rules shared by every FP8 attention entry point: the reference

@@ -205,6 +205,15 @@ __device__ __forceinline__ void tma_load_3d_pair_hint(uint32_t dst_smem, const C
       ::"r"(dst_smem), "l"(map), "r"(x), "r"(y), "r"(z), "r"(mbar_cluster_addr), "l"(pol)
       : "memory");
 }
+// tiled 3-D load into this CTA's smem, completion bytes on this CTA's own barrier
+__device__ __forceinline__ void tma_load_3d_hint(uint32_t dst_smem, const CUtensorMap* map, int x, int y,
+                                                 int z, uint64_t* mbar, uint64_t pol) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      ".L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], %6;"
+      ::"r"(dst_smem), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(mbar)), "l"(pol)
+      : "memory");
+}
 // TMA 3-D tile store shared -> global (bulk async-group completion)
 __device__ __forceinline__ void tma_store_3d_hint(const void* map, uint32_t src_smem, int x, int y,
                                                   int z, uint64_t pol) {
@@ -295,23 +304,34 @@ __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols
 // issuing thread shares its scheduler with busy warps, and every extra integer instruction per
 // MMA costs tensor-pipe time.  Descriptors differ only in their low word (start address >> 4),
 // so each step is two 32-bit adds, two register-pair moves and the MMA.
-//   QK^T of one 128-key block: 18 steps over five 128-byte chunks (step (j,kk): +512*j + 2*kk)
-#define LT_QK_STEP(INC, PRED)                                  \
-  "add.u32 alo, %2, " #INC ";\n\tadd.u32 blo, %3, " #INC ";\n\t" \
-  "mov.b64 ad, {alo, %4};\n\tmov.b64 bd, {blo, %5};\n\t"        \
+//   QK^T of one 128-key block: 18 steps.  The 512 latent dims of Q sit in TENSOR MEMORY (A
+//   operand read from TMEM: lane = row, four e4m3 values per 32-bit column, 8 columns per
+//   32-dim step; with 64 rows per CTA the rows are duplicated in lanes 64-127), because with
+//   only 64 rows per CTA the shared-memory operand reads of an N = 128 step (A 2 KB + this
+//   CTA's half of B for both CTAs 4 KB per ~35 tensor cycles) exceed what shared memory
+//   delivers.  K comes from shared memory: four 128-byte-swizzled chunks of 128 dims (step
+//   (j,kk): +512*j + 2*kk in 16-byte units) and the compact 64-byte-swizzled rope chunk (two
+//   steps at +2048, +2050), whose 64 Q dims also stay in shared memory (a_rope_lo, hi64).
+#define LT_QK_TS_STEP(AINC, BINC, PRED)                                        \
+  "add.u32 qa, %2, " #AINC ";\n\tadd.u32 blo, %3, " #BINC ";\n\tmov.b64 bd, {blo, %4};\n\t" \
+  "@pe tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], [qa], bd, %1, " #PRED ";\n\t"
+#define LT_QK_SS_STEP(INC, PRED)                                               \
+  "add.u32 alo, %6, " #INC ";\n\tadd.u32 blo, %3, 2048 + " #INC ";\n\t"           \
+  "mov.b64 ad, {alo, %5};\n\tmov.b64 bd, {blo, %5};\n\t"                       \
   "@pe tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], ad, bd, %1, " #PRED ";\n\t"
-__device__ __forceinline__ void mma_f8_pair_qk18(uint32_t d_tmem, uint32_t idesc, uint32_t a_lo,
-                                                 uint32_t b_lo, uint32_t a_hi, uint32_t b_hi) {
+__device__ __forceinline__ void mma_f8_pair_qk18(uint32_t d_tmem, uint32_t idesc, uint32_t q_tmem,
+                                                 uint32_t b_lo, uint32_t hi128, uint32_t hi64,
+                                                 uint32_t a_rope_lo) {
   asm volatile(
-      "{\n\t.reg .pred pz, po, pe;\n\t.reg .b32 alo, blo;\n\t.reg .b64 ad, bd;\n\t"
+      "{\n\t.reg .pred pz, po, pe;\n\t.reg .b32 qa, alo, blo;\n\t.reg .b64 ad, bd;\n\t"
       "setp.ne.b32 pz, 0, 0;\n\tsetp.eq.b32 po, 0, 0;\n\telect.sync _|pe, 0xffffffff;\n\t"
-      LT_QK_STEP(0, pz) LT_QK_STEP(2, po) LT_QK_STEP(4, po) LT_QK_STEP(6, po)
-      LT_QK_STEP(512, po) LT_QK_STEP(514, po) LT_QK_STEP(516, po) LT_QK_STEP(518, po)
-      LT_QK_STEP(1024, po) LT_QK_STEP(1026, po) LT_QK_STEP(1028, po) LT_QK_STEP(1030, po)
-      LT_QK_STEP(1536, po) LT_QK_STEP(1538, po) LT_QK_STEP(1540, po) LT_QK_STEP(1542, po)
-      LT_QK_STEP(2048, po) LT_QK_STEP(2050, po)
+      LT_QK_TS_STEP(0, 0, pz) LT_QK_TS_STEP(8, 2, po) LT_QK_TS_STEP(16, 4, po) LT_QK_TS_STEP(24, 6, po)
+      LT_QK_TS_STEP(32, 512, po) LT_QK_TS_STEP(40, 514, po) LT_QK_TS_STEP(48, 516, po) LT_QK_TS_STEP(56, 518, po)
+      LT_QK_TS_STEP(64, 1024, po) LT_QK_TS_STEP(72, 1026, po) LT_QK_TS_STEP(80, 1028, po) LT_QK_TS_STEP(88, 1030, po)
+      LT_QK_TS_STEP(96, 1536, po) LT_QK_TS_STEP(104, 1538, po) LT_QK_TS_STEP(112, 1540, po) LT_QK_TS_STEP(120, 1542, po)
+      LT_QK_SS_STEP(0, po) LT_QK_SS_STEP(2, po)
       "}"
-      ::"r"(d_tmem), "r"(idesc), "r"(a_lo), "r"(b_lo), "r"(a_hi), "r"(b_hi)
+      ::"r"(d_tmem), "r"(idesc), "r"(q_tmem), "r"(b_lo), "r"(hi128), "r"(hi64), "r"(a_rope_lo)
       : "memory");
 }
 //   P V of one 128-key block: two N = 256 halves (D column offset 128, V chunk +1024) x four
