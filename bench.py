@@ -691,6 +691,9 @@ def main():
     ap.add_argument("--tokens", type=int, default=0,
                     help="shrink the workload to this many query tokens per GPU (profiling aid; "
                          "the default, the full configuration, is the only benchmark number)")
+    ap.add_argument("--only-native", action="store_true",
+                    help="run only the native-cache (bf16 route) record of the workload and print it "
+                         "(profiling aid for masked_mla_bf16_kernel)")
     ap.add_argument("--measure-fp8-peak", action="store_true",
                     help="print the tcgen05 dense rates measured by the library's probe and exit")
     ap.add_argument("--ref-module-worker", action="store_true", help=argparse.SUPPRESS)
@@ -708,6 +711,11 @@ def main():
     if args.measure_fp8_peak:
         torch.cuda.set_device(0)
         print(json.dumps({"tcgen05_dense_tflops": fp8_peaks(api), "bf16_cublas": load_peaks()}), flush=True)
+        return
+    if args.only_native:
+        torch.cuda.set_device(0)
+        print(json.dumps(native_record(api, w, torch.device("cuda", 0), args.steps, load_peaks()["bf16_tflops"])),
+              flush=True)
         return
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
