@@ -58,8 +58,12 @@ inline uint32_t fast_div_mul(int64_t n_max, int d) {
 }
 
 // NT threads per tile; VPT int4 loads cached per thread (0: nothing cached, the second
-// pass re-reads the tile)
-template <int NT, int VPT>
+// pass re-reads the tile).  PLAIN: no block table and one rank-table entry per bitmap word
+// (the common case), so the candidate pass carries neither the translation nor the
+// partial-rank loop.  (Forcing 32 registers per thread so that every warp slot of the SM is
+// filled was measured 3-8 % slower: the kernel is bound by shared-memory transactions, not
+// by occupancy.)
+template <int NT, int VPT, bool PLAIN>
 __global__ void __launch_bounds__(NT)
 union_qm_kernel(const UnionParams p) {
   constexpr int kUnionThreads = NT;
@@ -136,9 +140,10 @@ union_qm_kernel(const UnionParams p) {
   // phase 3: exclusive rank of every bitmap word (or every 2^rank_shift-th word)
   {
     int r = before + incl - mine;
-    const int rmask = (1 << p.rank_shift) - 1;
+    const int rank_shift = PLAIN ? 0 : p.rank_shift;
+    const int rmask = (1 << rank_shift) - 1;
     for (int w = w0; w < w1; ++w) {
-      if ((w & rmask) == 0) rtab[w >> p.rank_shift] = (uint16_t)r;
+      if ((w & rmask) == 0) rtab[w >> rank_shift] = (uint16_t)r;
       r += __popc(bm[w]);
     }
   }
@@ -149,20 +154,25 @@ union_qm_kernel(const UnionParams p) {
 
   // phase 4: every candidate looks up its rank, sets its token's membership bit and
   // writes its own slot of the sorted list (duplicates write the same value)
-  const int32_t* bt_row = p.btab ? p.btab + (size_t)p.req_pg[g] * p.bt_stride : nullptr;
+  const int32_t* bt_row = (!PLAIN && p.btab) ? p.btab + (size_t)p.req_pg[g] * p.bt_stride : nullptr;
   int32_t* out_row = p.u_phys + (size_t)g * cap;
   int32_t* list_dst = p.stage_list ? list_s : out_row;
   auto mark = [&](int pos, int qrow) {
     if ((unsigned)pos >= (unsigned)S) return;
     const int w = pos >> 5;
-    int r = rtab[w >> p.rank_shift];
-    if (p.rank_shift)
-      for (int x = (w >> p.rank_shift) << p.rank_shift; x < w; ++x) r += __popc(bm[x]);
+    int r;
+    if (PLAIN) {
+      r = rtab[w];
+    } else {
+      r = rtab[w >> p.rank_shift];
+      if (p.rank_shift)
+        for (int x = (w >> p.rank_shift) << p.rank_shift; x < w; ++x) r += __popc(bm[x]);
+    }
     r += __popc(bm[w] & ((1u << (pos & 31)) - 1u));
     if (r >= cap) return;
     atomicOr(&qm_s[qrow + (r >> 5)], 1u << (r & 31));
     int phys = pos;
-    if (bt_row) {
+    if (!PLAIN && bt_row) {
       const int blk = fast_div(pos, p.bsz, p.bsz_mul);
       phys = blk < p.bt_blocks ? bt_row[blk] * p.bsz + (pos - blk * p.bsz) : -1;
     }
@@ -218,7 +228,8 @@ union_qm_kernel(const UnionParams p) {
 template <int NT, int VPT>
 static int launch_union(const UnionParams& p, int ng, size_t smem, cudaStream_t stream) {
   constexpr int kUnionThreads = NT;
-  auto kern = union_qm_kernel<NT, VPT>;
+  const bool plain = p.btab == nullptr && p.rank_shift == 0;
+  auto kern = plain ? union_qm_kernel<NT, VPT, true> : union_qm_kernel<NT, VPT, false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return LITEDSA_ERR_CUDA;
   kern<<<ng, kUnionThreads, smem, stream>>>(p);
