@@ -323,6 +323,42 @@ int litedsa_masked_mla_fp8_kv656_noalloc(const void* q8, const void* kv656, cons
                                          int64_t indices_row_stride, int* mismatch_flag,
                                          void* stream);
 
+/*
+ * The step before the union: index logits and top-k selection, producing the
+ * `topk_indices [T, k] i32` tensor that litedsa_union_qm takes
+ * (kernels/b200/dsa/litedsa.cu:31-33).  The reference repository removed its own indexer
+ * (README.md:3-6), so these two entry points have NO counterpart there; they implement the
+ * published FP8 form of the DeepSeek-V3.2 lightning indexer:
+ *
+ *   logit[t, s] = k_scale[s] * sum_h weights[t, h] * relu(q_idx8[t, h, :] . k_idx8[s, :])
+ *
+ * for the T query tokens at positions q_pos0 .. q_pos0 + T - 1 and the keys s <= position.
+ *   q_idx8   [T, Hi, 128] e4m3 codes, dense, Hi in {32, 64, 128}
+ *   k_idx8   [S, 128] e4m3 codes, rows k_row_stride bytes apart (multiple of 16)
+ *   weights  [T, Hi] fp32 (head weight x query scale x softmax scale)
+ *   k_scale  [S] fp32 or NULL (1.0)
+ *   logits   [T, logits_row_stride] fp32.  Written: every s <= q_pos0 + t.  Entries beyond a
+ *            token's position are -inf inside the key tiles its CTA processed and untouched
+ *            beyond; litedsa_topk_select never reads them.
+ * Asynchronous on `stream`; bounded waits report through litedsa_index_status.
+ */
+int litedsa_index_logits_fp8(const void* q_idx8, const void* k_idx8, const float* weights,
+                             const float* k_scale, float* logits, int T, int Hi, int S, int q_pos0,
+                             long long k_row_stride, long long logits_row_stride, void* stream);
+
+/*
+ * Exact top-k of every row of `logits`: topk_idx[t, :] = the k positions i < len(t) with the
+ * largest values, listed in ascending position; ties at the k-th value go to the smaller
+ * positions; NaN sorts below every number.  Rows with len(t) <= k list 0 .. len(t) - 1 and
+ * are padded with -1.  len(t) = lengths[t] (clamped to [0, S]) or, when lengths is NULL,
+ * min(S, q_pos0 + t + 1) (causal).  No allocation, no host synchronisation.
+ */
+int litedsa_topk_select(const float* logits, const int32_t* lengths, int32_t* topk_idx, int T, int S,
+                        int k, int q_pos0, long long logits_row_stride, void* stream);
+
+/* Status block of the index-logits kernel; same layout and return rule as litedsa_attn_status. */
+int litedsa_index_status(int* out4_host, int reset);
+
 #ifdef __cplusplus
 }
 #endif

@@ -408,6 +408,87 @@ def set_wait_limit_ns(limit_ns: int) -> int:
     return int(old.value)
 
 
+# --------------------------------------------------------------------------- indexer + top-k
+def index_logits_fp8(q_idx8: torch.Tensor, k_idx8: torch.Tensor, weights: torch.Tensor,
+                     k_scale: Optional[torch.Tensor], q_pos0: int,
+                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Index logits ``[T, S]`` fp32 of the FP8 lightning indexer:
+    ``k_scale[s] * sum_h weights[t,h] * relu(q_idx8[t,h,:] . k_idx8[s,:])`` for ``s <= q_pos0 + t``.
+
+    ``q_idx8`` [T, Hi, 128] and ``k_idx8`` [S, 128] hold e4m3 codes (uint8 or float8_e4m3fn),
+    ``weights`` [T, Hi] fp32, ``k_scale`` [S] fp32 or None.  Entries beyond a token's position
+    are -inf or untouched (see include/litedsa_b200.h); ``topk_select`` never reads them.
+    """
+    for t, n in ((q_idx8, "q_idx8"), (k_idx8, "k_idx8")):
+        if not t.is_cuda or t.element_size() != 1:
+            raise TypeError(f"{n} must be a CUDA tensor of 1-byte e4m3 codes")
+    _need(weights, "weights", torch.float32, 2)
+    if q_idx8.dim() != 3 or q_idx8.shape[2] != 128 or not q_idx8.is_contiguous():
+        raise ValueError("q_idx8 must be a contiguous [T, Hi, 128] tensor")
+    if k_idx8.dim() != 2 or k_idx8.shape[1] != 128 or k_idx8.stride(1) != 1:
+        raise ValueError("k_idx8 must be [S, 128] with unit inner stride")
+    T, Hi, _ = q_idx8.shape
+    S = k_idx8.shape[0]
+    if tuple(weights.shape) != (T, Hi) or not weights.is_contiguous():
+        raise ValueError("weights must be a contiguous [T, Hi] tensor")
+    if k_scale is not None:
+        _need(k_scale, "k_scale", torch.float32, 1)
+        if k_scale.numel() != S or not k_scale.is_contiguous():
+            raise ValueError("k_scale must be a contiguous [S] tensor")
+    if out is None:
+        out = torch.empty((T, S), dtype=torch.float32, device=q_idx8.device)
+    _need(out, "out", torch.float32, 2)
+    if out.shape[0] != T or out.shape[1] < S or out.stride(1) != 1:
+        raise ValueError("out must be [T, >= S] fp32 with unit inner stride")
+    with torch.cuda.device(q_idx8.device):
+        check(_lib.lib().litedsa_index_logits_fp8(_ptr(q_idx8), _ptr(k_idx8), _ptr(weights), _ptr(k_scale),
+                                                  _ptr(out), T, Hi, S, int(q_pos0), k_idx8.stride(0),
+                                                  out.stride(0), _stream(q_idx8)), "index_logits_fp8")
+    return out
+
+
+def topk_select(logits: torch.Tensor, k: int, *, q_pos0: int = 0, lengths: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Exact top-``k`` positions of every row of ``logits`` [T, S] fp32 among its first
+    ``lengths[t]`` entries (default: causal, ``min(S, q_pos0 + t + 1)``), ascending in position,
+    ties at the k-th value towards smaller positions, -1 padding for short rows.  The result is
+    the ``topk_idx`` tensor ``union_qm`` takes."""
+    _need(logits, "logits", torch.float32, 2)
+    if logits.stride(1) != 1:
+        raise ValueError("logits must have unit inner stride")
+    T, S = logits.shape
+    if lengths is not None:
+        _need(lengths, "lengths", torch.int32, 1)
+        if lengths.numel() != T or not lengths.is_contiguous():
+            raise ValueError("lengths must be a contiguous [T] int32 tensor")
+    if out is None:
+        out = torch.empty((T, int(k)), dtype=torch.int32, device=logits.device)
+    _need(out, "out", torch.int32, 2)
+    if tuple(out.shape) != (T, int(k)) or not out.is_contiguous():
+        raise ValueError("out must be a contiguous [T, k] int32 tensor")
+    with torch.cuda.device(logits.device):
+        check(_lib.lib().litedsa_topk_select(_ptr(logits), _ptr(lengths), _ptr(out), T, S, int(k),
+                                             int(q_pos0), logits.stride(0), _stream(logits)), "topk_select")
+    return out
+
+
+def lite_topk(q_idx8: torch.Tensor, k_idx8: torch.Tensor, weights: torch.Tensor,
+              k_scale: Optional[torch.Tensor], k: int, q_pos0: int, *,
+              logits_workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Indexer + selection in one call: ``topk_idx`` [T, k] int32 (-1 padded) for the T query
+    tokens at positions ``q_pos0 ...`` -- the input of ``union_qm`` / ``sparse_prefill``."""
+    logits = index_logits_fp8(q_idx8, k_idx8, weights, k_scale, q_pos0, out=logits_workspace)
+    S = k_idx8.shape[0]
+    # a workspace wider than S: select over the first S columns of every row
+    view = logits if logits.shape[1] == S else logits.as_strided((logits.shape[0], S), (logits.stride(0), 1))
+    return topk_select(view, k, q_pos0=q_pos0)
+
+
+def index_status(reset: bool = False, device=None) -> Tuple[int, int, int, int]:
+    """Status word of the index-logits kernel (see :func:`attn_status`)."""
+    return _status("litedsa_index_status", reset, device)
+
+
 # --------------------------------------------------------------------------- operand preparation
 def quantize_e4m3(x: torch.Tensor, scale: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """e4m3 codes (uint8) of ``x / scale`` for a contiguous bf16 CUDA tensor (saturating)."""

@@ -18,7 +18,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OUT_DIR = PKG / "_C"
 LIB = OUT_DIR / "liblitedsa_b200.so"
-SOURCES = ["abi.cu", "union_qm.cu", "attn_fp8.cu", "prep.cu", "noalloc.cu", "attn_dsv4.cu", "attn_bf16.cu", "peak_probe.cu"]
+SOURCES = ["abi.cu", "union_qm.cu", "attn_fp8.cu", "prep.cu", "noalloc.cu", "attn_dsv4.cu", "attn_bf16.cu", "peak_probe.cu", "index_topk.cu"]
 
 
 def _nvcc() -> str:

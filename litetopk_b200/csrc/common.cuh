@@ -214,6 +214,15 @@ __device__ __forceinline__ void tma_load_3d_hint(uint32_t dst_smem, const CUtens
       ::"r"(dst_smem), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(mbar)), "l"(pol)
       : "memory");
 }
+// tiled 2-D load into this CTA's smem, completion bytes on this CTA's own barrier
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst_smem, const CUtensorMap* map, int x, int y,
+                                                 uint64_t* mbar, uint64_t pol) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      ".L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
+      ::"r"(dst_smem), "l"(map), "r"(x), "r"(y), "r"(smem_u32(mbar)), "l"(pol)
+      : "memory");
+}
 // TMA 3-D tile store shared -> global (bulk async-group completion)
 __device__ __forceinline__ void tma_store_3d_hint(const void* map, uint32_t src_smem, int x, int y,
                                                   int z, uint64_t pol) {
@@ -296,6 +305,34 @@ __device__ __forceinline__ void tmem_relinquish_pair() {
 }
 __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+// single-CTA (cta_group::1) forms: TMEM allocation, one FP8 MMA with shared-memory operands,
+// commit to a barrier of this CTA.  Issued by ONE thread (mma / commit) or one warp (alloc).
+__device__ __forceinline__ void tmem_alloc_cta(uint32_t* dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(dst_smem)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_cta() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_cta(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void mma_f8_cta(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                           uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit_cta(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+               ::"r"(smem_u32(bar))
                : "memory");
 }
 // A whole K-loop of MMAs in one instruction stream, executed by a fully converged warp whose

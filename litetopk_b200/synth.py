@@ -283,3 +283,21 @@ def attended_pairs(w: Workload, topk_idx: Optional[torch.Tensor] = None) -> int:
 
 FLOP_PER_PAIR = 2 * D_QK + 2 * D_LATENT  # QK over 576 dims + PV over 512 dims
 SM_SCALE = 1.0 / math.sqrt(192.0)
+
+
+def make_indexer_operands(tokens: int, s_kv: int, index_heads: int = 64, seed: int = 0, device="cpu"):
+    """Synthetic operands of the FP8 lightning indexer: ``q_idx8`` [tokens, Hi, 128] and
+    ``k_idx8`` [s_kv, 128] e4m3 codes (uint8) of N(0,1) values scaled to the e4m3 range,
+    ``weights`` [tokens, Hi] fp32 (head weights ~ N(0,1) / sqrt(Hi) times the query scales and
+    the softmax scale 128^-0.5), ``k_scale`` [s_kv] fp32 (amax / 448 per key)."""
+    gen = _gen(seed * 7919 + 11, device)
+    q = torch.randn((tokens, index_heads, 128), generator=gen, device=device)
+    k = torch.randn((s_kv, 128), generator=gen, device=device)
+    hw = torch.randn((tokens, index_heads), generator=gen, device=device) / index_heads ** 0.5
+    q_scale = q.abs().amax(dim=2).clamp_min(1e-8) / E4M3_MAX            # [tokens, Hi]
+    k_scale = k.abs().amax(dim=1).clamp_min(1e-8) / E4M3_MAX            # [s_kv]
+    q8 = e4m3_codes(q / q_scale[:, :, None])
+    k8 = e4m3_codes(k / k_scale[:, None])
+    weights = (hw * q_scale * 128 ** -0.5).float().contiguous()
+    return q8, k8, weights, k_scale.float().contiguous()
+

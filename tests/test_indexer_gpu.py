@@ -1,0 +1,126 @@
+"""Index logits and top-k selection on the GPU against the CPU oracle.
+
+The reference repository has no indexer any more, so there is no module to compare with:
+the logits are checked against the fp64 restatement of the formula, the selection is checked
+to be EXACT on the kernel's own logits (set, order, tie rule, padding), and the two together
+against the oracle's selection on the oracle's logits."""
+import numpy as np
+import pytest
+import torch
+
+from litetopk_b200 import api, synth
+from oracle import indexer_oracle as io
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _ops(T, S, Hi, seed):
+    q8, k8, w, ks = synth.make_indexer_operands(T, S, Hi, seed=seed)
+    return q8, k8, w, ks
+
+
+@pytest.mark.parametrize("T,S,Hi,pos0", [
+    (64, 1100, 64, 1000),       # S and the causal bound inside a key tile
+    (37, 700, 64, 650),         # token count not a multiple of the CTA's 8 tokens
+    (48, 900, 32, 800),         # 32 index heads: 16 tokens per CTA
+    (20, 520, 128, 500),        # 128 index heads: 4 tokens per CTA
+    (16, 300, 64, 0),           # prefill from position 0: short causal rows
+])
+def test_index_logits_match_the_formula(T, S, Hi, pos0):
+    q8, k8, w, ks = _ops(T, S, Hi, seed=T + S)
+    ref = io.index_logits(q8, k8, w, ks, pos0)                      # fp64
+    got = api.index_logits_fp8(q8.to(DEV), k8.to(DEV), w.to(DEV), ks.to(DEV), pos0)
+    torch.cuda.synchronize()
+    assert api.index_status(reset=True)[0] == 0
+    got = got.cpu().double()
+    valid = torch.arange(S)[None, :] <= (pos0 + torch.arange(T))[:, None]
+    scale = ref[valid].abs().max().item()
+    err = (got[valid] - ref[valid]).abs().max().item()
+    # fp32 accumulation of 64..128 exact products per head and of Hi weighted terms
+    assert err <= 2e-6 * scale * Hi ** 0.5, (err, scale)
+
+
+def test_index_logits_without_key_scales_and_strided_keys():
+    T, S, Hi, pos0 = 24, 400, 64, 390
+    q8, k8, w, _ = _ops(T, S, Hi, seed=9)
+    wide = torch.zeros((S, 160), dtype=torch.uint8)
+    wide[:, :128] = k8
+    ref = io.index_logits(q8, k8, w, None, pos0)
+    got = api.index_logits_fp8(q8.to(DEV), wide.to(DEV)[:, :128], w.to(DEV), None, pos0).cpu().double()
+    valid = torch.arange(S)[None, :] <= (pos0 + torch.arange(T))[:, None]
+    assert (got[valid] - ref[valid]).abs().max().item() <= 2e-5 * ref[valid].abs().max().item()
+
+
+def _random_logits(T, S, seed, levels=None):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn((T, S), generator=g)
+    if levels:                                   # many exact ties
+        x = torch.round(x * levels) / levels
+    return x
+
+
+@pytest.mark.parametrize("T,S,k,pos0,levels", [
+    (32, 4096, 512, 4000, None),
+    (32, 4096, 1024, 3000, 8),               # heavy ties at the threshold
+    (16, 8192, 2048, 8000, None),
+    (24, 3000, 2048, 1900, None),            # rows shorter than, equal to and longer than k
+    (8, 60000, 2048, 59000, None),           # row too long for shared memory: global passes
+    (8, 60000, 512, 59990, 4),
+])
+def test_topk_select_is_exact(T, S, k, pos0, levels):
+    x = _random_logits(T, S, seed=S + k, levels=levels)
+    x[0, 5] = float("nan")
+    ref = io.topk_exact(x, k, q_pos0=pos0)
+    got = api.topk_select(x.to(DEV), k, q_pos0=pos0)
+    torch.cuda.synchronize()
+    assert np.array_equal(got.cpu().numpy(), ref)
+
+
+def test_topk_select_with_lengths_and_row_pitch():
+    T, S, k = 12, 2048, 256
+    x = _random_logits(T, 2304, seed=4)
+    lens = torch.tensor([0, 1, 255, 256, 257, 2048, 2047, 1000, 300, 256, 5, 2048], dtype=torch.int32)
+    ref = io.topk_exact(x[:, :S], k, lengths=lens)
+    xd = x.to(DEV)
+    got = api.topk_select(xd.as_strided((T, S), (2304, 1)), k, lengths=lens.to(DEV))
+    torch.cuda.synchronize()
+    assert np.array_equal(got.cpu().numpy(), ref)
+
+
+def test_lite_topk_feeds_the_union_and_agrees_with_the_oracle():
+    T, S, Hi, k, pos0 = 64, 4096, 64, 512, 4096 - 64
+    q8, k8, w, ks = _ops(T, S, Hi, seed=21)
+    got = api.lite_topk(q8.to(DEV), k8.to(DEV), w.to(DEV), ks.to(DEV), k, pos0)
+    torch.cuda.synchronize()
+    ref_logits = io.index_logits(q8, k8, w, ks, pos0)
+    ref = io.topk_exact(ref_logits.float(), k, q_pos0=pos0)
+    g = got.cpu().numpy()
+    same = sum(len(np.intersect1d(g[t], ref[t])) for t in range(T)) / (T * k)
+    assert same >= 0.999, same              # only near-ties at the threshold may differ
+    tol = 1e-5 * ref_logits[torch.isfinite(ref_logits)].abs().max().item()
+    assert sum(io.check_topk(ref_logits.float(), got, k, q_pos0=pos0, tol=tol).values()) == 0
+    # the selection is a valid input of the union operator
+    u, m, c = api.union_qm(got, 2, seq_space=S, return_counts=True)
+    torch.cuda.synchronize()
+    assert int(c.min()) >= k and int(c.max()) <= 2 * k
+
+
+def test_full_width_rows_sampled():
+    """Config-1-sized rows (32768 keys, k = 2048, 64 heads): 256 tokens at the tail."""
+    T, S, Hi, k = 256, 32768, 64, 2048
+    pos0 = S - T
+    q8, k8, w, ks = _ops(T, S, Hi, seed=33)
+    logits = api.index_logits_fp8(q8.to(DEV), k8.to(DEV), w.to(DEV), ks.to(DEV), pos0)
+    sel = api.topk_select(logits, k, q_pos0=pos0)
+    torch.cuda.synchronize()
+    assert api.index_status(reset=True)[0] == 0
+    rows = [0, 1, 7, 8, 100, 255]
+    ref = io.topk_exact(logits[rows].cpu(), k, lengths=torch.tensor([pos0 + r + 1 for r in rows]))
+    assert np.array_equal(sel[rows].cpu().numpy(), ref)
+    gl = logits[rows].cpu().double()
+    for i, r in enumerate(rows):
+        n = pos0 + r + 1
+        ref_row = io.index_logits(q8[r:r + 1], k8, w[r:r + 1], ks, pos0 + r)[0]
+        d = (gl[i, :n] - ref_row[:n]).abs().max().item()
+        assert d <= 2e-5 * ref_row[:n].abs().max().item()
