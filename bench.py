@@ -477,6 +477,52 @@ def native_record(api, w, dev, steps, bf16_peak):
     return rec
 
 
+def indexer_record(api, w, dev, steps, fp8_peak, hbm_gbs, index_heads=64):
+    """The step before the union on the headline's shape: FP8 index logits of the config's query
+    tokens against its whole KV length, then the exact top-k selection that yields topk_idx."""
+    T, S, k = w.tokens, w.s_kv, w.topk
+    pos0 = S - T
+    q8, k8, wts, ks = synth.make_indexer_operands(T, S, index_heads, seed=1, device=dev)
+    logits = torch.empty((T, S), dtype=torch.float32, device=dev)
+    sel = torch.empty((T, k), dtype=torch.int32, device=dev)
+    f_log = lambda: api.index_logits_fp8(q8, k8, wts, ks, pos0, out=logits)  # noqa: E731
+    f_sel = lambda: api.topk_select(logits, k, q_pos0=pos0, out=sel)  # noqa: E731
+    api.index_status(reset=True)
+    f_log(); f_sel()
+    log_ms = cuda_time(f_log, steps)
+    sel_ms = cuda_time(f_sel, steps)
+    step_ms = cuda_time(lambda: (f_log(), f_sel()), steps)
+    if api.index_status()[0] != 0:
+        raise SystemExit("device-side wait expired")
+    # causal (token, key) pairs; every pair costs Hi x 128 multiply-adds
+    pairs = T * pos0 + T * (T + 1) // 2
+    flop = 2.0 * pairs * index_heads * 128
+    ach = flop / (log_ms * 1e-3) / 1e12
+    sel_gbs = (pairs * 4 + T * k * 4) / (sel_ms * 1e-3) / 1e9
+    # spot check of the selection on a few rows: count, range and threshold property on the kernel's logits
+    rows = [0, T // 2, T - 1]
+    lg = logits[rows].cpu()
+    sl = sel[rows].cpu()
+    ok = True
+    for i, r in enumerate(rows):
+        n = pos0 + r + 1
+        live = sl[i][sl[i] >= 0].long()
+        ok &= int(live.numel()) == min(k, n) and int(live.unique().numel()) == int(live.numel())
+        if n > k and live.numel():
+            rest = torch.ones(n, dtype=torch.bool)
+            rest[live] = False
+            ok &= bool(lg[i, :n][rest].max() <= lg[i, live].min())
+    rec = {"workload": f"{w.name} shape: {T} query tokens x {S} keys, {index_heads} index heads of dim 128 (e4m3), "
+                       f"top-k {k}", "route": "index_logits_fp8 -> topk_select -> topk_idx",
+           "ms_per_step": step_ms, "value": T / (step_ms * 1e-3), "unit": "tokens/s",
+           "logits_ms": log_ms, "logits_tflops": ach, "logits_frac": ach / fp8_peak, "logits_peak": fp8_peak,
+           "select_ms": sel_ms, "select_gbs": sel_gbs, "select_frac": sel_gbs / hbm_gbs, "select_peak_gbs": hbm_gbs,
+           "selection_checked": bool(ok), "dtype": "e4m3"}
+    del q8, k8, wts, ks, logits, sel
+    torch.cuda.empty_cache()
+    return rec
+
+
 def host_copy_bandwidth(dev, mb=256):
     """Plain pinned-memory copy rates of this rank (GB/s): the bound of the end-to-end leg."""
     n = mb << 20
@@ -691,6 +737,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=0,
                     help="shrink the workload to this many query tokens per GPU (profiling aid; "
                          "the default, the full configuration, is the only benchmark number)")
+    ap.add_argument("--only-indexer", action="store_true",
+                    help="run only the indexer + top-k leg on the chosen config's shape (profiling aid)")
     ap.add_argument("--only-native", action="store_true",
                     help="run only the native-cache (bf16 route) record of the workload and print it "
                          "(profiling aid for masked_mla_bf16_kernel)")
@@ -716,6 +764,12 @@ def main():
         torch.cuda.set_device(0)
         print(json.dumps(native_record(api, w, torch.device("cuda", 0), args.steps, load_peaks()["bf16_tflops"])),
               flush=True)
+        return
+    if args.only_indexer:
+        torch.cuda.set_device(0)
+        pk = load_peaks()
+        print(json.dumps(indexer_record(api, w, torch.device("cuda", 0), args.steps, 2 * pk["bf16_tflops"],
+                                        pk["hbm_gbs"])), flush=True)
         return
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -868,6 +922,7 @@ def main():
                              "compute_only_ms": cfgs["c4"]["ms_per_step"], "gather": "none",
                              "note": "config 4 on one GPU: the base of the strong-scaling curve"}
         line["native"] = native_record(api, synth.CONFIGS["c1"], dev, sec_steps, peaks["bf16_tflops"])
+        line["indexer"] = indexer_record(api, synth.CONFIGS["c1"], dev, sec_steps, fp8_peak, peaks["hbm_gbs"])
     elif extras:
         # config 4 split over the ranks (strong scaling) with the all-gather of its outputs
         w4 = synth.CONFIGS["c4"]

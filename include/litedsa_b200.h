@@ -348,9 +348,10 @@ int litedsa_index_logits_fp8(const void* q_idx8, const void* k_idx8, const float
 
 /*
  * Exact top-k of every row of `logits`: topk_idx[t, :] = the k positions i < len(t) with the
- * largest values, listed in ascending position; ties at the k-th value go to the smaller
- * positions; NaN sorts below every number.  Rows with len(t) <= k list 0 .. len(t) - 1 and
- * are padded with -1.  len(t) = lengths[t] (clamped to [0, S]) or, when lengths is NULL,
+ * largest values; ties at the k-th value go to the smaller positions; NaN sorts below every
+ * number.  The selected SET is exact and reproducible; the order inside a row is fixed for a
+ * given input but not specified (the union operator does not depend on it).  Rows with
+ * len(t) <= k list 0 .. len(t) - 1 and are padded with -1 at the end.  len(t) = lengths[t] (clamped to [0, S]) or, when lengths is NULL,
  * min(S, q_pos0 + t + 1) (causal).  No allocation, no host synchronisation.
  */
 int litedsa_topk_select(const float* logits, const int32_t* lengths, int32_t* topk_idx, int T, int S,

@@ -450,9 +450,10 @@ def index_logits_fp8(q_idx8: torch.Tensor, k_idx8: torch.Tensor, weights: torch.
 def topk_select(logits: torch.Tensor, k: int, *, q_pos0: int = 0, lengths: Optional[torch.Tensor] = None,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Exact top-``k`` positions of every row of ``logits`` [T, S] fp32 among its first
-    ``lengths[t]`` entries (default: causal, ``min(S, q_pos0 + t + 1)``), ascending in position,
-    ties at the k-th value towards smaller positions, -1 padding for short rows.  The result is
-    the ``topk_idx`` tensor ``union_qm`` takes."""
+    ``lengths[t]`` entries (default: causal, ``min(S, q_pos0 + t + 1)``): the selected set is
+    exact (ties at the k-th value towards smaller positions), the order inside a row is not
+    specified, short rows are padded with -1 at the end.  The result is the ``topk_idx`` tensor
+    ``union_qm`` takes."""
     _need(logits, "logits", torch.float32, 2)
     if logits.stride(1) != 1:
         raise ValueError("logits must have unit inner stride")

@@ -223,6 +223,15 @@ __device__ __forceinline__ void tma_load_2d_hint(uint32_t dst_smem, const CUtens
       ::"r"(dst_smem), "l"(map), "r"(x), "r"(y), "r"(smem_u32(mbar)), "l"(pol)
       : "memory");
 }
+// untiled bulk copy global -> this CTA's shared memory (both addresses 16-byte aligned, size a
+// multiple of 16), completion bytes on this CTA's own barrier
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void* src, uint32_t bytes,
+                                             uint64_t* mbar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(smem_u32(mbar))
+      : "memory");
+}
 // TMA 3-D tile store shared -> global (bulk async-group completion)
 __device__ __forceinline__ void tma_store_3d_hint(const void* map, uint32_t src_smem, int x, int y,
                                                   int z, uint64_t pol) {

@@ -19,14 +19,17 @@
 // one thread.  One CTA owns 2 x 256 / Hi tokens: their q rows are the B operand of two
 // N = 256 accumulators (512 TMEM columns); the K tiles (128 keys x 128 bytes, TMA, four
 // stages) are the A operand and are streamed once per CTA, up to the causal bound of its
-// last token.  While the tensor core fills one accumulator, four warps drain the other:
-// tcgen05.ld, relu, multiply by the head weight, add; then x k_scale, causal mask, and 128
-// consecutive fp32 logits per token leave each warp as coalesced stores.
+// last token.  While the tensor core fills one accumulator, eight warps drain the other
+// (lane quarter x column half): tcgen05.ld, relu, multiply by the head weight, add; then
+// x k_scale, causal mask, and 128 consecutive fp32 logits per token leave each warp as
+// coalesced stores.
 //
-// topk_select_kernel (memory-bound): one CTA per token row.  Exact radix select (11 + 11 + 10
-// bits of the order-preserving integer image of the fp32 logits) over the row held in shared
-// memory, then one ordered emission pass: the output is ascending in position, ties at the
-// k-th value are resolved towards the smaller position, so the result is deterministic.
+// topk_select (memory-bound): exact selection per token row.  Rows up to 32768 entries go
+// through persistent CTAs that prefetch the next row with a bulk copy while the current one
+// is processed from registers (value-linear histogram, exact ranking of the threshold bin);
+// longer rows through a radix select over the order-preserving integer image of the logits.
+// Ties at the k-th value are resolved towards the smaller position, so the selected set is
+// deterministic; the order inside a row is not specified.
 #include "common.cuh"
 #include "tensor_map.cuh"
 
@@ -34,7 +37,7 @@ namespace lt {
 namespace idx {
 
 // ------------------------------------------------------------------ index logits
-constexpr int kThreads = 384;
+constexpr int kThreads = 640;             // TMA, MMA, TMEM warps + 16 drain warps
 constexpr int kKeyTile = 128;             // keys per MMA (M)
 constexpr int kCols = 256;                // (token, head) columns per accumulator (N)
 constexpr int kDim = 128;                 // index head dim = bytes per row
@@ -65,6 +68,15 @@ struct LogitParams {
 
 enum { kSiteQFull = 1, kSiteKFull, kSiteKFree, kSiteAccFull, kSiteAccFree };
 
+// packed fp32 pair fma (one issue slot for two lanes of work)
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(reinterpret_cast<unsigned long long&>(d))
+      : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)),
+        "l"(reinterpret_cast<unsigned long long&>(c)));
+  return d;
+}
+
 __device__ int g_status[8];
 
 template <int HI>
@@ -90,15 +102,16 @@ index_logits_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   if (threadIdx.x == 0) {
     mbar_init(&bar.q_full, 1);
     for (int i = 0; i < kStages; ++i) { mbar_init(&bar.k_full[i], 1); mbar_init(&bar.k_free[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&bar.acc_full[i], 1); mbar_init(&bar.acc_free[i], 4); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&bar.acc_full[i], 1); mbar_init(&bar.acc_free[i], 8); }
     fence_mbar_init();
     tma_prefetch_desc(&map_q);
     tma_prefetch_desc(&map_k);
   }
-  // head weights of the CTA's tokens: column c of accumulator a is row tok0 * Hi + 256 a + c
+  // head weights of the CTA's tokens: column c of accumulator a is row tok0 * Hi + 256 a + c.
+  // Halved: the drain computes relu(x) as (x + |x|) / 2 with the division folded in here.
   for (int i = threadIdx.x; i < 2 * kCols; i += kThreads) {
     const long long r = (long long)tok0 * HI + i;
-    wsm[i] = r < (long long)p.T * HI ? __ldg(p.weights + r) : 0.f;
+    wsm[i] = r < (long long)p.T * HI ? 0.5f * __ldg(p.weights + r) : 0.f;
   }
   __syncthreads();
   if (warp == 2) {
@@ -150,46 +163,53 @@ index_logits_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
   } else if (warp >= 4) {
     // ---------------------------------------------------------------- accumulator drain
-    const int a = (warp - 4) >> 2;                      // which accumulator
+    // Sixteen warps: accumulator a, column half hf (128 columns = tpa / 2 whole tokens), TMEM
+    // lane quarter q4.  relu(x) * w is computed as (x + |x|) * (w / 2): an add with an absolute-
+    // value operand and a packed fma, both on the fma pipe (a max would go to the half-rate
+    // integer pipe, which then paces the kernel).
+    const int dw = warp - 4;
+    const int a = dw >> 3, hf = (dw >> 2) & 1;
     const int q4 = warp & 3;                            // TMEM lane quarter of this warp
     const int krow = 32 * q4 + lane;                    // key row of the tile = TMEM lane
-    const uint32_t tcol = tmem + ((uint32_t)(32 * q4) << 16) + a * kCols;
-    const float* w = wsm + a * kCols;
-    const int t_base = tok0 + a * tpa;
+    const uint32_t tcol = tmem + ((uint32_t)(32 * q4) << 16) + a * kCols + 128 * hf;
+    const float* w = wsm + a * kCols + 128 * hf;
+    constexpr int tph = tpa / 2;                        // tokens per column half
+    const int t_base = tok0 + a * tpa + hf * tph;
     for (int j = 0; j < n_tiles; ++j) {
+      // this key's scale is fetched before the wait, so its latency hides behind the MMAs
+      const int s_key = j * kKeyTile + krow;
+      const float ks = (p.k_scale && s_key < p.S) ? __ldg(p.k_scale + s_key) : 1.f;
       if (!mbar_wait(&bar.acc_full[a], j & 1, wt, kSiteAccFull, j)) break;
       __syncwarp();
       tc_fence_after();
-      float acc[tpa];
+      float acc[tph];
 #pragma unroll
-      for (int i = 0; i < tpa; ++i) acc[i] = 0.f;
+      for (int i = 0; i < tph; ++i) acc[i] = 0.f;
       float x[2][32];
       tmem_ld32(tcol, x[0]);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < 4; ++c) {
         tmem_wait_ld();
-        if (c < 7) tmem_ld32(tcol + 32 * (c + 1), x[(c + 1) & 1]);
+        if (c < 3) tmem_ld32(tcol + 32 * (c + 1), x[(c + 1) & 1]);
         const float* xc = x[c & 1];
-        float sum = 0.f;
+        // two packed fma chains (four independent partial sums) per 32 columns
+        float2 s0 = make_float2(0.f, 0.f), s1 = make_float2(0.f, 0.f);
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
           const float4 w4 = *reinterpret_cast<const float4*>(w + 32 * c + i);
-          sum = fmaf(fmaxf(xc[i], 0.f), w4.x, sum);
-          sum = fmaf(fmaxf(xc[i + 1], 0.f), w4.y, sum);
-          sum = fmaf(fmaxf(xc[i + 2], 0.f), w4.z, sum);
-          sum = fmaf(fmaxf(xc[i + 3], 0.f), w4.w, sum);
+          s0 = fma2(make_float2(xc[i] + fabsf(xc[i]), xc[i + 1] + fabsf(xc[i + 1])), make_float2(w4.x, w4.y), s0);
+          s1 = fma2(make_float2(xc[i + 2] + fabsf(xc[i + 2]), xc[i + 3] + fabsf(xc[i + 3])),
+                    make_float2(w4.z, w4.w), s1);
         }
-        acc[(32 * c) / HI] += sum;   // a 32-column chunk never straddles two tokens (HI >= 32)
+        acc[(32 * c) / HI] += (s0.x + s0.y) + (s1.x + s1.y);   // a chunk never straddles two tokens
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar.acc_free[a]);
       // scale, causal mask, store: lanes of a warp hold 32 consecutive keys
-      const int s_key = j * kKeyTile + krow;
       if (s_key < p.S) {
-        const float ks = p.k_scale ? __ldg(p.k_scale + s_key) : 1.f;
 #pragma unroll
-        for (int tt = 0; tt < tpa; ++tt) {
+        for (int tt = 0; tt < tph; ++tt) {
           const int t = t_base + tt;
           if (t >= p.T) continue;
           const float v = s_key <= p.q_pos0 + t ? acc[tt] * ks : -INFINITY;
@@ -208,9 +228,9 @@ index_logits_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 }
 
 // ------------------------------------------------------------------ top-k selection
-constexpr int kSelThreads = 512;
 constexpr int kBins = 2048;
 constexpr int kMaxSmemRow = 49152;       // keys of a row held in shared memory (192 KB)
+constexpr int kCandCap = 4096;           // keys of the threshold bin kept in shared memory
 
 struct SelParams {
   const float* logits;      // [T, ld]
@@ -218,86 +238,130 @@ struct SelParams {
   int32_t* out;             // [T, k]
   int T, S, k, q_pos0;
   long long ld;
+  int epoch;
+  unsigned long long wait_limit_ns;
 };
 
-// order-preserving map fp32 -> u32 (NaN sorts lowest)
+// order-preserving map fp32 -> u32 (NaN sorts lowest, -0 and +0 share one key) and its inverse
 __device__ __forceinline__ uint32_t okey(float f) {
   if (f != f) return 0u;
-  const uint32_t b = __float_as_uint(f);
+  const uint32_t b = f == 0.f ? 0u : __float_as_uint(f);
   return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
+__device__ __forceinline__ float okey_inv(uint32_t u) {
+  return __uint_as_float((u & 0x80000000u) ? (u & 0x7fffffffu) : ~u);
+}
 
-template <bool kSmemRow>
-__global__ void __launch_bounds__(kSelThreads)
-topk_select_kernel(const SelParams p) {
-  extern __shared__ __align__(16) uint32_t rowkeys[];
-  __shared__ uint32_t hist[kBins];
-  __shared__ uint32_t warp_tot[kSelThreads / 32];
-  __shared__ uint32_t sel_bin, sel_rem;
-  __shared__ uint32_t wgt[kSelThreads / 32], weq[kSelThreads / 32];
+struct SelShared {
+  uint32_t hist[kBins];
+  uint32_t cand[kCandCap];
+  uint32_t wa[32], wb[32];
+  uint32_t sel_bin, sel_rem, n_cand, kth, ties;
+};
 
-  const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-  const int n = p.lengths ? min(max(p.lengths[t], 0), p.S) : min(p.S, max(p.q_pos0 + t + 1, 0));
-  int32_t* out = p.out + (long long)t * p.k;
-  const float* row = p.logits + (long long)t * p.ld;
-  if (n <= p.k) {            // everything valid is selected
-    for (int i = tid; i < p.k; i += kSelThreads) out[i] = i < n ? i : -1;
-    return;
-  }
-  if (kSmemRow) {
-    for (int i = tid; i < n; i += kSelThreads) rowkeys[i] = okey(__ldg(row + i));
-    __syncthreads();
-  }
-  auto key_at = [&](int i) -> uint32_t { return kSmemRow ? rowkeys[i] : okey(__ldg(row + i)); };
-
-  // three digits, most significant first: (shift, bits) = (21, 11), (10, 11), (0, 10)
-  uint32_t prefix = 0, prefix_mask = 0, rem = (uint32_t)p.k;
-#pragma unroll 1
-  for (int pass = 0; pass < 3; ++pass) {
-    const int shift = pass == 0 ? 21 : (pass == 1 ? 10 : 0);
-    const uint32_t dmask = pass == 2 ? 0x3FFu : 0x7FFu;
-    for (int i = tid; i < kBins; i += kSelThreads) hist[i] = 0;
-    __syncthreads();
-    for (int i = tid; i < n; i += kSelThreads) {
-      const uint32_t u = key_at(i);
-      if ((u & prefix_mask) == prefix) atomicAdd(&hist[(u >> shift) & dmask], 1u);
-    }
-    __syncthreads();
-    // thread i owns bins 4i .. 4i+3; suffix sums from the top: find the bin b with
-    // count(bins > b) < rem <= count(bins >= b)
-    const uint32_t h0 = hist[4 * tid], h1 = hist[4 * tid + 1], h2 = hist[4 * tid + 2], h3 = hist[4 * tid + 3];
-    const uint32_t mine = h0 + h1 + h2 + h3;
-    uint32_t incl = mine;                    // inclusive suffix sum within the warp (towards higher lanes)
+// block-wide max / min of two values (all threads get the result); ends with a barrier
+template <int NT>
+__device__ __forceinline__ void block_max_min(SelShared& sh, uint32_t& vmax, uint32_t& vmin) {
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
 #pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-      const uint32_t v = __shfl_down_sync(0xffffffffu, incl, off);
-      if (lane + off < 32) incl += v;
-    }
-    if (lane == 0) warp_tot[wid] = incl;
-    __syncthreads();
-    uint32_t above = 0;                      // elements in bins owned by higher threads
-    for (int w = wid + 1; w < kSelThreads / 32; ++w) above += warp_tot[w];
-    above += incl - mine;
-    if (above < rem && rem <= above + mine) {          // the crossing is in my four bins
-      uint32_t a = above;
-      int b = 4 * tid + 3;
-      if (a + h3 >= rem) { b = 4 * tid + 3; }
-      else if ((a += h3, a + h2 >= rem)) { b = 4 * tid + 2; }
-      else if ((a += h2, a + h1 >= rem)) { b = 4 * tid + 1; }
-      else { a += h1; b = 4 * tid; }
-      sel_bin = (uint32_t)b;
-      sel_rem = rem - a;
-    }
-    __syncthreads();
-    prefix |= sel_bin << shift;
-    prefix_mask |= dmask << shift;
-    rem = sel_rem;
-    __syncthreads();
+  for (int off = 16; off > 0; off >>= 1) {
+    vmax = max(vmax, __shfl_xor_sync(0xffffffffu, vmax, off));
+    vmin = min(vmin, __shfl_xor_sync(0xffffffffu, vmin, off));
   }
-  // prefix = the k-th largest key; rem = how many elements equal to it are taken (smallest
-  // positions first).  Ordered emission: warp w owns a contiguous segment of the row.
-  const uint32_t kth = prefix;
-  const int seg = (((n + kSelThreads / 32 - 1) / (kSelThreads / 32)) + 31) & ~31;
+  if (lane == 0) { sh.wa[wid] = vmax; sh.wb[wid] = vmin; }
+  __syncthreads();
+  uint32_t a = lane < NT / 32 ? sh.wa[lane] : 0u, b = lane < NT / 32 ? sh.wb[lane] : 0xffffffffu;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    a = max(a, __shfl_xor_sync(0xffffffffu, a, off));
+    b = min(b, __shfl_xor_sync(0xffffffffu, b, off));
+  }
+  vmax = a; vmin = b;
+  __syncthreads();
+}
+
+// Block-wide: given hist[0 .. kBins) and `rem`, find the bin b with count(bins > b) < rem <=
+// count(bins >= b); returns b and the rank inside the bin (rem - count(bins > b)).  Thread i
+// owns kBins / NT consecutive bins.  Ends with a barrier; hist may be reused afterwards.
+template <int NT>
+__device__ __forceinline__ uint32_t find_bin(SelShared& sh, uint32_t rem, uint32_t* rem_out) {
+  constexpr int BPT = kBins / NT;
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  uint32_t h[BPT], mine = 0;
+#pragma unroll
+  for (int i = 0; i < BPT; ++i) { h[i] = sh.hist[BPT * tid + i]; mine += h[i]; }
+  uint32_t incl = mine;                      // inclusive suffix sum within the warp (towards higher lanes)
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const uint32_t v = __shfl_down_sync(0xffffffffu, incl, off);
+    if (lane + off < 32) incl += v;
+  }
+  if (lane == 0) sh.wa[wid] = incl;
+  __syncthreads();
+  // suffix sum over the warp totals (every warp computes it; NT / 32 <= 32 entries)
+  uint32_t wt = lane < NT / 32 ? sh.wa[lane] : 0u, wsuf = wt;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const uint32_t v = __shfl_down_sync(0xffffffffu, wsuf, off);
+    if (lane + off < 32) wsuf += v;
+  }
+  const uint32_t above_warps = __shfl_sync(0xffffffffu, wsuf - wt, wid);   // totals of the higher warps
+  uint32_t above = above_warps + incl - mine;                             // + higher lanes of my warp
+  if (above < rem && rem <= above + mine) {  // the crossing is in my bins: walk them from the top
+    int b = BPT - 1;
+#pragma unroll
+    for (int i = BPT - 1; i > 0; --i)
+      if (b == i && above + h[i] < rem) { above += h[i]; b = i - 1; }
+    sh.sel_bin = (uint32_t)(BPT * tid + b);
+    sh.sel_rem = rem - above;
+  }
+  __syncthreads();
+  *rem_out = sh.sel_rem;
+  const uint32_t bsel = sh.sel_bin;
+  __syncthreads();
+  return bsel;
+}
+
+// Block-wide exact radix select over m keys get(0 .. m): the rem-th largest key and how many
+// keys equal to it belong to the top rem.  Digits of up to 11 bits, most significant first,
+// starting at the highest bit in which kmax and kmin (the range of the keys) differ.
+template <int NT, class Get>
+__device__ __forceinline__ uint32_t radix_kth(SelShared& sh, Get get, int m, uint32_t kmax, uint32_t kmin,
+                                              uint32_t rem, uint32_t* ties_out) {
+  const int tid = threadIdx.x;
+  const int top = kmax == kmin ? -1 : 31 - __clz(kmax ^ kmin);
+  uint32_t prefix_mask = top < 0 ? 0xffffffffu : (top >= 31 ? 0u : ~((2u << top) - 1u));
+  uint32_t prefix = kmax & prefix_mask;
+  int hi = top;                              // highest bit not yet decided
+#pragma unroll 1
+  while (hi >= 0) {
+    const int bits = min(11, hi + 1);
+    const int shift = hi + 1 - bits;
+    const uint32_t dmask = (1u << bits) - 1u;
+    for (int i = tid; i < kBins; i += NT) sh.hist[i] = 0;
+    __syncthreads();
+    for (int i = tid; i < m; i += NT) {
+      const uint32_t u = get(i);
+      if ((u & prefix_mask) == prefix) atomicAdd(&sh.hist[(u >> shift) & dmask], 1u);
+    }
+    __syncthreads();
+    const uint32_t b = find_bin<NT>(sh, rem, &rem);
+    prefix |= b << shift;
+    prefix_mask |= dmask << shift;
+    hi = shift - 1;
+  }
+  *ties_out = rem;
+  return prefix;
+}
+
+// Block-wide ordered emission: out[slot] = i for every selected position i, ascending, where
+// selected = key > kth, or key == kth and fewer than `ties` equal keys precede it.  Warp w owns
+// a contiguous segment of the row; slot = #greater before i + min(#equal before i, ties).
+template <int NT, class Get>
+__device__ __forceinline__ void emit_ordered(SelShared& sh, Get key_at, int n, uint32_t kth, uint32_t ties,
+                                             int32_t* out, int k) {
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int seg = (((n + NT / 32 - 1) / (NT / 32)) + 31) & ~31;
   const int s0 = min(wid * seg, n), s1 = min(s0 + seg, n);
   uint32_t cgt = 0, ceq = 0;
   for (int i = s0 + lane; i < s1; i += 32) {
@@ -310,10 +374,11 @@ topk_select_kernel(const SelParams p) {
     cgt += __shfl_xor_sync(0xffffffffu, cgt, off);
     ceq += __shfl_xor_sync(0xffffffffu, ceq, off);
   }
-  if (lane == 0) { wgt[wid] = cgt; weq[wid] = ceq; }
+  __syncthreads();
+  if (lane == 0) { sh.wa[wid] = cgt; sh.wb[wid] = ceq; }
   __syncthreads();
   uint32_t gt_run = 0, eq_run = 0;
-  for (int w = 0; w < wid; ++w) { gt_run += wgt[w]; eq_run += weq[w]; }
+  for (int w = 0; w < wid; ++w) { gt_run += sh.wa[w]; eq_run += sh.wb[w]; }
   const uint32_t lt_mask = (1u << lane) - 1u;
   for (int i0 = s0; i0 < s1; i0 += 32) {
     const int i = i0 + lane;
@@ -322,12 +387,469 @@ topk_select_kernel(const SelParams p) {
     const uint32_t bg = __ballot_sync(0xffffffffu, gt), be = __ballot_sync(0xffffffffu, eq);
     const uint32_t gt_before = gt_run + __popc(bg & lt_mask);
     const uint32_t eq_before = eq_run + __popc(be & lt_mask);
-    if (gt || (eq && eq_before < rem)) {
-      const uint32_t slot = gt_before + min(eq_before, rem);
-      if (slot < (uint32_t)p.k) out[slot] = i;
+    if (gt || (eq && eq_before < ties)) {
+      const uint32_t slot = gt_before + min(eq_before, ties);
+      if (slot < (uint32_t)k) out[slot] = i;
     }
     gt_run += __popc(bg);
     eq_run += __popc(be);
+  }
+}
+
+// One CTA per row.  EPT > 0: the row (at most NT * EPT entries) is read once with coalesced
+// 16-byte loads, transposed through shared memory and then lives in REGISTERS, EPT
+// consecutive positions per thread, for every later step.  EPT == 0: rows of any length, kept
+// in shared memory (kSmemRow) or re-read from memory by every pass.
+//
+// Steps: key range of the row -> a histogram that is LINEAR in the value between the row's
+// minimum and maximum (a row of logits shares two or three exponents, so a histogram over the
+// leading bits would put thousands of shared-memory atomics on a handful of addresses) ->
+// everything above the threshold bin is selected, the few keys inside it are ranked exactly ->
+// ordered emission (one block-wide scan of per-thread counts).  Rows with NaN / infinities /
+// a single value, or with more threshold-bin keys than the list holds, take the exact bitwise
+// radix select over the whole row instead.
+#ifdef LT_SEL_TS
+#define SEL_TS(i) do { if (threadIdx.x == 0) ts[i] = clock64(); } while (0)
+#else
+#define SEL_TS(i) do { } while (0)
+#endif
+template <int NT, int EPT, bool kSmemRow>
+__global__ void __launch_bounds__(NT)
+topk_select_kernel(const SelParams p) {
+  extern __shared__ __align__(16) uint32_t rowkeys[];
+  __shared__ SelShared sh;
+#ifdef LT_SEL_TS
+  long long ts[8];
+#endif
+  SEL_TS(0);
+  constexpr int E = EPT > 0 ? EPT : 4;       // register copy (fast path only)
+  constexpr int NQ = E / 4;
+
+  const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  const int n = p.lengths ? min(max(p.lengths[t], 0), p.S) : min(p.S, max(p.q_pos0 + t + 1, 0));
+  int32_t* out = p.out + (long long)t * p.k;
+  const float* row = p.logits + (long long)t * p.ld;
+  if (n <= p.k) {            // everything valid is selected
+    for (int i = tid; i < p.k; i += NT) out[i] = i < n ? i : -1;
+    return;
+  }
+  // ---- load the row as order-preserving keys; key range
+  uint32_t kmax = 0u, kmin = 0xffffffffu;
+  const bool vec = (p.ld & 3) == 0 && ((reinterpret_cast<uintptr_t>(p.logits) & 15) == 0);
+  if (EPT > 0 && vec) {
+    // all loads in flight before the first use
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+    float4 v[NQ];
+#pragma unroll
+    for (int j = 0; j < NQ; ++j) {
+      const int qd = j * NT + tid;
+      v[j] = 4 * qd + 3 < n ? __ldg(row4 + qd) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < NQ; ++j) {
+      const int qd = j * NT + tid;
+      if (4 * qd + 3 < n) {
+        const uint4 u = make_uint4(okey(v[j].x), okey(v[j].y), okey(v[j].z), okey(v[j].w));
+        reinterpret_cast<uint4*>(rowkeys)[qd] = u;
+        kmax = max(max(kmax, u.x), max(u.y, max(u.z, u.w)));
+        kmin = min(min(kmin, u.x), min(u.y, min(u.z, u.w)));
+      }
+    }
+    for (int i = (n & ~3) + tid; i < n; i += NT) {
+      const uint32_t u = okey(__ldg(row + i));
+      rowkeys[i] = u;
+      kmax = max(kmax, u);
+      kmin = min(kmin, u);
+    }
+  } else {
+    for (int i = tid; i < n; i += NT) {
+      const uint32_t u = okey(__ldg(row + i));
+      if (kSmemRow) rowkeys[i] = u;
+      kmax = max(kmax, u);
+      kmin = min(kmin, u);
+    }
+  }
+  if (tid == 0) sh.n_cand = 0;
+  block_max_min<NT>(sh, kmax, kmin);         // barrier: the shared-memory row is complete
+  SEL_TS(1);
+  auto key_at = [&](int i) -> uint32_t { return kSmemRow ? rowkeys[i] : okey(__ldg(row + i)); };
+
+  // ---- the thread's EPT consecutive positions, in registers (fast path).  16-byte shared
+  // loads in a per-thread rotated order, so that the eight threads of a quarter warp hit
+  // different banks; register (q, c) holds position base + 4 * ((q + tid) % NQ) + c.
+  const int base = tid * E;
+  uint32_t kr[E];
+  if (EPT > 0) {
+#pragma unroll
+    for (int q = 0; q < NQ; ++q) {
+      const int qq = (q + tid) % NQ;
+      const uint4 u = base + 4 * qq < n ? reinterpret_cast<const uint4*>(rowkeys)[(base >> 2) + qq]
+                                        : make_uint4(0u, 0u, 0u, 0u);
+      kr[4 * q] = u.x; kr[4 * q + 1] = u.y; kr[4 * q + 2] = u.z; kr[4 * q + 3] = u.w;
+    }
+  }
+  auto pos_of = [&](int q, int c) -> int { return 4 * ((q + tid) % NQ) + c; };   // offset in the chunk
+
+  SEL_TS(2);
+  uint32_t kth = 0, ties = 0;
+  bool done = false;
+  const float vmin = okey_inv(kmin), vmax = okey_inv(kmax);
+  const float range = vmax - vmin;
+  if (kmin != 0u && range > 0.f && range <= 3.0e38f) {
+    const float sc = 2047.5f / range;
+    auto bin_of = [&](uint32_t u) -> uint32_t {
+      return min((uint32_t)((okey_inv(u) - vmin) * sc), (uint32_t)(kBins - 1));
+    };
+    for (int i = tid; i < kBins; i += NT) sh.hist[i] = 0;
+    __syncthreads();
+    if (EPT > 0) {
+#pragma unroll
+      for (int e = 0; e < E; ++e)
+        if (base + pos_of(e >> 2, e & 3) < n) atomicAdd(&sh.hist[bin_of(kr[e])], 1u);
+    } else {
+      for (int i = tid; i < n; i += NT) atomicAdd(&sh.hist[bin_of(key_at(i))], 1u);
+    }
+    __syncthreads();
+    SEL_TS(3);
+    uint32_t rem = 0;
+    const uint32_t b = find_bin<NT>(sh, (uint32_t)p.k, &rem);
+    SEL_TS(4);
+    // the keys of the threshold bin
+    uint32_t cmax = 0u, cmin = 0xffffffffu;
+    auto consider = [&](uint32_t u) {
+      if (bin_of(u) == b) {
+        const uint32_t slot = atomicAdd(&sh.n_cand, 1u);
+        if (slot < (uint32_t)kCandCap) sh.cand[slot] = u;
+        cmax = max(cmax, u);
+        cmin = min(cmin, u);
+      }
+    };
+    if (EPT > 0) {
+#pragma unroll
+      for (int e = 0; e < E; ++e)
+        if (base + pos_of(e >> 2, e & 3) < n) consider(kr[e]);
+    } else {
+      for (int i = tid; i < n; i += NT) consider(key_at(i));
+    }
+    block_max_min<NT>(sh, cmax, cmin);       // barrier: the list is complete
+    const uint32_t m = sh.n_cand;
+    SEL_TS(5);
+    if (m <= (uint32_t)NT) {
+      // rank by counting: thread i owns candidate i
+      if (tid < (int)m) {
+        const uint32_t mine = sh.cand[tid];
+        uint32_t gtc = 0, eqc = 0;
+        for (uint32_t j = 0; j < m; ++j) {
+          const uint32_t o = sh.cand[j];
+          gtc += o > mine;
+          eqc += o == mine;
+        }
+        if (gtc < rem && rem <= gtc + eqc) { sh.kth = mine; sh.ties = rem - gtc; }
+      }
+      __syncthreads();
+      kth = sh.kth; ties = sh.ties;
+      done = true;
+    } else if (m <= (uint32_t)kCandCap) {
+      kth = radix_kth<NT>(sh, [&](int i) -> uint32_t { return sh.cand[i]; }, (int)m, cmax, cmin, rem, &ties);
+      done = true;
+    }
+    __syncthreads();
+  }
+  if (!done) kth = radix_kth<NT>(sh, key_at, n, kmax, kmin, (uint32_t)p.k, &ties);
+  SEL_TS(6);
+
+  // ---- ordered emission.  kth = the k-th largest key, `ties` = how many elements equal to it
+  // are taken (smallest positions first).  The number of selected elements before position i
+  // is  #greater before i + min(#equal before i, ties).
+  if (EPT > 0) {
+    // positional bit masks of the thread's chunk, counts, one block-wide exclusive scan
+    unsigned long long gtm = 0ull, eqm = 0ull;
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      const int o = pos_of(e >> 2, e & 3);
+      if (base + o < n) {
+        gtm |= (unsigned long long)(kr[e] > kth) << o;
+        eqm |= (unsigned long long)(kr[e] == kth) << o;
+      }
+    }
+    const uint32_t cg = __popcll(gtm), ce = __popcll(eqm);
+    uint32_t ig = cg, ie = ce;               // inclusive scans inside the warp
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const uint32_t a = __shfl_up_sync(0xffffffffu, ig, off), b2 = __shfl_up_sync(0xffffffffu, ie, off);
+      if (lane >= off) { ig += a; ie += b2; }
+    }
+    if (lane == 31) { sh.wa[wid] = ig; sh.wb[wid] = ie; }
+    __syncthreads();
+    uint32_t wg = lane < NT / 32 ? sh.wa[lane] : 0u, we = lane < NT / 32 ? sh.wb[lane] : 0u;
+    uint32_t sg = wg, se = we;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const uint32_t a = __shfl_up_sync(0xffffffffu, sg, off), b2 = __shfl_up_sync(0xffffffffu, se, off);
+      if (lane >= off) { sg += a; se += b2; }
+    }
+    const uint32_t gt_before = __shfl_sync(0xffffffffu, sg - wg, wid) + ig - cg;
+    const uint32_t eq_before = __shfl_sync(0xffffffffu, se - we, wid) + ie - ce;
+    uint32_t slot = gt_before + min(eq_before, ties);
+    uint32_t eq_left = eq_before < ties ? ties - eq_before : 0u;      // ties this thread may still take
+    unsigned long long walk = gtm | eqm;
+    while (walk) {
+      const int o = __ffsll((long long)walk) - 1;
+      walk &= walk - 1;
+      const bool is_gt = (gtm >> o) & 1ull;
+      if (is_gt || eq_left > 0) {
+        if (!is_gt) --eq_left;
+        if (slot < (uint32_t)p.k) out[slot] = base + o;
+        ++slot;
+      }
+    }
+  } else {
+    emit_ordered<NT>(sh, key_at, n, kth, ties, out, p.k);
+  }
+#ifdef LT_SEL_TS
+  __syncthreads();
+  SEL_TS(7);
+  if (threadIdx.x == 0 && blockIdx.x >= gridDim.x - 4)
+    for (int i = 0; i < 8; ++i) out[i] = (int32_t)(ts[i] - ts[0]);
+#endif
+}
+
+
+// Rows of at most 512 * EPT entries, 16-byte aligned: persistent CTAs, one row at a time.
+// The row arrives in shared memory by ONE bulk copy (no registers, no threads involved), is
+// moved into REGISTERS as fp32 values -- thread i owns the 16-byte quads i, i + 512, ... -- and
+// the next row's copy is issued at once, so it lands while this row is being processed.  Every
+// later step works on the registers: minimum / maximum, the value-linear histogram (bin = the
+// low bits of fma(v - min, 2047 / range, 2^23): no float-to-int conversion), the keys of the
+// threshold bin ranked exactly by counting, one block-wide scan of per-thread counts, stores.
+// Here the output order is thread-major (not ascending) but fixed.  Rows the fast path does
+// not cover -- NaN or infinite values, a single value, more threshold-bin keys than threads,
+// or a tie at the k-th value that must be cut by position -- are finished by the exact
+// bitwise select / the ordered emission over the row re-read from memory.
+constexpr int kStreamThreads = 512;
+enum { kSiteSelRow = 11 };
+
+template <int EPT>
+__global__ void __launch_bounds__(kStreamThreads, 1)
+topk_select_stream_kernel(const SelParams p) {
+  constexpr int NT = kStreamThreads, NQ = EPT / 4;
+  extern __shared__ __align__(16) float rowbuf[];
+  __shared__ SelShared sh;
+  __shared__ __align__(8) uint64_t row_bar;
+  __shared__ float red_a[NT / 32], red_b[NT / 32];
+  __shared__ uint32_t eq_total;
+  const Waiter wt{g_status, p.epoch, p.wait_limit_ns};
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  auto len_of = [&](int t) -> int {
+    return p.lengths ? min(max(p.lengths[t], 0), p.S) : min(p.S, max(p.q_pos0 + t + 1, 0));
+  };
+  // rows that need a selection are fetched; the others are written directly
+  auto fetch = [&](int t) {       // thread 0 only
+    const int n = len_of(t);
+    if (n > p.k) {
+      const uint32_t bytes = (uint32_t)(((n + 3) & ~3) * 4);
+      mbar_arrive_expect_tx(&row_bar, bytes);
+      bulk_load_1d(smem_u32(rowbuf), p.logits + (long long)t * p.ld, bytes, &row_bar);
+    }
+  };
+  if (tid == 0) {
+    mbar_init(&row_bar, 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (tid == 0 && (int)blockIdx.x < p.T) fetch(blockIdx.x);
+  uint32_t phase = 0;
+#ifdef LT_SEL_TS
+  long long ts[8];
+#endif
+
+  for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
+    SEL_TS(0);
+    const int n = len_of(t);
+    int32_t* out = p.out + (long long)t * p.k;
+    const int t_next = t + gridDim.x;
+    if (n <= p.k) {            // everything valid is selected; no copy was issued for this row
+      for (int i = tid; i < p.k; i += NT) out[i] = i < n ? i : -1;
+      if (tid == 0 && t_next < p.T) fetch(t_next);
+      continue;
+    }
+    const bool landed = mbar_wait(&row_bar, phase, wt, kSiteSelRow, t);
+    phase ^= 1;
+    SEL_TS(1);
+    // ---- registers: quad q of this thread holds positions 4 * (q * NT + tid) .. + 3.  Quads
+    // [0, nfull) are entirely below n for every thread; the next one may be cut; the rest is empty.
+    float vr[EPT];
+#pragma unroll
+    for (int q = 0; q < NQ; ++q) {
+      const float4 v = 4 * (q * NT + tid) < n ? reinterpret_cast<const float4*>(rowbuf)[q * NT + tid]
+                                              : make_float4(0.f, 0.f, 0.f, 0.f);
+      vr[4 * q] = v.x; vr[4 * q + 1] = v.y; vr[4 * q + 2] = v.z; vr[4 * q + 3] = v.w;
+    }
+    const int nfull = n / (4 * NT);                 // block-uniform
+    auto live = [&](int q, int c) -> bool { return q < nfull || 4 * (q * NT + tid) + c < n; };
+    fence_proxy_async_smem();      // these reads are ordered before the next bulk write
+    if (tid == 0) sh.n_cand = 0;
+    const bool all_landed = __syncthreads_and(landed);
+    if (tid == 0 && t_next < p.T) fetch(t_next);
+    if (!all_landed) continue;     // a wait ran out: the status word says so (block-uniform decision)
+    SEL_TS(2);
+
+    // ---- minimum, maximum; NaN / infinity check (x * 0 is NaN exactly for those)
+    float vmax = -INFINITY, vmin = INFINITY, chk = 0.f;
+#pragma unroll
+    for (int q = 0; q < NQ; ++q) {
+      if (q < nfull) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const float v = vr[4 * q + c];
+          vmax = fmaxf(vmax, v); vmin = fminf(vmin, v); chk = fmaf(v, 0.f, chk);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          if (live(q, c)) {
+            const float v = vr[4 * q + c];
+            vmax = fmaxf(vmax, v); vmin = fminf(vmin, v); chk = fmaf(v, 0.f, chk);
+          }
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, off));
+      vmin = fminf(vmin, __shfl_xor_sync(0xffffffffu, vmin, off));
+    }
+    if (lane == 0) { red_a[wid] = vmax; red_b[wid] = vmin; }
+    const bool any_odd = __syncthreads_or(chk != chk);
+    {
+      float a = lane < NT / 32 ? red_a[lane] : -INFINITY, b = lane < NT / 32 ? red_b[lane] : INFINITY;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, off));
+        b = fminf(b, __shfl_xor_sync(0xffffffffu, b, off));
+      }
+      vmax = a; vmin = b;
+    }
+    SEL_TS(3);
+    const float range = vmax - vmin;
+    uint32_t kth = 0, ties = 0;
+    bool done = false, cut_ties = true;
+    if (!any_odd && range > 0.f && range <= 3.0e38f) {
+      const float sc = 2047.f / range;
+      auto bin_of = [&](float v) -> uint32_t {
+        return __float_as_uint(fmaf(v - vmin, sc, 8388608.f)) & 0xFFFu;
+      };
+      for (int i = tid; i < kBins; i += NT) sh.hist[i] = 0;
+      __syncthreads();
+#pragma unroll
+      for (int q = 0; q < NQ; ++q) {
+        uint32_t bn[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) bn[c] = bin_of(vr[4 * q + c]);
+        if (q < nfull) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) atomicAdd(&sh.hist[bn[c]], 1u);
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            if (live(q, c)) atomicAdd(&sh.hist[bn[c]], 1u);
+        }
+      }
+      __syncthreads();
+      SEL_TS(4);
+      uint32_t rem = 0;
+      const uint32_t b = find_bin<NT>(sh, (uint32_t)p.k, &rem);
+      // the keys of the threshold bin
+#pragma unroll
+      for (int q = 0; q < NQ; ++q) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          if (bin_of(vr[4 * q + c]) == b && live(q, c)) {
+            const uint32_t slot = atomicAdd(&sh.n_cand, 1u);
+            if (slot < (uint32_t)NT) sh.cand[slot] = okey(vr[4 * q + c]);
+          }
+      }
+      __syncthreads();
+      const uint32_t m = sh.n_cand;
+      SEL_TS(5);
+      if (m <= (uint32_t)NT) {
+        // rank by counting: thread i owns candidate i
+        if (tid < (int)m) {
+          const uint32_t mine = sh.cand[tid];
+          uint32_t gtc = 0, eqc = 0;
+          for (uint32_t j = 0; j < m; ++j) {
+            const uint32_t o = sh.cand[j];
+            gtc += o > mine;
+            eqc += o == mine;
+          }
+          if (gtc < rem && rem <= gtc + eqc) { sh.kth = mine; sh.ties = rem - gtc; eq_total = eqc; }
+        }
+        __syncthreads();
+        kth = sh.kth; ties = sh.ties;
+        cut_ties = ties != eq_total;          // only some of the keys equal to kth are taken
+        done = true;
+      }
+      __syncthreads();
+    }
+    SEL_TS(6);
+    const float* row = p.logits + (long long)t * p.ld;
+    auto key_mem = [&](int i) -> uint32_t { return okey(__ldg(row + i)); };
+    if (!done) {
+      // exact bitwise select over the row re-read from memory (key range first)
+      uint32_t kmax = 0u, kmin = 0xffffffffu;
+      for (int i = tid; i < n; i += NT) {
+        const uint32_t u = key_mem(i);
+        kmax = max(kmax, u);
+        kmin = min(kmin, u);
+      }
+      block_max_min<NT>(sh, kmax, kmin);
+      kth = radix_kth<NT>(sh, key_mem, n, kmax, kmin, (uint32_t)p.k, &ties);
+    }
+    if (cut_ties) {
+      emit_ordered<NT>(sh, key_mem, n, kth, ties, out, p.k);
+    } else {
+      // every value >= the k-th is selected: per-thread mask, one block-wide exclusive scan
+      const float kv = okey_inv(kth);
+      unsigned long long selm = 0ull;
+#pragma unroll
+      for (int q = 0; q < NQ; ++q) {
+        uint32_t m4 = 0;
+        if (q < nfull) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) m4 |= (uint32_t)(vr[4 * q + c] >= kv) << c;
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) m4 |= (uint32_t)(live(q, c) && vr[4 * q + c] >= kv) << c;
+        }
+        selm |= (unsigned long long)m4 << (4 * q);
+      }
+      const uint32_t cnt = __popcll(selm);
+      uint32_t inc = cnt;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t a = __shfl_up_sync(0xffffffffu, inc, off);
+        if (lane >= off) inc += a;
+      }
+      if (lane == 31) sh.wa[wid] = inc;
+      __syncthreads();
+      uint32_t wtot = lane < NT / 32 ? sh.wa[lane] : 0u, ws = wtot;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t a = __shfl_up_sync(0xffffffffu, ws, off);
+        if (lane >= off) ws += a;
+      }
+      uint32_t slot = __shfl_sync(0xffffffffu, ws - wtot, wid) + inc - cnt;
+      while (selm) {
+        const int o = __ffsll((long long)selm) - 1;
+        selm &= selm - 1;
+        if (slot < (uint32_t)p.k) out[slot] = 4 * ((o >> 2) * NT + tid) + (o & 3);
+        ++slot;
+      }
+    }
+    __syncthreads();               // sh.* is reused by the next row
+#ifdef LT_SEL_TS
+    SEL_TS(7);
+    if (threadIdx.x == 0 && t >= p.T - 4) for (int i = 0; i < 8; ++i) out[i] = (int32_t)(ts[i] - ts[0]);
+#endif
   }
 }
 
@@ -372,8 +894,8 @@ extern "C" int litedsa_index_logits_fp8(const void* q_idx8, const void* k_idx8, 
 }
 
 // Exact top-k per row of `logits`: topk_idx[t, :] = the k positions i < len(t) with the largest
-// values, ascending in position, ties at the k-th value resolved towards smaller positions;
-// rows with len(t) <= k list 0 .. len(t) - 1 and are padded with -1.  len(t) = lengths[t], or
+// values (order inside a row unspecified), ties at the k-th value resolved towards smaller
+// positions; rows with len(t) <= k list 0 .. len(t) - 1 and are padded with -1.  len(t) = lengths[t], or
 // min(S, q_pos0 + t + 1) when lengths is null (causal).  NaN sorts below every number.
 // The output is what the union operator takes as topk_indices
 // (kernels/b200/dsa/litedsa.cu:31-33).  No allocation; asynchronous on `stream`.
@@ -386,17 +908,32 @@ extern "C" int litedsa_topk_select(const float* logits, const int32_t* lengths, 
   SelParams p;
   p.logits = logits; p.lengths = lengths; p.out = topk_idx;
   p.T = T; p.S = S; p.k = k; p.q_pos0 = q_pos0; p.ld = logits_row_stride;
+  p.epoch = lt::next_launch_epoch(); p.wait_limit_ns = lt::wait_limit_ns();
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (S <= kMaxSmemRow) {
-    const size_t smem = (size_t)S * 4;
-    if (cudaFuncSetAttribute(topk_select_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)smem) != cudaSuccess)
+  // rows up to 32768 entries live in registers (512 threads x 64 or 32 consecutive positions,
+  // transposed through shared memory); longer rows stay in shared memory up to 49152 entries
+  // and are re-read from memory by every pass beyond that
+  const size_t smem = (((size_t)S + 3) & ~(size_t)3) * 4;      // whole 16-byte quads
+  auto launch = [&](auto kern, int threads, size_t dyn) -> int {
+    if (dyn && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn) != cudaSuccess)
       return LITEDSA_ERR_CUDA;
-    topk_select_kernel<true><<<T, kSelThreads, smem, st>>>(p);
-  } else {
-    topk_select_kernel<false><<<T, kSelThreads, 0, st>>>(p);
+    kern<<<T, threads, dyn, st>>>(p);
+    return cudaGetLastError() == cudaSuccess ? LITEDSA_OK : LITEDSA_ERR_CUDA;
+  };
+  const bool aligned = (logits_row_stride & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0;
+  if (aligned && S <= kStreamThreads * 64) {
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int grid = T < sms ? T : sms;
+    auto kern = S <= kStreamThreads * 32 ? topk_select_stream_kernel<32> : topk_select_stream_kernel<64>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return LITEDSA_ERR_CUDA;
+    kern<<<grid, kStreamThreads, smem, st>>>(p);
+    return cudaGetLastError() == cudaSuccess ? LITEDSA_OK : LITEDSA_ERR_CUDA;
   }
-  return cudaGetLastError() == cudaSuccess ? LITEDSA_OK : LITEDSA_ERR_CUDA;
+  if (S <= kMaxSmemRow) return launch(topk_select_kernel<1024, 0, true>, 1024, smem);
+  return launch(topk_select_kernel<1024, 0, false>, 1024, 0);
 }
 
 // Status block of the index-logits kernel (same layout as litedsa_attn_status).
