@@ -615,17 +615,46 @@ topk_select_kernel(const SelParams p) {
 }
 
 
+constexpr int kSurvCap = 8192;           // survivors of the sampled filter kept in shared memory
+
+// block-wide float max / min (NaN operands are ignored); all threads get the result
+template <int NT>
+__device__ __forceinline__ void block_fmax_fmin(float* red_a, float* red_b, float& vmax, float& vmin) {
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, off));
+    vmin = fminf(vmin, __shfl_xor_sync(0xffffffffu, vmin, off));
+  }
+  if (lane == 0) { red_a[wid] = vmax; red_b[wid] = vmin; }
+  __syncthreads();
+  float a = lane < NT / 32 ? red_a[lane] : -INFINITY, b = lane < NT / 32 ? red_b[lane] : INFINITY;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, off));
+    b = fminf(b, __shfl_xor_sync(0xffffffffu, b, off));
+  }
+  vmax = a; vmin = b;
+  __syncthreads();
+}
+
 // Rows of at most 512 * EPT entries, 16-byte aligned: persistent CTAs, one row at a time.
 // The row arrives in shared memory by ONE bulk copy (no registers, no threads involved), is
 // moved into REGISTERS as fp32 values -- thread i owns the 16-byte quads i, i + 512, ... -- and
-// the next row's copy is issued at once, so it lands while this row is being processed.  Every
-// later step works on the registers: minimum / maximum, the value-linear histogram (bin = the
-// low bits of fma(v - min, 2047 / range, 2^23): no float-to-int conversion), the keys of the
-// threshold bin ranked exactly by counting, one block-wide scan of per-thread counts, stores.
-// Here the output order is thread-major (not ascending) but fixed.  Rows the fast path does
-// not cover -- NaN or infinite values, a single value, more threshold-bin keys than threads,
-// or a tie at the k-th value that must be cut by position -- are finished by the exact
-// bitwise select / the ordered emission over the row re-read from memory.
+// the next row's copy is issued at once, so it lands while this row is being processed.
+// Selection without sorting and without touching most elements more than once:
+//   1. 2048 evenly spaced samples of the row give a threshold that, with overwhelming
+//      probability, a little more than k elements exceed;
+//   2. one compare per element builds the survivors' positional masks (block-wide scan);
+//   3. the ~1.3 k survivors' positions go to shared memory, their values are re-read;
+//   4. among them: value-linear histogram (bin = the low bits of fma(v - min, 2047 / range,
+//      2^23): no float-to-int conversion), suffix scan, the few keys of the threshold bin ranked
+//      exactly by counting;
+//   5. survivors >= the k-th value are written out (block-wide scan of per-thread counts).
+// The output order is fixed but not ascending.  Whatever the fast path does not cover -- too
+// few or too many survivors, NaN or infinite values, a single value, more threshold-bin keys
+// than threads, a tie at the k-th value that must be cut by position -- is finished by the
+// exact bitwise radix select and the ordered emission over the row re-read from memory.
 constexpr int kStreamThreads = 512;
 enum { kSiteSelRow = 11 };
 
@@ -633,7 +662,9 @@ template <int EPT>
 __global__ void __launch_bounds__(kStreamThreads, 1)
 topk_select_stream_kernel(const SelParams p) {
   constexpr int NT = kStreamThreads, NQ = EPT / 4;
-  extern __shared__ __align__(16) float rowbuf[];
+  extern __shared__ __align__(16) float rowbuf[];      // the row | survivor values | survivor positions
+  float* sval = rowbuf + ((p.S + 3) & ~3);
+  uint16_t* spos = reinterpret_cast<uint16_t*>(sval + kSurvCap);
   __shared__ SelShared sh;
   __shared__ __align__(8) uint64_t row_bar;
   __shared__ float red_a[NT / 32], red_b[NT / 32];
@@ -686,6 +717,11 @@ topk_select_stream_kernel(const SelParams p) {
       vr[4 * q] = v.x; vr[4 * q + 1] = v.y; vr[4 * q + 2] = v.z; vr[4 * q + 3] = v.w;
     }
     const int nfull = n / (4 * NT);                 // block-uniform
+    // 2048 samples of the row, evenly spaced over its positions (read while the row is still
+    // in shared memory): they place the threshold of the filter below
+    float smp[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) smp[i] = rowbuf[(int)(((long long)(4 * tid + i) * n) >> 11)];
     auto live = [&](int q, int c) -> bool { return q < nfull || 4 * (q * NT + tid) + c < n; };
     fence_proxy_async_smem();      // these reads are ordered before the next bulk write
     if (tid == 0) sh.n_cand = 0;
@@ -694,135 +730,56 @@ topk_select_stream_kernel(const SelParams p) {
     if (!all_landed) continue;     // a wait ran out: the status word says so (block-uniform decision)
     SEL_TS(2);
 
-    // ---- minimum, maximum; NaN / infinity check (x * 0 is NaN exactly for those)
-    float vmax = -INFINITY, vmin = INFINITY, chk = 0.f;
+    const float* row = p.logits + (long long)t * p.ld;
+    auto key_mem = [&](int i) -> uint32_t { return okey(__ldg(row + i)); };
+    bool fast = true;                // block-uniform: the fast path still applies
+    uint32_t kth = 0, ties = 0;
+    bool have_kth = false;
+
+    // ---- 1. a threshold from the sample.  With q = k / n the expected number of samples above
+    // the k-th value is 2048 q; four standard deviations and a few bins above that, the sample
+    // rank r gives a value that at least k elements of the row exceed (probability of the
+    // opposite about 3e-5 per row; that case and every other surprise take the exact path).
+    // Short rows skip the filter: everything survives.
+    float t_lo = -INFINITY;
+    if (n > kSurvCap / 2) {
+      float smax = fmaxf(fmaxf(smp[0], smp[1]), fmaxf(smp[2], smp[3]));
+      float smin = fminf(fminf(smp[0], smp[1]), fminf(smp[2], smp[3]));
+      block_fmax_fmin<NT>(red_a, red_b, smax, smin);
+      const float srange = smax - smin;
+      const float qf = (float)p.k / (float)n, mean = 2048.f * qf;
+      const uint32_t r = (uint32_t)ceilf(mean + 4.f * sqrtf(mean * (1.f - qf)) + 8.f);
+      if (srange > 0.f && srange <= 3.0e38f && r < 2048u) {
+        const float sc = 2047.f / srange;
+        for (int i = tid; i < kBins; i += NT) sh.hist[i] = 0;
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (smp[i] == smp[i]) atomicAdd(&sh.hist[__float_as_uint(fmaf(smp[i] - smin, sc, 8388608.f)) & 0xFFFu], 1u);
+        __syncthreads();
+        uint32_t rem_s = 0;
+        const uint32_t b = find_bin<NT>(sh, r, &rem_s);
+        t_lo = smin + (float)(b > 1u ? b - 2u : 0u) / sc;     // two bins below: rounding-safe lower edge
+        if (b <= 1u) t_lo = -INFINITY;
+      }
+    }
+    SEL_TS(3);
+
+    // ---- 2. filter: count the thread's survivors, block-wide exclusive scan
+    uint32_t nsel = 0;
 #pragma unroll
     for (int q = 0; q < NQ; ++q) {
       if (q < nfull) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const float v = vr[4 * q + c];
-          vmax = fmaxf(vmax, v); vmin = fminf(vmin, v); chk = fmaf(v, 0.f, chk);
-        }
+        for (int c = 0; c < 4; ++c) nsel += vr[4 * q + c] >= t_lo;
       } else {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
-          if (live(q, c)) {
-            const float v = vr[4 * q + c];
-            vmax = fmaxf(vmax, v); vmin = fminf(vmin, v); chk = fmaf(v, 0.f, chk);
-          }
+        for (int c = 0; c < 4; ++c) nsel += live(q, c) && vr[4 * q + c] >= t_lo;
       }
     }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-      vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, off));
-      vmin = fminf(vmin, __shfl_xor_sync(0xffffffffu, vmin, off));
-    }
-    if (lane == 0) { red_a[wid] = vmax; red_b[wid] = vmin; }
-    const bool any_odd = __syncthreads_or(chk != chk);
+    uint32_t slot = 0, m_s = 0;
     {
-      float a = lane < NT / 32 ? red_a[lane] : -INFINITY, b = lane < NT / 32 ? red_b[lane] : INFINITY;
-#pragma unroll
-      for (int off = 16; off > 0; off >>= 1) {
-        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, off));
-        b = fminf(b, __shfl_xor_sync(0xffffffffu, b, off));
-      }
-      vmax = a; vmin = b;
-    }
-    SEL_TS(3);
-    const float range = vmax - vmin;
-    uint32_t kth = 0, ties = 0;
-    bool done = false, cut_ties = true;
-    if (!any_odd && range > 0.f && range <= 3.0e38f) {
-      const float sc = 2047.f / range;
-      auto bin_of = [&](float v) -> uint32_t {
-        return __float_as_uint(fmaf(v - vmin, sc, 8388608.f)) & 0xFFFu;
-      };
-      for (int i = tid; i < kBins; i += NT) sh.hist[i] = 0;
-      __syncthreads();
-#pragma unroll
-      for (int q = 0; q < NQ; ++q) {
-        uint32_t bn[4];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) bn[c] = bin_of(vr[4 * q + c]);
-        if (q < nfull) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c) atomicAdd(&sh.hist[bn[c]], 1u);
-        } else {
-#pragma unroll
-          for (int c = 0; c < 4; ++c)
-            if (live(q, c)) atomicAdd(&sh.hist[bn[c]], 1u);
-        }
-      }
-      __syncthreads();
-      SEL_TS(4);
-      uint32_t rem = 0;
-      const uint32_t b = find_bin<NT>(sh, (uint32_t)p.k, &rem);
-      // the keys of the threshold bin
-#pragma unroll
-      for (int q = 0; q < NQ; ++q) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-          if (bin_of(vr[4 * q + c]) == b && live(q, c)) {
-            const uint32_t slot = atomicAdd(&sh.n_cand, 1u);
-            if (slot < (uint32_t)NT) sh.cand[slot] = okey(vr[4 * q + c]);
-          }
-      }
-      __syncthreads();
-      const uint32_t m = sh.n_cand;
-      SEL_TS(5);
-      if (m <= (uint32_t)NT) {
-        // rank by counting: thread i owns candidate i
-        if (tid < (int)m) {
-          const uint32_t mine = sh.cand[tid];
-          uint32_t gtc = 0, eqc = 0;
-          for (uint32_t j = 0; j < m; ++j) {
-            const uint32_t o = sh.cand[j];
-            gtc += o > mine;
-            eqc += o == mine;
-          }
-          if (gtc < rem && rem <= gtc + eqc) { sh.kth = mine; sh.ties = rem - gtc; eq_total = eqc; }
-        }
-        __syncthreads();
-        kth = sh.kth; ties = sh.ties;
-        cut_ties = ties != eq_total;          // only some of the keys equal to kth are taken
-        done = true;
-      }
-      __syncthreads();
-    }
-    SEL_TS(6);
-    const float* row = p.logits + (long long)t * p.ld;
-    auto key_mem = [&](int i) -> uint32_t { return okey(__ldg(row + i)); };
-    if (!done) {
-      // exact bitwise select over the row re-read from memory (key range first)
-      uint32_t kmax = 0u, kmin = 0xffffffffu;
-      for (int i = tid; i < n; i += NT) {
-        const uint32_t u = key_mem(i);
-        kmax = max(kmax, u);
-        kmin = min(kmin, u);
-      }
-      block_max_min<NT>(sh, kmax, kmin);
-      kth = radix_kth<NT>(sh, key_mem, n, kmax, kmin, (uint32_t)p.k, &ties);
-    }
-    if (cut_ties) {
-      emit_ordered<NT>(sh, key_mem, n, kth, ties, out, p.k);
-    } else {
-      // every value >= the k-th is selected: per-thread mask, one block-wide exclusive scan
-      const float kv = okey_inv(kth);
-      unsigned long long selm = 0ull;
-#pragma unroll
-      for (int q = 0; q < NQ; ++q) {
-        uint32_t m4 = 0;
-        if (q < nfull) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c) m4 |= (uint32_t)(vr[4 * q + c] >= kv) << c;
-        } else {
-#pragma unroll
-          for (int c = 0; c < 4; ++c) m4 |= (uint32_t)(live(q, c) && vr[4 * q + c] >= kv) << c;
-        }
-        selm |= (unsigned long long)m4 << (4 * q);
-      }
-      const uint32_t cnt = __popcll(selm);
+      const uint32_t cnt = nsel;
       uint32_t inc = cnt;
 #pragma unroll
       for (int off = 1; off < 32; off <<= 1) {
@@ -837,14 +794,127 @@ topk_select_stream_kernel(const SelParams p) {
         const uint32_t a = __shfl_up_sync(0xffffffffu, ws, off);
         if (lane >= off) ws += a;
       }
-      uint32_t slot = __shfl_sync(0xffffffffu, ws - wtot, wid) + inc - cnt;
-      while (selm) {
-        const int o = __ffsll((long long)selm) - 1;
-        selm &= selm - 1;
-        if (slot < (uint32_t)p.k) out[slot] = 4 * ((o >> 2) * NT + tid) + (o & 3);
-        ++slot;
+      slot = __shfl_sync(0xffffffffu, ws - wtot, wid) + inc - cnt;
+      m_s = __shfl_sync(0xffffffffu, ws, NT / 32 - 1);
+      __syncthreads();
+    }
+    if (m_s < (uint32_t)p.k || m_s > (uint32_t)kSurvCap) fast = false;   // too few (threshold too high) / too many
+    SEL_TS(4);
+
+    if (fast) {
+      // ---- 3. survivors: values and positions out of the registers into shared memory
+#pragma unroll
+      for (int q = 0; q < NQ; ++q) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const bool keep = (q < nfull || live(q, c)) && vr[4 * q + c] >= t_lo;
+          if (keep) {
+            sval[slot] = vr[4 * q + c];
+            spos[slot] = (uint16_t)(4 * (q * NT + tid) + c);
+            ++slot;
+          }
+        }
+      }
+      __syncthreads();
+      float vmax = -INFINITY, vmin = INFINITY, chk = 0.f;
+      for (uint32_t i = tid; i < m_s; i += NT) {
+        const float v = sval[i];
+        vmax = fmaxf(vmax, v); vmin = fminf(vmin, v); chk = fmaf(v, 0.f, chk);
+      }
+      const bool any_odd = __syncthreads_or(chk != chk);
+      block_fmax_fmin<NT>(red_a, red_b, vmax, vmin);
+      const float range = vmax - vmin;
+      // ---- 4. exact selection among the survivors: value-linear histogram, threshold bin,
+      // its keys ranked by counting
+      if (!any_odd && range > 0.f && range <= 3.0e38f) {
+        const float sc = 2047.f / range;
+        auto bin_of = [&](float v) -> uint32_t {
+          return __float_as_uint(fmaf(v - vmin, sc, 8388608.f)) & 0xFFFu;
+        };
+        for (int i = tid; i < kBins; i += NT) sh.hist[i] = 0;
+        __syncthreads();
+        for (uint32_t i = tid; i < m_s; i += NT) atomicAdd(&sh.hist[bin_of(sval[i])], 1u);
+        __syncthreads();
+        uint32_t rem = 0;
+        const uint32_t b = find_bin<NT>(sh, (uint32_t)p.k, &rem);
+        for (uint32_t i = tid; i < m_s; i += NT) {
+          const float v = sval[i];
+          if (bin_of(v) == b) {
+            const uint32_t c = atomicAdd(&sh.n_cand, 1u);
+            if (c < (uint32_t)NT) sh.cand[c] = okey(v);
+          }
+        }
+        __syncthreads();
+        const uint32_t m = sh.n_cand;
+        if (m <= (uint32_t)NT) {
+          if (tid < (int)m) {
+            const uint32_t mine = sh.cand[tid];
+            uint32_t gtc = 0, eqc = 0;
+            for (uint32_t j = 0; j < m; ++j) {
+              const uint32_t o = sh.cand[j];
+              gtc += o > mine;
+              eqc += o == mine;
+            }
+            if (gtc < rem && rem <= gtc + eqc) { sh.kth = mine; sh.ties = rem - gtc; eq_total = eqc; }
+          }
+          __syncthreads();
+          kth = sh.kth; ties = sh.ties;
+          have_kth = true;
+          if (ties != eq_total) fast = false;     // the tie at the k-th value must be cut by position
+        } else {
+          fast = false;
+        }
+        __syncthreads();
+      } else {
+        fast = false;
       }
     }
+    SEL_TS(5);
+
+    if (fast) {
+      // ---- 5. emission: every survivor >= the k-th value; thread i owns a contiguous run of
+      // survivor slots; one block-wide exclusive scan of the counts
+      const float kv = okey_inv(kth);
+      const uint32_t per = (m_s + NT - 1) / NT;
+      const uint32_t i0 = min((uint32_t)tid * per, m_s), i1 = min(i0 + per, m_s);
+      uint32_t cnt = 0;
+      for (uint32_t i = i0; i < i1; ++i) cnt += sval[i] >= kv;
+      uint32_t inc = cnt;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t a = __shfl_up_sync(0xffffffffu, inc, off);
+        if (lane >= off) inc += a;
+      }
+      if (lane == 31) sh.wa[wid] = inc;
+      __syncthreads();
+      uint32_t wtot = lane < NT / 32 ? sh.wa[lane] : 0u, ws = wtot;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t a = __shfl_up_sync(0xffffffffu, ws, off);
+        if (lane >= off) ws += a;
+      }
+      uint32_t o = __shfl_sync(0xffffffffu, ws - wtot, wid) + inc - cnt;
+      for (uint32_t i = i0; i < i1; ++i)
+        if (sval[i] >= kv) {
+          if (o < (uint32_t)p.k) out[o] = spos[i];
+          ++o;
+        }
+    } else {
+      // ---- exact path over the row re-read from memory: bitwise radix select (unless the
+      // k-th value is already known) and ordered emission
+      if (!have_kth) {
+        uint32_t kmax = 0u, kmin = 0xffffffffu;
+        for (int i = tid; i < n; i += NT) {
+          const uint32_t u = key_mem(i);
+          kmax = max(kmax, u);
+          kmin = min(kmin, u);
+        }
+        block_max_min<NT>(sh, kmax, kmin);
+        kth = radix_kth<NT>(sh, key_mem, n, kmax, kmin, (uint32_t)p.k, &ties);
+      }
+      emit_ordered<NT>(sh, key_mem, n, kth, ties, out, p.k);
+    }
+    SEL_TS(6);
     __syncthreads();               // sh.* is reused by the next row
 #ifdef LT_SEL_TS
     SEL_TS(7);
@@ -927,9 +997,10 @@ extern "C" int litedsa_topk_select(const float* logits, const int32_t* lengths, 
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int grid = T < sms ? T : sms;
     auto kern = S <= kStreamThreads * 32 ? topk_select_stream_kernel<32> : topk_select_stream_kernel<64>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    const size_t dyn = smem + (size_t)kSurvCap * 6;      // + survivor values (fp32) and positions (u16)
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn) != cudaSuccess)
       return LITEDSA_ERR_CUDA;
-    kern<<<grid, kStreamThreads, smem, st>>>(p);
+    kern<<<grid, kStreamThreads, dyn, st>>>(p);
     return cudaGetLastError() == cudaSuccess ? LITEDSA_OK : LITEDSA_ERR_CUDA;
   }
   if (S <= kMaxSmemRow) return launch(topk_select_kernel<1024, 0, true>, 1024, smem);
