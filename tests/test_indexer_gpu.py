@@ -89,6 +89,35 @@ def test_topk_select_is_exact(T, S, k, pos0, levels):
     assert np.array_equal(_canon(got), ref)
 
 
+@pytest.mark.parametrize("kind", ["sample_high", "sample_flat", "sample_low", "inf", "few_distinct"])
+def test_topk_select_when_the_sampled_threshold_misleads(kind):
+    """Rows built against the fast path of the streaming kernel, whose filter threshold comes
+    from 2048 evenly spaced samples (positions (j * n) >> 11): the samples lie about the row, or
+    the row holds infinities / very few distinct values.  The result must still be exact."""
+    T, S, k = 6, 32768, 2048
+    x = _random_logits(T, S, seed=77)
+    lens = torch.tensor([32768, 30001, 20000, 32768, 9000, 4097], dtype=torch.int32)
+    for t in range(T):
+        n = int(lens[t])
+        pos = (torch.arange(2048, dtype=torch.int64) * n) >> 11
+        if kind == "sample_high":            # samples far above the rest: threshold too high
+            x[t, pos] += 10.0
+        elif kind == "sample_flat":          # all samples equal
+            x[t, pos] = 100.0
+        elif kind == "sample_low":           # samples far below the rest: far too many survivors
+            x[t, pos] -= 10.0
+        elif kind == "inf":
+            x[t, pos[::7]] = float("inf")
+            x[t, pos[3::11]] = float("-inf")
+        elif kind == "few_distinct":
+            x[t] = torch.round(x[t] * 2) / 2
+    ref = io.topk_exact(x, k, lengths=lens)
+    got = api.topk_select(x.to(DEV), k, lengths=lens.to(DEV))
+    torch.cuda.synchronize()
+    assert api.index_status(reset=True)[0] == 0
+    assert np.array_equal(_canon(got), ref)
+
+
 def test_topk_select_with_lengths_and_row_pitch():
     T, S, k = 12, 2048, 256
     x = _random_logits(T, 2304, seed=4)
