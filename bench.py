@@ -728,7 +728,7 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--gather", choices=("auto", "fused", "ce", "nccl"), default="auto",
                     help="N > 1: how the ranks' outputs are gathered (auto: the fastest measured "
-                         "form for this N: epilogue peer stores up to 4 GPUs, NCCL beyond)")
+                         "form: the attention epilogue's peer stores at every N up to 8)")
     ap.add_argument("--scaling", choices=("weak", "strong"), default="weak",
                     help="N > 1: the configuration per GPU (weak) or split across the GPUs (strong)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -795,7 +795,7 @@ def main():
         return
 
     if args.gather == "auto":
-        args.gather = "fused" if world <= 4 else "nccl"
+        args.gather = "fused" if world <= 8 else "nccl"
     if args.scaling == "strong" and world > 1:
         if w.tokens % (world * w.group):
             raise SystemExit("strong scaling needs tokens divisible by gpus x tokens-per-tile")
