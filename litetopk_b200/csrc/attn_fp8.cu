@@ -450,9 +450,8 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
       const int v = __ldg(p.indices + (size_t)c.tile * p.idx_stride + (size_t)c.k * kBlockKeys + my_key);
       return ((unsigned)v < (unsigned)p.s_kv) ? v : 0;     // out-of-range rows are masked later
     };
-    // The indices of a block are loaded three blocks before its gather is issued (a cold index
-    // line comes from HBM): look-ahead cursors run ahead of the issue cursors and feed two
-    // three-deep register pipelines.
+    // The indices of a block are loaded right after the previous block's gather has been issued
+    // (one block ahead), so a cold index line from HBM is in flight while that gather lands.
     int kidx = 0, vidx = 0;
     if (ck.tile < p.ng) { kidx = load_idx(ck); vidx = load_idx(cv); }
     const uint8_t* kvb = p.kv;
@@ -784,7 +783,8 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
       }
     }
   } else {
-    // ------------------------------------------------------------ index-validity bits
+    // ------------------------------------------------------------ index-validity bits (warp kWarpValid)
+    static_assert(kWarpValid == kWarpRelay + 1 && kWarpValid + 1 == kWarpEpi0, "role layout");
     int kb0 = 0;
     for (int tile = cid; tile < p.ng; tile += ncl) {
       const int count = tile_count(tile);

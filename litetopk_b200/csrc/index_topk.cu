@@ -396,36 +396,19 @@ __device__ __forceinline__ void emit_ordered(SelShared& sh, Get key_at, int n, u
   }
 }
 
-// One CTA per row.  EPT > 0: the row (at most NT * EPT entries) is read once with coalesced
-// 16-byte loads, transposed through shared memory and then lives in REGISTERS, EPT
-// consecutive positions per thread, for every later step.  EPT == 0: rows of any length, kept
-// in shared memory (kSmemRow) or re-read from memory by every pass.
-//
-// Steps: key range of the row -> a histogram that is LINEAR in the value between the row's
-// minimum and maximum (a row of logits shares two or three exponents, so a histogram over the
-// leading bits would put thousands of shared-memory atomics on a handful of addresses) ->
-// everything above the threshold bin is selected, the few keys inside it are ranked exactly ->
-// ordered emission (one block-wide scan of per-thread counts).  Rows with NaN / infinities /
-// a single value, or with more threshold-bin keys than the list holds, take the exact bitwise
-// radix select over the whole row instead.
-#ifdef LT_SEL_TS
-#define SEL_TS(i) do { if (threadIdx.x == 0) ts[i] = clock64(); } while (0)
-#else
-#define SEL_TS(i) do { } while (0)
-#endif
-template <int NT, int EPT, bool kSmemRow>
-__global__ void __launch_bounds__(NT)
+// One CTA per row, rows of any length and alignment: the exact bitwise radix select over the
+// row's order-preserving keys (kept in shared memory when they fit, re-read from memory by
+// every pass otherwise) and the ordered emission.  This is the path for logits tensors whose
+// rows are not 16-byte aligned; aligned rows go through the streaming kernels below, which fall
+// back to the same two steps whenever their fast path does not apply.
+constexpr int kGenericThreads = 1024;
+template <bool kSmemRow>
+__global__ void __launch_bounds__(kGenericThreads)
 topk_select_kernel(const SelParams p) {
+  constexpr int NT = kGenericThreads;
   extern __shared__ __align__(16) uint32_t rowkeys[];
   __shared__ SelShared sh;
-#ifdef LT_SEL_TS
-  long long ts[8];
-#endif
-  SEL_TS(0);
-  constexpr int E = EPT > 0 ? EPT : 4;       // register copy (fast path only)
-  constexpr int NQ = E / 4;
-
-  const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  const int t = blockIdx.x, tid = threadIdx.x;
   const int n = p.lengths ? min(max(p.lengths[t], 0), p.S) : min(p.S, max(p.q_pos0 + t + 1, 0));
   int32_t* out = p.out + (long long)t * p.k;
   const float* row = p.logits + (long long)t * p.ld;
@@ -433,187 +416,19 @@ topk_select_kernel(const SelParams p) {
     for (int i = tid; i < p.k; i += NT) out[i] = i < n ? i : -1;
     return;
   }
-  // ---- load the row as order-preserving keys; key range
   uint32_t kmax = 0u, kmin = 0xffffffffu;
-  const bool vec = (p.ld & 3) == 0 && ((reinterpret_cast<uintptr_t>(p.logits) & 15) == 0);
-  if (EPT > 0 && vec) {
-    // all loads in flight before the first use
-    const float4* row4 = reinterpret_cast<const float4*>(row);
-    float4 v[NQ];
-#pragma unroll
-    for (int j = 0; j < NQ; ++j) {
-      const int qd = j * NT + tid;
-      v[j] = 4 * qd + 3 < n ? __ldg(row4 + qd) : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-#pragma unroll
-    for (int j = 0; j < NQ; ++j) {
-      const int qd = j * NT + tid;
-      if (4 * qd + 3 < n) {
-        const uint4 u = make_uint4(okey(v[j].x), okey(v[j].y), okey(v[j].z), okey(v[j].w));
-        reinterpret_cast<uint4*>(rowkeys)[qd] = u;
-        kmax = max(max(kmax, u.x), max(u.y, max(u.z, u.w)));
-        kmin = min(min(kmin, u.x), min(u.y, min(u.z, u.w)));
-      }
-    }
-    for (int i = (n & ~3) + tid; i < n; i += NT) {
-      const uint32_t u = okey(__ldg(row + i));
-      rowkeys[i] = u;
-      kmax = max(kmax, u);
-      kmin = min(kmin, u);
-    }
-  } else {
-    for (int i = tid; i < n; i += NT) {
-      const uint32_t u = okey(__ldg(row + i));
-      if (kSmemRow) rowkeys[i] = u;
-      kmax = max(kmax, u);
-      kmin = min(kmin, u);
-    }
+  for (int i = tid; i < n; i += NT) {
+    const uint32_t u = okey(__ldg(row + i));
+    if (kSmemRow) rowkeys[i] = u;
+    kmax = max(kmax, u);
+    kmin = min(kmin, u);
   }
-  if (tid == 0) sh.n_cand = 0;
   block_max_min<NT>(sh, kmax, kmin);         // barrier: the shared-memory row is complete
-  SEL_TS(1);
   auto key_at = [&](int i) -> uint32_t { return kSmemRow ? rowkeys[i] : okey(__ldg(row + i)); };
-
-  // ---- the thread's EPT consecutive positions, in registers (fast path).  16-byte shared
-  // loads in a per-thread rotated order, so that the eight threads of a quarter warp hit
-  // different banks; register (q, c) holds position base + 4 * ((q + tid) % NQ) + c.
-  const int base = tid * E;
-  uint32_t kr[E];
-  if (EPT > 0) {
-#pragma unroll
-    for (int q = 0; q < NQ; ++q) {
-      const int qq = (q + tid) % NQ;
-      const uint4 u = base + 4 * qq < n ? reinterpret_cast<const uint4*>(rowkeys)[(base >> 2) + qq]
-                                        : make_uint4(0u, 0u, 0u, 0u);
-      kr[4 * q] = u.x; kr[4 * q + 1] = u.y; kr[4 * q + 2] = u.z; kr[4 * q + 3] = u.w;
-    }
-  }
-  auto pos_of = [&](int q, int c) -> int { return 4 * ((q + tid) % NQ) + c; };   // offset in the chunk
-
-  SEL_TS(2);
-  uint32_t kth = 0, ties = 0;
-  bool done = false;
-  const float vmin = okey_inv(kmin), vmax = okey_inv(kmax);
-  const float range = vmax - vmin;
-  if (kmin != 0u && range > 0.f && range <= 3.0e38f) {
-    const float sc = 2047.5f / range;
-    auto bin_of = [&](uint32_t u) -> uint32_t {
-      return min((uint32_t)((okey_inv(u) - vmin) * sc), (uint32_t)(kBins - 1));
-    };
-    for (int i = tid; i < kBins; i += NT) sh.hist[i] = 0;
-    __syncthreads();
-    if (EPT > 0) {
-#pragma unroll
-      for (int e = 0; e < E; ++e)
-        if (base + pos_of(e >> 2, e & 3) < n) atomicAdd(&sh.hist[bin_of(kr[e])], 1u);
-    } else {
-      for (int i = tid; i < n; i += NT) atomicAdd(&sh.hist[bin_of(key_at(i))], 1u);
-    }
-    __syncthreads();
-    SEL_TS(3);
-    uint32_t rem = 0;
-    const uint32_t b = find_bin<NT>(sh, (uint32_t)p.k, &rem);
-    SEL_TS(4);
-    // the keys of the threshold bin
-    uint32_t cmax = 0u, cmin = 0xffffffffu;
-    auto consider = [&](uint32_t u) {
-      if (bin_of(u) == b) {
-        const uint32_t slot = atomicAdd(&sh.n_cand, 1u);
-        if (slot < (uint32_t)kCandCap) sh.cand[slot] = u;
-        cmax = max(cmax, u);
-        cmin = min(cmin, u);
-      }
-    };
-    if (EPT > 0) {
-#pragma unroll
-      for (int e = 0; e < E; ++e)
-        if (base + pos_of(e >> 2, e & 3) < n) consider(kr[e]);
-    } else {
-      for (int i = tid; i < n; i += NT) consider(key_at(i));
-    }
-    block_max_min<NT>(sh, cmax, cmin);       // barrier: the list is complete
-    const uint32_t m = sh.n_cand;
-    SEL_TS(5);
-    if (m <= (uint32_t)NT) {
-      // rank by counting: thread i owns candidate i
-      if (tid < (int)m) {
-        const uint32_t mine = sh.cand[tid];
-        uint32_t gtc = 0, eqc = 0;
-        for (uint32_t j = 0; j < m; ++j) {
-          const uint32_t o = sh.cand[j];
-          gtc += o > mine;
-          eqc += o == mine;
-        }
-        if (gtc < rem && rem <= gtc + eqc) { sh.kth = mine; sh.ties = rem - gtc; }
-      }
-      __syncthreads();
-      kth = sh.kth; ties = sh.ties;
-      done = true;
-    } else if (m <= (uint32_t)kCandCap) {
-      kth = radix_kth<NT>(sh, [&](int i) -> uint32_t { return sh.cand[i]; }, (int)m, cmax, cmin, rem, &ties);
-      done = true;
-    }
-    __syncthreads();
-  }
-  if (!done) kth = radix_kth<NT>(sh, key_at, n, kmax, kmin, (uint32_t)p.k, &ties);
-  SEL_TS(6);
-
-  // ---- ordered emission.  kth = the k-th largest key, `ties` = how many elements equal to it
-  // are taken (smallest positions first).  The number of selected elements before position i
-  // is  #greater before i + min(#equal before i, ties).
-  if (EPT > 0) {
-    // positional bit masks of the thread's chunk, counts, one block-wide exclusive scan
-    unsigned long long gtm = 0ull, eqm = 0ull;
-#pragma unroll
-    for (int e = 0; e < E; ++e) {
-      const int o = pos_of(e >> 2, e & 3);
-      if (base + o < n) {
-        gtm |= (unsigned long long)(kr[e] > kth) << o;
-        eqm |= (unsigned long long)(kr[e] == kth) << o;
-      }
-    }
-    const uint32_t cg = __popcll(gtm), ce = __popcll(eqm);
-    uint32_t ig = cg, ie = ce;               // inclusive scans inside the warp
-#pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-      const uint32_t a = __shfl_up_sync(0xffffffffu, ig, off), b2 = __shfl_up_sync(0xffffffffu, ie, off);
-      if (lane >= off) { ig += a; ie += b2; }
-    }
-    if (lane == 31) { sh.wa[wid] = ig; sh.wb[wid] = ie; }
-    __syncthreads();
-    uint32_t wg = lane < NT / 32 ? sh.wa[lane] : 0u, we = lane < NT / 32 ? sh.wb[lane] : 0u;
-    uint32_t sg = wg, se = we;
-#pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-      const uint32_t a = __shfl_up_sync(0xffffffffu, sg, off), b2 = __shfl_up_sync(0xffffffffu, se, off);
-      if (lane >= off) { sg += a; se += b2; }
-    }
-    const uint32_t gt_before = __shfl_sync(0xffffffffu, sg - wg, wid) + ig - cg;
-    const uint32_t eq_before = __shfl_sync(0xffffffffu, se - we, wid) + ie - ce;
-    uint32_t slot = gt_before + min(eq_before, ties);
-    uint32_t eq_left = eq_before < ties ? ties - eq_before : 0u;      // ties this thread may still take
-    unsigned long long walk = gtm | eqm;
-    while (walk) {
-      const int o = __ffsll((long long)walk) - 1;
-      walk &= walk - 1;
-      const bool is_gt = (gtm >> o) & 1ull;
-      if (is_gt || eq_left > 0) {
-        if (!is_gt) --eq_left;
-        if (slot < (uint32_t)p.k) out[slot] = base + o;
-        ++slot;
-      }
-    }
-  } else {
-    emit_ordered<NT>(sh, key_at, n, kth, ties, out, p.k);
-  }
-#ifdef LT_SEL_TS
-  __syncthreads();
-  SEL_TS(7);
-  if (threadIdx.x == 0 && blockIdx.x >= gridDim.x - 4)
-    for (int i = 0; i < 8; ++i) out[i] = (int32_t)(ts[i] - ts[0]);
-#endif
+  uint32_t ties = 0;
+  const uint32_t kth = radix_kth<NT>(sh, key_at, n, kmax, kmin, (uint32_t)p.k, &ties);
+  emit_ordered<NT>(sh, key_at, n, kth, ties, out, p.k);
 }
-
 
 constexpr int kSurvCap = 8192;           // survivors of the sampled filter kept in shared memory
 
@@ -636,6 +451,146 @@ __device__ __forceinline__ void block_fmax_fmin(float* red_a, float* red_b, floa
   }
   vmax = a; vmin = b;
   __syncthreads();
+}
+
+// Block-wide, second half of a row for the streaming kernels.  The m_s survivors of the filter
+// sit in shared memory (values sval, positions spos).  fast: the filter kept at least k and at
+// most kSurvCap entries.  Steps: exact selection among the survivors (value-linear histogram,
+// threshold bin, its keys ranked by counting), then every survivor >= the k-th value is written
+// out (thread i owns a contiguous run of survivor slots; one block-wide exclusive scan).  When
+// the fast path does not apply -- or stops applying: NaN / infinite values, a single value,
+// more threshold-bin keys than threads, a tie at the k-th value that must be cut by position --
+// the row is finished exactly from memory: bitwise radix select (unless the k-th value is
+// already known) and ordered emission.
+template <int NT, class PosT>
+__device__ __forceinline__ void finish_row(SelShared& sh, float* red_a, float* red_b, uint32_t* eq_total,
+                                           const float* sval, const PosT* spos, uint32_t m_s, bool fast,
+                                           const float* row, int n, int k, int32_t* out) {
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  uint32_t kth = 0, ties = 0;
+  bool have_kth = false;
+  if (fast) {
+    float vmax = -INFINITY, vmin = INFINITY, chk = 0.f;
+    for (uint32_t i = tid; i < m_s; i += NT) {
+      const float v = sval[i];
+      vmax = fmaxf(vmax, v); vmin = fminf(vmin, v); chk = fmaf(v, 0.f, chk);
+    }
+    const bool any_odd = __syncthreads_or(chk != chk);
+    block_fmax_fmin<NT>(red_a, red_b, vmax, vmin);
+    const float range = vmax - vmin;
+    if (!any_odd && range > 0.f && range <= 3.0e38f) {
+      const float sc = 2047.f / range;
+      auto bin_of = [&](float v) -> uint32_t {
+        return __float_as_uint(fmaf(v - vmin, sc, 8388608.f)) & 0xFFFu;
+      };
+      for (int i = tid; i < kBins; i += NT) sh.hist[i] = 0;
+      __syncthreads();
+      for (uint32_t i = tid; i < m_s; i += NT) atomicAdd(&sh.hist[bin_of(sval[i])], 1u);
+      __syncthreads();
+      uint32_t rem = 0;
+      const uint32_t b = find_bin<NT>(sh, (uint32_t)k, &rem);
+      for (uint32_t i = tid; i < m_s; i += NT) {
+        const float v = sval[i];
+        if (bin_of(v) == b) {
+          const uint32_t c = atomicAdd(&sh.n_cand, 1u);
+          if (c < (uint32_t)NT) sh.cand[c] = okey(v);
+        }
+      }
+      __syncthreads();
+      const uint32_t m = sh.n_cand;
+      if (m <= (uint32_t)NT) {
+        if (tid < (int)m) {
+          const uint32_t mine = sh.cand[tid];
+          uint32_t gtc = 0, eqc = 0;
+          for (uint32_t j = 0; j < m; ++j) {
+            const uint32_t o = sh.cand[j];
+            gtc += o > mine;
+            eqc += o == mine;
+          }
+          if (gtc < rem && rem <= gtc + eqc) { sh.kth = mine; sh.ties = rem - gtc; *eq_total = eqc; }
+        }
+        __syncthreads();
+        kth = sh.kth; ties = sh.ties;
+        have_kth = true;
+        if (ties != *eq_total) fast = false;      // the tie at the k-th value must be cut by position
+      } else {
+        fast = false;
+      }
+      __syncthreads();
+    } else {
+      fast = false;
+    }
+  }
+  if (fast) {
+    const float kv = okey_inv(kth);
+    const uint32_t per = (m_s + NT - 1) / NT;
+    const uint32_t i0 = min((uint32_t)tid * per, m_s), i1 = min(i0 + per, m_s);
+    uint32_t cnt = 0;
+    for (uint32_t i = i0; i < i1; ++i) cnt += sval[i] >= kv;
+    uint32_t inc = cnt;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const uint32_t a = __shfl_up_sync(0xffffffffu, inc, off);
+      if (lane >= off) inc += a;
+    }
+    if (lane == 31) sh.wa[wid] = inc;
+    __syncthreads();
+    uint32_t wtot = lane < NT / 32 ? sh.wa[lane] : 0u, ws = wtot;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const uint32_t a = __shfl_up_sync(0xffffffffu, ws, off);
+      if (lane >= off) ws += a;
+    }
+    uint32_t o = __shfl_sync(0xffffffffu, ws - wtot, wid) + inc - cnt;
+    for (uint32_t i = i0; i < i1; ++i)
+      if (sval[i] >= kv) {
+        if (o < (uint32_t)k) out[o] = (int32_t)spos[i];
+        ++o;
+      }
+  } else {
+    auto key_mem = [&](int i) -> uint32_t { return okey(__ldg(row + i)); };
+    if (!have_kth) {
+      uint32_t kmax = 0u, kmin = 0xffffffffu;
+      for (int i = tid; i < n; i += NT) {
+        const uint32_t u = key_mem(i);
+        kmax = max(kmax, u);
+        kmin = min(kmin, u);
+      }
+      block_max_min<NT>(sh, kmax, kmin);
+      kth = radix_kth<NT>(sh, key_mem, n, kmax, kmin, (uint32_t)k, &ties);
+    }
+    emit_ordered<NT>(sh, key_mem, n, kth, ties, out, k);
+  }
+}
+
+// Block-wide: a filter threshold from 2048 samples smp[4] per thread of a row of n entries.
+// With q = k / n the expected number of samples above the k-th value is 2048 q; four standard
+// deviations and a few bins above that, the sample rank r gives a value that at least k
+// elements of the row exceed (probability of the opposite about 3e-5 per row; that case and
+// every other surprise take the exact path).  -inf when no useful threshold exists.
+template <int NT>
+__device__ __forceinline__ float sampled_threshold(SelShared& sh, float* red_a, float* red_b,
+                                                   const float (&smp)[4], int n, int k) {
+  float smax = fmaxf(fmaxf(smp[0], smp[1]), fmaxf(smp[2], smp[3]));
+  float smin = fminf(fminf(smp[0], smp[1]), fminf(smp[2], smp[3]));
+  block_fmax_fmin<NT>(red_a, red_b, smax, smin);
+  const float srange = smax - smin;
+  const float qf = (float)k / (float)n, mean = 2048.f * qf;
+  const uint32_t r = (uint32_t)ceilf(mean + 4.f * sqrtf(mean * (1.f - qf)) + 8.f);
+  float t_lo = -INFINITY;
+  if (srange > 0.f && srange <= 3.0e38f && r < 2048u) {
+    const float sc = 2047.f / srange;
+    for (int i = threadIdx.x; i < kBins; i += NT) sh.hist[i] = 0;
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (smp[i] == smp[i]) atomicAdd(&sh.hist[__float_as_uint(fmaf(smp[i] - smin, sc, 8388608.f)) & 0xFFFu], 1u);
+    __syncthreads();
+    uint32_t rem_s = 0;
+    const uint32_t b = find_bin<NT>(sh, r, &rem_s);
+    if (b > 1u) t_lo = smin + (float)(b - 2u) / sc;       // two bins below: rounding-safe lower edge
+  }
+  return t_lo;
 }
 
 // Rows of at most 512 * EPT entries, 16-byte aligned: persistent CTAs, one row at a time.
@@ -690,12 +645,8 @@ topk_select_stream_kernel(const SelParams p) {
   __syncthreads();
   if (tid == 0 && (int)blockIdx.x < p.T) fetch(blockIdx.x);
   uint32_t phase = 0;
-#ifdef LT_SEL_TS
-  long long ts[8];
-#endif
 
   for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
-    SEL_TS(0);
     const int n = len_of(t);
     int32_t* out = p.out + (long long)t * p.k;
     const int t_next = t + gridDim.x;
@@ -706,7 +657,6 @@ topk_select_stream_kernel(const SelParams p) {
     }
     const bool landed = mbar_wait(&row_bar, phase, wt, kSiteSelRow, t);
     phase ^= 1;
-    SEL_TS(1);
     // ---- registers: quad q of this thread holds positions 4 * (q * NT + tid) .. + 3.  Quads
     // [0, nfull) are entirely below n for every thread; the next one may be cut; the rest is empty.
     float vr[EPT];
@@ -728,42 +678,13 @@ topk_select_stream_kernel(const SelParams p) {
     const bool all_landed = __syncthreads_and(landed);
     if (tid == 0 && t_next < p.T) fetch(t_next);
     if (!all_landed) continue;     // a wait ran out: the status word says so (block-uniform decision)
-    SEL_TS(2);
 
     const float* row = p.logits + (long long)t * p.ld;
-    auto key_mem = [&](int i) -> uint32_t { return okey(__ldg(row + i)); };
     bool fast = true;                // block-uniform: the fast path still applies
-    uint32_t kth = 0, ties = 0;
-    bool have_kth = false;
 
-    // ---- 1. a threshold from the sample.  With q = k / n the expected number of samples above
-    // the k-th value is 2048 q; four standard deviations and a few bins above that, the sample
-    // rank r gives a value that at least k elements of the row exceed (probability of the
-    // opposite about 3e-5 per row; that case and every other surprise take the exact path).
-    // Short rows skip the filter: everything survives.
+    // ---- 1. a threshold from the sample; short rows skip the filter: everything survives
     float t_lo = -INFINITY;
-    if (n > kSurvCap / 2) {
-      float smax = fmaxf(fmaxf(smp[0], smp[1]), fmaxf(smp[2], smp[3]));
-      float smin = fminf(fminf(smp[0], smp[1]), fminf(smp[2], smp[3]));
-      block_fmax_fmin<NT>(red_a, red_b, smax, smin);
-      const float srange = smax - smin;
-      const float qf = (float)p.k / (float)n, mean = 2048.f * qf;
-      const uint32_t r = (uint32_t)ceilf(mean + 4.f * sqrtf(mean * (1.f - qf)) + 8.f);
-      if (srange > 0.f && srange <= 3.0e38f && r < 2048u) {
-        const float sc = 2047.f / srange;
-        for (int i = tid; i < kBins; i += NT) sh.hist[i] = 0;
-        __syncthreads();
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-          if (smp[i] == smp[i]) atomicAdd(&sh.hist[__float_as_uint(fmaf(smp[i] - smin, sc, 8388608.f)) & 0xFFFu], 1u);
-        __syncthreads();
-        uint32_t rem_s = 0;
-        const uint32_t b = find_bin<NT>(sh, r, &rem_s);
-        t_lo = smin + (float)(b > 1u ? b - 2u : 0u) / sc;     // two bins below: rounding-safe lower edge
-        if (b <= 1u) t_lo = -INFINITY;
-      }
-    }
-    SEL_TS(3);
+    if (n > kSurvCap / 2) t_lo = sampled_threshold<NT>(sh, red_a, red_b, smp, n, p.k);
 
     // ---- 2. filter: count the thread's survivors, block-wide exclusive scan
     uint32_t nsel = 0;
@@ -799,7 +720,6 @@ topk_select_stream_kernel(const SelParams p) {
       __syncthreads();
     }
     if (m_s < (uint32_t)p.k || m_s > (uint32_t)kSurvCap) fast = false;   // too few (threshold too high) / too many
-    SEL_TS(4);
 
     if (fast) {
       // ---- 3. survivors: values and positions out of the registers into shared memory
@@ -816,69 +736,104 @@ topk_select_stream_kernel(const SelParams p) {
         }
       }
       __syncthreads();
-      float vmax = -INFINITY, vmin = INFINITY, chk = 0.f;
-      for (uint32_t i = tid; i < m_s; i += NT) {
-        const float v = sval[i];
-        vmax = fmaxf(vmax, v); vmin = fminf(vmin, v); chk = fmaf(v, 0.f, chk);
-      }
-      const bool any_odd = __syncthreads_or(chk != chk);
-      block_fmax_fmin<NT>(red_a, red_b, vmax, vmin);
-      const float range = vmax - vmin;
-      // ---- 4. exact selection among the survivors: value-linear histogram, threshold bin,
-      // its keys ranked by counting
-      if (!any_odd && range > 0.f && range <= 3.0e38f) {
-        const float sc = 2047.f / range;
-        auto bin_of = [&](float v) -> uint32_t {
-          return __float_as_uint(fmaf(v - vmin, sc, 8388608.f)) & 0xFFFu;
-        };
-        for (int i = tid; i < kBins; i += NT) sh.hist[i] = 0;
-        __syncthreads();
-        for (uint32_t i = tid; i < m_s; i += NT) atomicAdd(&sh.hist[bin_of(sval[i])], 1u);
-        __syncthreads();
-        uint32_t rem = 0;
-        const uint32_t b = find_bin<NT>(sh, (uint32_t)p.k, &rem);
-        for (uint32_t i = tid; i < m_s; i += NT) {
-          const float v = sval[i];
-          if (bin_of(v) == b) {
-            const uint32_t c = atomicAdd(&sh.n_cand, 1u);
-            if (c < (uint32_t)NT) sh.cand[c] = okey(v);
-          }
-        }
-        __syncthreads();
-        const uint32_t m = sh.n_cand;
-        if (m <= (uint32_t)NT) {
-          if (tid < (int)m) {
-            const uint32_t mine = sh.cand[tid];
-            uint32_t gtc = 0, eqc = 0;
-            for (uint32_t j = 0; j < m; ++j) {
-              const uint32_t o = sh.cand[j];
-              gtc += o > mine;
-              eqc += o == mine;
-            }
-            if (gtc < rem && rem <= gtc + eqc) { sh.kth = mine; sh.ties = rem - gtc; eq_total = eqc; }
-          }
-          __syncthreads();
-          kth = sh.kth; ties = sh.ties;
-          have_kth = true;
-          if (ties != eq_total) fast = false;     // the tie at the k-th value must be cut by position
-        } else {
-          fast = false;
-        }
-        __syncthreads();
-      } else {
-        fast = false;
-      }
     }
-    SEL_TS(5);
+    finish_row<NT>(sh, red_a, red_b, &eq_total, sval, spos, m_s, fast, row, n, p.k, out);
+    __syncthreads();               // sh.* is reused by the next row
+  }
+}
 
-    if (fast) {
-      // ---- 5. emission: every survivor >= the k-th value; thread i owns a contiguous run of
-      // survivor slots; one block-wide exclusive scan of the counts
-      const float kv = okey_inv(kth);
-      const uint32_t per = (m_s + NT - 1) / NT;
-      const uint32_t i0 = min((uint32_t)tid * per, m_s), i1 = min(i0 + per, m_s);
+
+// Rows of any length, 16-byte aligned: persistent CTAs; a row streams through two 64 KB
+// shared-memory buffers (bulk copies, two chunks in flight, running across rows), its 2048
+// samples are read from memory first.  Per chunk a thread filters 32 elements straight out of
+// shared memory (count, block-wide scan, survivors appended to the list); after the last chunk
+// the survivors are finished like in the register kernel above.
+constexpr int kChunk = 16384;            // floats per chunk
+enum { kSiteSelChunk = 12 };
+
+__global__ void __launch_bounds__(kStreamThreads, 1)
+topk_select_chunked_kernel(const SelParams p) {
+  constexpr int NT = kStreamThreads, NQ = kChunk / 4 / NT;
+  extern __shared__ __align__(16) float cbuf[];       // 2 chunks | survivor values | survivor positions
+  float* sval = cbuf + 2 * kChunk;
+  uint32_t* spos = reinterpret_cast<uint32_t*>(sval + kSurvCap);
+  __shared__ SelShared sh;
+  __shared__ __align__(8) uint64_t bar[2];
+  __shared__ float red_a[NT / 32], red_b[NT / 32];
+  __shared__ uint32_t eq_total;
+  const Waiter wt{g_status, p.epoch, p.wait_limit_ns};
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  auto len_of = [&](int t) -> int {
+    return p.lengths ? min(max(p.lengths[t], 0), p.S) : min(p.S, max(p.q_pos0 + t + 1, 0));
+  };
+  auto chunks_of = [&](int n) -> int { return (n + kChunk - 1) / kChunk; };
+  // fetch cursor (thread 0): next (row, chunk) to request and its running chunk number
+  int tf = blockIdx.x, cf = 0;
+  uint32_t gf = 0;
+  auto skip_short = [&]() { while (tf < p.T && len_of(tf) <= p.k) tf += gridDim.x; };
+  auto fetch_next = [&]() {       // thread 0 only
+    if (tf >= p.T) return;
+    const int n = len_of(tf);
+    const int start = cf * kChunk;
+    const uint32_t bytes = (uint32_t)(min(kChunk, ((n + 3) & ~3) - start) * 4);
+    uint64_t* b = &bar[gf & 1];
+    mbar_arrive_expect_tx(b, bytes);
+    bulk_load_1d(smem_u32(cbuf + (gf & 1) * kChunk), p.logits + (long long)tf * p.ld + start, bytes, b);
+    ++gf;
+    if (++cf == chunks_of(n)) { cf = 0; tf += gridDim.x; skip_short(); }
+  };
+  if (tid == 0) {
+    mbar_init(&bar[0], 1);
+    mbar_init(&bar[1], 1);
+    fence_mbar_init();
+    skip_short();
+    fetch_next();
+    fetch_next();
+  }
+  __syncthreads();
+  uint32_t gc = 0;                 // running number of the next chunk to consume
+
+  for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
+    const int n = len_of(t);
+    int32_t* out = p.out + (long long)t * p.k;
+    if (n <= p.k) {            // everything valid is selected; nothing was fetched for this row
+      for (int i = tid; i < p.k; i += NT) out[i] = i < n ? i : -1;
+      continue;
+    }
+    const float* row = p.logits + (long long)t * p.ld;
+    // 2048 evenly spaced samples, read from memory while the first chunk lands
+    float smp[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) smp[i] = __ldg(row + (int)(((long long)(4 * tid + i) * n) >> 11));
+    if (tid == 0) sh.n_cand = 0;
+    float t_lo = -INFINITY;
+    if (n > kSurvCap / 2) t_lo = sampled_threshold<NT>(sh, red_a, red_b, smp, n, p.k);
+    else __syncthreads();
+
+    bool fast = true;
+    uint32_t m_run = 0;
+    const int nch = chunks_of(n);
+    for (int c = 0; c < nch; ++c, ++gc) {
+      const bool landed = mbar_wait(&bar[gc & 1], (gc >> 1) & 1, wt, kSiteSelChunk, c);
+      const float4* buf = reinterpret_cast<const float4*>(cbuf + (gc & 1) * kChunk);
+      const int start = c * kChunk;
+      // this thread's 8 quads of the chunk: positions start + 4 * (q * NT + tid) .. + 3
+      float4 v[NQ];
       uint32_t cnt = 0;
-      for (uint32_t i = i0; i < i1; ++i) cnt += sval[i] >= kv;
+#pragma unroll
+      for (int q = 0; q < NQ; ++q) {
+        const int pos = start + 4 * (q * NT + tid);
+        v[q] = pos < n ? buf[q * NT + tid] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+        if (pos + 3 >= n) {      // the row's last quad may be cut: entries beyond n never survive
+          if (pos + 1 >= n) v[q].y = NAN;
+          if (pos + 2 >= n) v[q].z = NAN;
+          if (pos + 3 >= n) v[q].w = NAN;
+          if (pos >= n) v[q].x = NAN;
+        }
+        cnt += (v[q].x >= t_lo) + (v[q].y >= t_lo) + (v[q].z >= t_lo) + (v[q].w >= t_lo);
+      }
+      fence_proxy_async_smem();    // these reads are ordered before the next bulk write of the buffer
+      // block-wide exclusive scan of the counts (its barrier also frees the buffer)
       uint32_t inc = cnt;
 #pragma unroll
       for (int off = 1; off < 32; off <<= 1) {
@@ -886,40 +841,33 @@ topk_select_stream_kernel(const SelParams p) {
         if (lane >= off) inc += a;
       }
       if (lane == 31) sh.wa[wid] = inc;
-      __syncthreads();
+      const bool all_landed = __syncthreads_and(landed);
+      if (tid == 0) fetch_next();
       uint32_t wtot = lane < NT / 32 ? sh.wa[lane] : 0u, ws = wtot;
 #pragma unroll
       for (int off = 1; off < 32; off <<= 1) {
         const uint32_t a = __shfl_up_sync(0xffffffffu, ws, off);
         if (lane >= off) ws += a;
       }
-      uint32_t o = __shfl_sync(0xffffffffu, ws - wtot, wid) + inc - cnt;
-      for (uint32_t i = i0; i < i1; ++i)
-        if (sval[i] >= kv) {
-          if (o < (uint32_t)p.k) out[o] = spos[i];
-          ++o;
+      uint32_t slot = m_run + __shfl_sync(0xffffffffu, ws - wtot, wid) + inc - cnt;
+      const uint32_t total = __shfl_sync(0xffffffffu, ws, NT / 32 - 1);
+      if (!all_landed || m_run + total > (uint32_t)kSurvCap) fast = false;   // block-uniform
+      if (fast) {
+#pragma unroll
+        for (int q = 0; q < NQ; ++q) {
+          const uint32_t pos = (uint32_t)(start + 4 * (q * NT + tid));
+          if (v[q].x >= t_lo) { sval[slot] = v[q].x; spos[slot] = pos; ++slot; }
+          if (v[q].y >= t_lo) { sval[slot] = v[q].y; spos[slot] = pos + 1; ++slot; }
+          if (v[q].z >= t_lo) { sval[slot] = v[q].z; spos[slot] = pos + 2; ++slot; }
+          if (v[q].w >= t_lo) { sval[slot] = v[q].w; spos[slot] = pos + 3; ++slot; }
         }
-    } else {
-      // ---- exact path over the row re-read from memory: bitwise radix select (unless the
-      // k-th value is already known) and ordered emission
-      if (!have_kth) {
-        uint32_t kmax = 0u, kmin = 0xffffffffu;
-        for (int i = tid; i < n; i += NT) {
-          const uint32_t u = key_mem(i);
-          kmax = max(kmax, u);
-          kmin = min(kmin, u);
-        }
-        block_max_min<NT>(sh, kmax, kmin);
-        kth = radix_kth<NT>(sh, key_mem, n, kmax, kmin, (uint32_t)p.k, &ties);
       }
-      emit_ordered<NT>(sh, key_mem, n, kth, ties, out, p.k);
+      m_run += total;
+      __syncthreads();             // sh.wa is reused by the next chunk's scan
     }
-    SEL_TS(6);
+    if (m_run < (uint32_t)p.k) fast = false;       // the threshold was too high
+    finish_row<NT>(sh, red_a, red_b, &eq_total, sval, spos, m_run, fast, row, n, p.k, out);
     __syncthreads();               // sh.* is reused by the next row
-#ifdef LT_SEL_TS
-    SEL_TS(7);
-    if (threadIdx.x == 0 && t >= p.T - 4) for (int i = 0; i < 8; ++i) out[i] = (int32_t)(ts[i] - ts[0]);
-#endif
   }
 }
 
@@ -1003,8 +951,19 @@ extern "C" int litedsa_topk_select(const float* logits, const int32_t* lengths, 
     kern<<<grid, kStreamThreads, dyn, st>>>(p);
     return cudaGetLastError() == cudaSuccess ? LITEDSA_OK : LITEDSA_ERR_CUDA;
   }
-  if (S <= kMaxSmemRow) return launch(topk_select_kernel<1024, 0, true>, 1024, smem);
-  return launch(topk_select_kernel<1024, 0, false>, 1024, 0);
+  if (aligned) {
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const size_t dyn = (size_t)2 * kChunk * 4 + (size_t)kSurvCap * 8;
+    if (cudaFuncSetAttribute(topk_select_chunked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)dyn) != cudaSuccess)
+      return LITEDSA_ERR_CUDA;
+    topk_select_chunked_kernel<<<T < sms ? T : sms, kStreamThreads, dyn, st>>>(p);
+    return cudaGetLastError() == cudaSuccess ? LITEDSA_OK : LITEDSA_ERR_CUDA;
+  }
+  if (S <= kMaxSmemRow) return launch(topk_select_kernel<true>, kGenericThreads, smem);
+  return launch(topk_select_kernel<false>, kGenericThreads, 0);
 }
 
 // Status block of the index-logits kernel (same layout as litedsa_attn_status).

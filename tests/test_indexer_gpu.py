@@ -89,14 +89,15 @@ def test_topk_select_is_exact(T, S, k, pos0, levels):
     assert np.array_equal(_canon(got), ref)
 
 
+@pytest.mark.parametrize("S", [32768, 70000])      # register-resident rows / chunked streaming
 @pytest.mark.parametrize("kind", ["sample_high", "sample_flat", "sample_low", "inf", "few_distinct"])
-def test_topk_select_when_the_sampled_threshold_misleads(kind):
+def test_topk_select_when_the_sampled_threshold_misleads(kind, S):
     """Rows built against the fast path of the streaming kernel, whose filter threshold comes
     from 2048 evenly spaced samples (positions (j * n) >> 11): the samples lie about the row, or
     the row holds infinities / very few distinct values.  The result must still be exact."""
-    T, S, k = 6, 32768, 2048
+    T, k = 6, 2048
     x = _random_logits(T, S, seed=77)
-    lens = torch.tensor([32768, 30001, 20000, 32768, 9000, 4097], dtype=torch.int32)
+    lens = torch.tensor([S, S - 2767, S // 2 + 3, S, 9000, 4097], dtype=torch.int32)
     for t in range(T):
         n = int(lens[t])
         pos = (torch.arange(2048, dtype=torch.int64) * n) >> 11
@@ -125,6 +126,24 @@ def test_topk_select_with_lengths_and_row_pitch():
     ref = io.topk_exact(x[:, :S], k, lengths=lens)
     xd = x.to(DEV)
     got = api.topk_select(xd.as_strided((T, S), (2304, 1)), k, lengths=lens.to(DEV))
+    torch.cuda.synchronize()
+    assert np.array_equal(_canon(got), ref)
+
+
+@pytest.mark.parametrize("S,k", [(3000, 256), (60001, 1024)])
+def test_topk_select_on_unaligned_rows(S, k):
+    """A row pitch that is not a multiple of four floats: the generic kernel (row keys in shared
+    memory, or re-read from memory for long rows) instead of the streaming ones."""
+    T = 5
+    pitch = S + 1 + (S % 2)                 # odd
+    g = torch.Generator().manual_seed(S)
+    buf = torch.randn((T * pitch + 8,), generator=g)
+    buf[::97] = torch.round(buf[::97])      # some ties
+    xd = buf.to(DEV)
+    view = xd[1:].as_strided((T, S), (pitch, 1))
+    lens = torch.tensor([S, S - 1, k + 1, k, S // 2], dtype=torch.int32)
+    ref = io.topk_exact(buf[1:].as_strided((T, S), (pitch, 1)), k, lengths=lens)
+    got = api.topk_select(view, k, lengths=lens.to(DEV))
     torch.cuda.synchronize()
     assert np.array_equal(_canon(got), ref)
 
