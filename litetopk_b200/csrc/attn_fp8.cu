@@ -255,13 +255,13 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
       float li = 0.f, real_m = -INFINITY;
       const int k_first = (g - kb0) & 1;          // first local block with (kb0 + k) % 2 == g
       uint2 mk = make_uint2(~0u, ~0u);
-      if (mrow && k_first < nb) mk = __ldg(reinterpret_cast<const uint2*>(mrow + (size_t)k_first * 4));
+      if (mrow && k_first < nb) mk = __ldcs(reinterpret_cast<const uint2*>(mrow + (size_t)k_first * 4));
 
       for (int k = k_first; k < nb; k += 2) {
         const int kb = kb0 + k;
         const uint32_t ph = (kb >> 1) & 1;
         uint2 mk_next = mk;
-        if (mrow && k + 2 < nb) mk_next = __ldg(reinterpret_cast<const uint2*>(mrow + (size_t)(k + 2) * 4));
+        if (mrow && k + 2 < nb) mk_next = __ldcs(reinterpret_cast<const uint2*>(mrow + (size_t)(k + 2) * 4));
 
         {
           const BlockIdx bi(kb);
@@ -441,13 +441,14 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
     Cursor ck, cv;   // K gather, V gather
     cur_init(ck);
     cur_init(cv);
-    // the KV cache is re-read by every tile (keep it in L2); q and out stream through once
+    // the KV cache is re-read by every tile (keep it in L2); q and out stream through once, and
+    // so do the index lists and membership words (streaming loads: they must not push KV rows out)
     const uint64_t pol_keep = l2_policy_evict_last(), pol_stream = l2_policy_evict_first();
     // lane l < 16 holds the index of own key 8pw + l%8 (K tile rows), lane l >= 16 of key
     // 16pw + l - 16 of the block's 128 keys (V tile rows)
     const int my_key = lane < 16 ? 64 * (int)cta + 8 * pw + (lane & 7) : 16 * pw + (lane - 16);
     auto load_idx = [&](const Cursor& c) -> int {
-      const int v = __ldg(p.indices + (size_t)c.tile * p.idx_stride + (size_t)c.k * kBlockKeys + my_key);
+      const int v = __ldcs(p.indices + (size_t)c.tile * p.idx_stride + (size_t)c.k * kBlockKeys + my_key);
       return ((unsigned)v < (unsigned)p.s_kv) ? v : 0;     // out-of-range rows are masked later
     };
     // The indices of a block are loaded right after the previous block's gather has been issued
@@ -790,13 +791,13 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
       const int count = tile_count(tile);
       const int nb = blocks_of(count);
       const int32_t* idx_row = p.indices + (size_t)tile * p.idx_stride;
-      int4 cur = __ldg(reinterpret_cast<const int4*>(idx_row) + lane);
+      int4 cur = __ldcs(reinterpret_cast<const int4*>(idx_row) + lane);
       for (int k = 0; k < nb; ++k) {
         const int kb = kb0 + k;
         const int s = kb & 1;
         const uint32_t ph = (kb >> 1) & 1;
         int4 nxt = cur;
-        if (k + 1 < nb) nxt = __ldg(reinterpret_cast<const int4*>(idx_row + (size_t)(k + 1) * kBlockKeys) + lane);
+        if (k + 1 < nb) nxt = __ldcs(reinterpret_cast<const int4*>(idx_row + (size_t)(k + 1) * kBlockKeys) + lane);
         const int rank0 = k * kBlockKeys + lane * 4;
         auto ok = [&](int idx, int rk) -> uint32_t {
           return (idx >= 0 && idx < p.s_kv && rk < count) ? 1u : 0u;

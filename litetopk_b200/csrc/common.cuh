@@ -276,6 +276,7 @@ __device__ __forceinline__ uint64_t l2_policy_evict_last() {
   asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
   return pol;
 }
+
 // 16-byte asynchronous global -> shared copy (LSU path, any shared destination) with an L2
 // eviction hint, and below the asynchronous arrival that fires when all earlier cp.async of
 // the thread have landed (.noinc: the arrival counts against the barrier's expected count)
