@@ -424,19 +424,26 @@ def dsv4_config_record(api, w, dev, steps, bf16_peak, with_ref):
     out = torch.empty((ng, 128, 512), dtype=torch.bfloat16, device=dev)
     lse = torch.empty((ng, 128), dtype=torch.float32, device=dev)
     api.bf16_status(reset=True)
-    ms_g = cuda_time(lambda: api.dsv4_masked_mla_bf16_out(ops[0], ops[1], ops[2], ops[3], ops[4], ops[5], ops[6],
-                                                          synth.SM_SCALE, w.heads, out, lse, None), steps)
-    if api.bf16_status()[0] != 0:
+    api.dsv4_status(reset=True)
+    call = lambda detect: api.dsv4_masked_mla_bf16_out(ops[0], ops[1], ops[2], ops[3], ops[4], ops[5], ops[6],  # noqa: E731
+                                                       synth.SM_SCALE, w.heads, out, lse, None, detect_runs=detect)
+    ms_g = cuda_time(lambda: call(True), steps)       # lists classified on the device: the range kernel runs
+    ms_gg = cuda_time(lambda: call(False), steps)     # the gather kernel, whatever the lists look like
+    if api.bf16_status()[0] != 0 or api.dsv4_status()[0] != 0:
         raise SystemExit("device-side wait expired")
     rec["gathered_list_form"] = {"ms_per_step": ms_g, "value": w.tokens / (ms_g * 1e-3),
                                  "frac": flop / (ms_g * 1e-3) / 1e12 / bf16_peak,
-                                 "entry": "dsv4_masked_mla_bf16 (reference argument list), 576 dims"}
+                                 "entry": "dsv4_masked_mla_bf16 (reference argument list), 576 dims; the index "
+                                          "lists are classified on the device (two contiguous runs each) and "
+                                          "the range kernel reads K / V with tiled TMA loads",
+                                 "gather_kernel_ms": ms_gg}
     del q, kc, kr, ops, out, lse
     torch.cuda.empty_cache()
     if with_ref:
         ref = ref_module_leg(w.name, 0, steps)
         if "unavailable" not in ref:
             ref["ratio_attn"] = ref["attn_ms"] / ms
+            ref["ratio_same_signature"] = ref["attn_ms"] / ms_g     # both through the reference's argument list
         rec["ref_module"] = ref
     return rec
 

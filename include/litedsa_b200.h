@@ -238,8 +238,17 @@ int litedsa_dsv4_status(int* out4_host, int reset);
  *   packed layout): q and out addressed in place inside [T, H_padded, d] tensors with
  *   h_per_q real heads per token, as in litedsa_masked_mla_fp8_ex -- the zero-copy form the
  *   reference planned for this operator (kernels/b200/dsa/DSV4_ZEROCOPY_PLAN.md:50-76).
- * With d = 576 the first call on a device reads a one-thread probe back synchronously
- * (dynamic shared-memory alignment): make that call outside stream capture.
+ *   workspace, workspace_bytes: NULL / 0, or a caller-owned device buffer of at least
+ *   16 + 16 * ng bytes (16-byte aligned).  With a workspace the library first classifies every
+ *   tile's index list ON THE DEVICE: when all of them are two contiguous ascending runs of rows
+ *   (the packed prefix + sliding window lists this operator exists for) the attention runs in
+ *   a kernel that reads K and V with plain tiled TMA loads instead of gathering rows; otherwise
+ *   the gather kernel runs.  Both kernels are enqueued and one of them returns at once, so
+ *   there is no host synchronisation and the results are the same to rounding (block
+ *   boundaries of the online softmax differ).  The workspace may be reused by later calls on
+ *   the same stream.
+ * With d = 576 or a workspace the first call on a device reads a one-thread probe back
+ * synchronously (dynamic shared-memory alignment): make that call outside stream capture.
  */
 int litedsa_dsv4_masked_mla_bf16(const void* q, const void* kv, const int32_t* indices,
                                  const int32_t* pref, const int32_t* win_lo,
@@ -248,7 +257,8 @@ int litedsa_dsv4_masked_mla_bf16(const void* q, const void* kv, const int32_t* i
                                  int ng, int s_kv, int topk, int d, int64_t q_row_stride,
                                  int64_t kv_row_stride, int64_t indices_row_stride,
                                  int64_t q_token_stride, int64_t q_head_stride,
-                                 int64_t out_token_stride, int64_t out_head_stride, void* stream);
+                                 int64_t out_token_stride, int64_t out_head_stride,
+                                 void* workspace, int64_t workspace_bytes, void* stream);
 
 /*
  * masked_mla_fp8's bf16 twin for KV caches that have no single-scale all-e4m3 form (per-128

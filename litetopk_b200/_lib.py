@@ -50,7 +50,8 @@ SIGNATURES = {
     "litedsa_dsv4_masked_mla_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                              c_void_p, c_float, c_int, c_void_p, c_void_p, c_void_p,
                                              c_int, c_int, c_int, c_int, c_int64, c_int64, c_int64,
-                                             c_int64, c_int64, c_int64, c_int64, c_void_p]),
+                                             c_int64, c_int64, c_int64, c_int64, c_void_p, c_int64,
+                                             c_void_p]),
     "litedsa_masked_mla_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
                                         c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                         c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p]),

@@ -311,7 +311,8 @@ def dsv4_masked_mla_bf16_out(q: torch.Tensor, kv: torch.Tensor, indices: torch.T
                              pref: torch.Tensor, win_lo: torch.Tensor, win_hi: torch.Tensor,
                              counts: torch.Tensor, sm_scale: float, h_per_q: int,
                              out: torch.Tensor, lse: torch.Tensor,
-                             attn_sink: Optional[torch.Tensor], *, in_place_heads: bool = False) -> None:
+                             attn_sink: Optional[torch.Tensor], *, in_place_heads: bool = False,
+                             detect_runs: bool = True) -> None:
     """The reference's DSv4 operator, same argument order
     (kernels/b200/dsa/litedsa_dsv4.cu:50-55): q [ng,128,d] bf16, kv [s_kv,(1,)d] bf16 flat
     workspace, indices [ng,(1,)topk] i32 ascending union rows (-1 padded, topk % 64 == 0),
@@ -323,7 +324,13 @@ def dsv4_masked_mla_bf16_out(q: torch.Tensor, kv: torch.Tensor, indices: torch.T
     ``[T, H_padded, 512]`` tensor with ``h_per_q`` real heads per token (unit inner stride);
     the kernel reads and writes them in place, so the pack copy of q and the unpack copy of out
     that the reference's packed path makes (kernels/b200/dsa/DSV4_ZEROCOPY_PLAN.md:12-22) go
-    away.  lse stays packed ``[ng,128]``."""
+    away.  lse stays packed ``[ng,128]``.
+
+    ``detect_runs`` (default): the index lists are classified on the device and, when every
+    tile's list is two contiguous runs of rows (the packed prefix + window pattern), the
+    attention runs in the kernel that reads K / V with tiled TMA loads instead of gathering
+    rows; otherwise in the gather kernel.  No host synchronisation either way; a small cached
+    device workspace (16 + 16 * ng bytes per device) carries the decision."""
     G = 128 // int(h_per_q)
     strides = (0, 0, 0, 0)
     if in_place_heads:
@@ -359,13 +366,30 @@ def dsv4_masked_mla_bf16_out(q: torch.Tensor, kv: torch.Tensor, indices: torch.T
     _need(counts, "counts", torch.int32, 1)
     if counts.shape[0] != ng or not counts.is_contiguous():
         raise ValueError("counts must be a contiguous [ng]")
+    ws = _runs_workspace(q.device, ng) if detect_runs else None
     with torch.cuda.device(q.device):
         rc = _lib.lib().litedsa_dsv4_masked_mla_bf16(
             _ptr(q), _ptr(kv), _ptr(indices), _ptr(pref), _ptr(win_lo), _ptr(win_hi), _ptr(counts),
             float(sm_scale), int(h_per_q), _ptr(out), _ptr(lse), _ptr(_sink128(attn_sink)), ng,
             kv.shape[0], topk, d, q_row_stride, kv.stride(0), indices.stride(0), strides[0], strides[1],
-            strides[2], strides[3], _stream(q))
+            strides[2], strides[3], _ptr(ws), 0 if ws is None else ws.numel(), _stream(q))
     check(rc, "dsv4_masked_mla_bf16")
+
+
+_RUNS_WS = {}
+
+
+def _runs_workspace(device: torch.device, ng: int) -> torch.Tensor:
+    """Per (device, stream) byte buffer for the run classification of the DSv4 operator
+    (grown on demand, reused by later calls on the same stream)."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(device).cuda_stream)
+    need = 16 + 16 * int(ng)
+    ws = _RUNS_WS.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty((max(need, 1 << 16),), dtype=torch.uint8, device=device)
+        _RUNS_WS[key] = ws
+    return ws
 
 
 def _status(fn_name: str, reset: bool, device) -> Tuple[int, int, int, int]:

@@ -112,6 +112,10 @@ struct Params {
   float scale_log2;
   int epoch;
   unsigned long long wait_limit_ns;
+  // the launch runs only if *gate == gate_value (null: always): the device-side choice between
+  // this kernel and the range kernel's rank mode
+  const int* gate;
+  int gate_value;
 };
 
 enum { kSiteQ = 201, kSiteKLand, kSiteKPeer, kSiteVLand, kSiteVPeer, kSiteQkDone, kSitePvDone,
@@ -152,6 +156,7 @@ masked_mla_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
   uint8_t* sm = smem_raw + (sbase - raw);
   Misc& ms = *reinterpret_cast<Misc*>(sm + PL::kOffMisc);
   const Waiter wt{g_status, p.epoch, p.wait_limit_ns};
+  if (p.gate != nullptr && *reinterpret_cast<const volatile int*>(p.gate) != p.gate_value) return;
   // refuse to run (uniformly, in both CTAs, before any barrier exists) if aligning the base
   // would push the plan past the allocation
   if ((sbase - raw) + PL::kUsed > PL::kSmem) {
@@ -716,6 +721,7 @@ struct Args {
   float sm_scale;
   // in-place addressing of q / out inside [T, H_padded, d] tensors (ELEMENTS, 0 = dense packed)
   int64_t q_token_stride, q_head_stride, out_token_stride, out_head_stride;
+  const int* gate = nullptr;      // run only if *gate == 1 (see Params)
 };
 
 // argument rules shared by both entry points (no CUDA call)
@@ -765,6 +771,7 @@ static int launch(const Args& a, cudaStream_t stream) {
   p.ng = a.ng; p.s_kv = a.s_kv; p.cap = a.topk; p.h_per_q = a.h_per_q; p.G = 128 / a.h_per_q;
   p.scale_log2 = a.sm_scale * kLog2e;
   p.epoch = next_launch_epoch(); p.wait_limit_ns = wait_limit_ns();
+  p.gate = a.gate; p.gate_value = 1;
   if (!smem_alignment_ok<kD>()) return LITEDSA_ERR_UNSUPPORTED;
   if (cudaFuncSetAttribute(masked_mla_bf16_kernel<kD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (int)PL::kSmem) != cudaSuccess)
@@ -834,12 +841,29 @@ extern "C" int litedsa_dsv4_masked_mla_bf16(const void* q, const void* kv, const
                                             int d, int64_t q_row_stride, int64_t kv_row_stride,
                                             int64_t indices_row_stride, int64_t q_token_stride,
                                             int64_t q_head_stride, int64_t out_token_stride,
-                                            int64_t out_head_stride, void* stream) {
+                                            int64_t out_head_stride, void* workspace,
+                                            int64_t workspace_bytes, void* stream) {
   using namespace lt::b16;
   if (!pref || !win_lo || !win_hi || !counts) return LITEDSA_ERR_ARG;
   Args a{q, kv, indices, counts, nullptr, pref, win_lo, win_hi, attn_sink, out, nullptr, lse,
          ng, s_kv, topk, d, h_per_q, q_row_stride, kv_row_stride, indices_row_stride, sm_scale,
          q_token_stride, q_head_stride, out_token_stride, out_head_stride};
+  const int rc = check(a);
+  if (rc != LITEDSA_OK) return rc;
+  // With a workspace the device decides: when every tile's index list is two contiguous runs
+  // of rows (the packed prefix + window pattern this operator exists for) the range kernel
+  // reads K and V with tiled TMA loads and the gather kernel returns at once; otherwise the
+  // range kernel returns at once and the gather kernel does the work.
+  if (workspace != nullptr) {
+    if (workspace_bytes < 16 + 16 * (int64_t)ng || ((uintptr_t)workspace & 15)) return LITEDSA_ERR_SHAPE;
+    const int rc2 = lt::dsv4_rank_enqueue(q, kv, indices, pref, win_lo, win_hi, counts, sm_scale, h_per_q, out,
+                                          lse, attn_sink, ng, s_kv, topk, d, q_row_stride, kv_row_stride,
+                                          indices_row_stride, q_token_stride, q_head_stride,
+                                          out_token_stride, out_head_stride, workspace,
+                                          reinterpret_cast<cudaStream_t>(stream));
+    if (rc2 != LITEDSA_OK) return rc2;
+    a.gate = reinterpret_cast<const int*>(workspace);
+  }
   return run(a, stream);
 }
 

@@ -74,6 +74,19 @@ struct Params {
   float scale_log2;
   int epoch;                          // this launch's epoch for the bounded waits
   unsigned long long wait_limit_ns;
+  // rank mode (the reference operator's argument list, litedsa_dsv4.cu:50-55, when every
+  // tile's gathered index list is two contiguous runs of rows of one flat KV workspace):
+  // runs[tile] = (first row of run 0, its length, first row of run 1, its length); a token may
+  // attend the list ranks  rank < pref  or  win_lo <= rank < win_hi  (rank < counts)
+  const int4* runs;          // [ng] or null (position mode)
+  const int32_t* pref;       // [ng, G]
+  const int32_t* win_lo;     // [ng, G]
+  const int32_t* win_hi;     // [ng, G]
+  const int32_t* counts;     // [ng] or null
+  // the launch runs only if *gate == gate_value (null: always); lets the host enqueue this
+  // kernel and the gather kernel back to back and have the device pick one of them
+  const int* gate;
+  int gate_value;
 };
 
 enum { kSiteQ = 101, kSiteKFull, kSiteVFull, kSiteQkDone, kSitePvDone, kSiteSFree, kSitePReady,
@@ -84,18 +97,32 @@ __device__ int g_status[8];
 
 // key segments of a tile: compressed blocks first, then window blocks
 struct TilePlan {
-  int p0, pref_max, wlo, count_w, nbc, nb;
+  int p0, pref_max, wlo, count_w, nbc, nb, row_c;   // row_c: first row of the first segment
 };
+template <bool kRank>
 __device__ __forceinline__ TilePlan plan_tile(const Params& p, int tile) {
   TilePlan t;
-  t.p0 = p.pos0 + tile * p.G;
-  const int plast = t.p0 + p.G - 1;
-  t.pref_max = min(plast / p.ratio, p.n_comp);
-  t.wlo = max(0, t.p0 - p.window + 1);
-  t.count_w = plast - t.wlo + 1;
+  if (kRank) {
+    const int4 r = __ldg(p.runs + tile);
+    t.p0 = 0;
+    t.row_c = r.x; t.pref_max = max(r.y, 0);
+    t.wlo = r.z;   t.count_w = max(r.w, 0);
+  } else {
+    t.p0 = p.pos0 + tile * p.G;
+    const int plast = t.p0 + p.G - 1;
+    t.row_c = 0;
+    t.pref_max = min(plast / p.ratio, p.n_comp);
+    t.wlo = max(0, t.p0 - p.window + 1);
+    t.count_w = plast - t.wlo + 1;
+  }
   t.nbc = (t.pref_max + kBlockKeys - 1) / kBlockKeys;
   t.nb = t.nbc + (t.count_w + kBlockKeys - 1) / kBlockKeys;
+  if (t.nb == 0) t.nb = 1;      // an empty list: one fully masked block keeps the pipeline uniform
   return t;
+}
+// bits [0, x) of a 32-bit word (x may be negative or beyond 32)
+__device__ __forceinline__ uint32_t low_bits(int x) {
+  return x <= 0 ? 0u : (x >= 32 ? 0xffffffffu : ((1u << x) - 1u));
 }
 
 __device__ __forceinline__ void mma_f16_elect(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
@@ -107,6 +134,7 @@ __device__ __forceinline__ void mma_f16_elect(uint32_t d_tmem, uint64_t adesc, u
       : "memory");
 }
 
+template <bool kRank>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kc32,
             const __grid_constant__ CUtensorMap map_kr32, const __grid_constant__ CUtensorMap map_kc64,
@@ -118,6 +146,8 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
   uint8_t* sm = smem_raw + (sbase - raw);
   Misc& ms = *reinterpret_cast<Misc*>(sm + kOffMisc);
   const Waiter wt{g_status, p.epoch, p.wait_limit_ns};
+  // device-side choice between this kernel and the gather kernel (uniform across the grid)
+  if (p.gate != nullptr && *reinterpret_cast<const volatile int*>(p.gate) != p.gate_value) return;
   // the plan leaves less than 1024 bytes for aligning the base: refuse to run (uniformly, in
   // both CTAs, before any barrier exists) if this launch's base needs more
   if ((sbase - raw) + kSmemUsed > kSmem) {
@@ -176,12 +206,23 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
     const uint32_t a_p_ready = mapa(smem_u32(&ms.p_ready), 0);
     int kb0 = 0, it = 0;
    for (int tile = cid; tile < p.ng; tile += ncl) {
-    const TilePlan tp = plan_tile(p, tile);
+    const TilePlan tp = plan_tile<kRank>(p, tile);
     const int nb = tp.nb;
-    const int pq = tp.p0 + q;
-    const int pref_q = min(pq / p.ratio, p.n_comp);
-    const int lo_q = max(pq - p.window + 1, 0) - tp.wlo;   // window-rank range of this token
-    const int hi_q = pq - tp.wlo + 1;
+    int pref_q, lo_q, hi_q;
+    if (kRank) {
+      // list ranks this token may attend: rank < pref_q, or lo_q <= rank < hi_q (all < cnt)
+      const int cnt = p.counts ? min(max(__ldg(p.counts + tile), 0), tp.pref_max + tp.count_w)
+                               : tp.pref_max + tp.count_w;
+      const size_t tq = (size_t)tile * p.G + q;
+      pref_q = min(__ldg(p.pref + tq), cnt);
+      lo_q = __ldg(p.win_lo + tq);
+      hi_q = min(__ldg(p.win_hi + tq), cnt);
+    } else {
+      const int pq = tp.p0 + q;
+      pref_q = min(pq / p.ratio, p.n_comp);
+      lo_q = max(pq - p.window + 1, 0) - tp.wlo;   // window-rank range of this token
+      hi_q = pq - tp.wlo + 1;
+    }
     float m = kMInit, li = 0.f, real_m = -INFINITY;
 
     for (int k = 0; k < nb; ++k) {
@@ -197,23 +238,39 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(a_s_free[s]);
 
-      // columns this thread holds: keys [32h, 32h+32) of the block, as a contiguous valid range
-      int v_lo, v_hi;
-      if (k < tp.nbc) {                       // compressed block: rank = 64k + j < pref_q
-        v_lo = 0;
-        v_hi = pref_q - (k * kBlockKeys + 32 * h);
-      } else {                                // window block: lo_q <= 64(k-nbc) + j < hi_q
-        const int base = (k - tp.nbc) * kBlockKeys + 32 * h;
-        v_lo = lo_q - base;
-        v_hi = hi_q - base;
-      }
-      v_lo = max(v_lo, 0);
-      v_hi = min(v_hi, 32);
       float cur = -INFINITY;
+      if (kRank) {
+        // columns this thread holds: 32 consecutive list ranks starting at `off`, of which the
+        // first `lim` exist in this segment; valid = existing and in one of the token's two
+        // rank ranges -- one 32-bit mask per block
+        const bool seg0 = k < tp.nbc;
+        const int base = (seg0 ? k : k - tp.nbc) * kBlockKeys + 32 * h;
+        const int lim = (seg0 ? tp.pref_max : tp.count_w) - base;
+        const int off = (seg0 ? 0 : tp.pref_max) + base;
+        const uint32_t vm = low_bits(lim) & (low_bits(pref_q - off) | (low_bits(hi_q - off) & ~low_bits(lo_q - off)));
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        sv[j] = (j >= v_lo && j < v_hi) ? sv[j] : -INFINITY;
-        cur = fmaxf(cur, sv[j]);
+        for (int j = 0; j < 32; ++j) {
+          sv[j] = ((vm >> j) & 1u) ? sv[j] : -INFINITY;
+          cur = fmaxf(cur, sv[j]);
+        }
+      } else {
+        // columns this thread holds: keys [32h, 32h+32) of the block, as a contiguous valid range
+        int v_lo, v_hi;
+        if (k < tp.nbc) {                       // compressed block: rank = 64k + j < pref_q
+          v_lo = 0;
+          v_hi = pref_q - (k * kBlockKeys + 32 * h);
+        } else {                                // window block: lo_q <= 64(k-nbc) + j < hi_q
+          const int base = (k - tp.nbc) * kBlockKeys + 32 * h;
+          v_lo = lo_q - base;
+          v_hi = hi_q - base;
+        }
+        v_lo = max(v_lo, 0);
+        v_hi = min(v_hi, 32);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          sv[j] = (j >= v_lo && j < v_hi) ? sv[j] : -INFINITY;
+          cur = fmaxf(cur, sv[j]);
+        }
       }
       cur *= c;
       ms.xbuf[kb & 1][tl] = cur;
@@ -296,7 +353,7 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
       const uint64_t pol_stream = l2_policy_evict_first();     // q streams through once
       int kb0 = 0, it = 0;
       for (int tile = cid; tile < p.ng; tile += ncl, ++it) {
-        const TilePlan tp = plan_tile(p, tile);
+        const TilePlan tp = plan_tile<kRank>(p, tile);
         const int nb = tp.nb;
         // the previous tile's Q must have been consumed by its last QK^T
         if (it > 0) mbar_wait(&ms.q_free, (it - 1) & 1, wt, kSiteQFree, it);
@@ -311,7 +368,7 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
           const int s = kb & 1;
           const uint32_t ph = (kb >> 1) & 1;
           const bool comp = k < tp.nbc;
-          const int row0 = comp ? k * kBlockKeys : tp.wlo + (k - tp.nbc) * kBlockKeys;
+          const int row0 = comp ? tp.row_c + k * kBlockKeys : tp.wlo + (k - tp.nbc) * kBlockKeys;
           const CUtensorMap* m32 = comp ? &map_kc32 : &map_kr32;
           const CUtensorMap* m64 = comp ? &map_kc64 : &map_kr64;
           if (kb >= 2) mbar_wait(&ms.qk_done[s], ph ^ 1, wt, kSiteKFree, k);   // K stage free
@@ -345,7 +402,7 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
     const uint32_t a_o_free = mapa(smem_u32(&ms.o_free), 0);
     int kb0 = 0, it = 0;
     for (int tile = cid; tile < p.ng; tile += ncl, ++it) {
-      const int nb = plan_tile(p, tile).nb;
+      const int nb = plan_tile<kRank>(p, tile).nb;
       const int kbl = kb0 + nb - 1;                 // last block of the tile
       mbar_wait(&ms.epi_ready, it & 1, wt, kSiteEpi, it);
       mbar_wait(&ms.pv_done[kbl & 1], (kbl >> 1) & 1, wt, kSiteEpi, nb);
@@ -402,7 +459,7 @@ dsv4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
     const uint32_t a_q_free_peer = mapa(smem_u32(&ms.q_free), 1);
     int kb0 = 0, it = 0;
     for (int tile = cid; tile < p.ng; tile += ncl, ++it) {
-      const int nb = plan_tile(p, tile).nb;
+      const int nb = plan_tile<kRank>(p, tile).nb;
       mbar_wait(&ms.q_full, it & 1, wt, kSiteQ, it);
       __syncwarp();
       for (int k = 0; k <= nb; ++k) {
@@ -512,14 +569,101 @@ static int max_clusters() {
   at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
   cfg.attrs = &at; cfg.numAttrs = 1;
   int q = 0;
-  if (cudaFuncSetAttribute(dsv4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) == cudaSuccess &&
-      cudaOccupancyMaxActiveClusters(&q, dsv4_kernel, &cfg) == cudaSuccess && q > 0)
+  if (cudaFuncSetAttribute(dsv4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) == cudaSuccess &&
+      cudaOccupancyMaxActiveClusters(&q, dsv4_kernel<false>, &cfg) == cudaSuccess && q > 0)
     n = q;
   cudaGetLastError();
   cached_dev = dev; cached = n;
   return n;
 }
 
+// One warp per tile: is the tile's gathered index list (its first counts[tile] entries) two
+// contiguous ascending runs of valid rows?  runs[tile] = (first row of run 0, its length, first
+// row of run 1, its length); a tile that is not sets *gate (cleared by the host beforehand) to 1.
+__global__ void __launch_bounds__(128)
+classify_runs_kernel(const int32_t* __restrict__ indices, long long idx_stride, int topk,
+                     const int32_t* __restrict__ counts, int ng, int s_kv, int4* __restrict__ runs,
+                     int* __restrict__ gate) {
+  const int tile = (int)((blockIdx.x * (unsigned)blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
+  if (tile >= ng) return;
+  const int32_t* row = indices + (size_t)tile * idx_stride;
+  const int cnt = min(max(counts ? __ldg(counts + tile) : topk, 0), topk);
+  int breaks = 0, first_break = 0x7fffffff, bad = 0;
+  for (int j = lane; j < cnt; j += 32) {
+    const int v = __ldg(row + j);
+    bad |= (v < 0 || v >= s_kv);
+    if (j + 1 < cnt && __ldg(row + j + 1) != v + 1) {
+      ++breaks;
+      first_break = min(first_break, j);
+    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    breaks += __shfl_xor_sync(0xffffffffu, breaks, off);
+    first_break = min(first_break, __shfl_xor_sync(0xffffffffu, first_break, off));
+    bad |= __shfl_xor_sync(0xffffffffu, bad, off);
+  }
+  if (lane == 0) {
+    const int l0 = breaks ? first_break + 1 : cnt;
+    const int a0 = cnt > 0 ? __ldg(row) : 0;
+    const int b0 = l0 < cnt ? __ldg(row + l0) : 0;
+    runs[tile] = make_int4(a0, l0, b0, cnt - l0);
+    if (bad || breaks > 1) atomicOr(gate, 1);
+  }
+}
+
+}  // namespace dsv4
+
+// Rank mode of the range kernel for the reference operator's argument list (see
+// litedsa_dsv4_masked_mla_bf16): classifies every tile's index list on the device, then enqueues
+// the range kernel gated on "every tile is two contiguous runs".  workspace: 16 + 16 * ng bytes
+// (gate word, then runs[ng]); the caller enqueues the gather kernel behind it, gated on the
+// opposite value, so exactly one of the two does the work -- no host synchronisation.
+int dsv4_rank_enqueue(const void* q, const void* kv, const int32_t* indices, const int32_t* pref,
+                      const int32_t* win_lo, const int32_t* win_hi, const int32_t* counts,
+                      float sm_scale, int h_per_q, void* out, float* lse, const float* attn_sink,
+                      int ng, int s_kv, int topk, int d, int64_t q_row_stride, int64_t kv_row_stride,
+                      int64_t indices_row_stride, int64_t q_token_stride, int64_t q_head_stride,
+                      int64_t out_token_stride, int64_t out_head_stride, void* workspace,
+                      cudaStream_t stream) {
+  using namespace dsv4;
+  int* gate = reinterpret_cast<int*>(workspace);
+  int4* runs = reinterpret_cast<int4*>(reinterpret_cast<char*>(workspace) + 16);
+  if (!smem_alignment_ok()) return LITEDSA_ERR_UNSUPPORTED;
+  if (cudaMemsetAsync(gate, 0, 16, stream) != cudaSuccess) return LITEDSA_ERR_CUDA;
+  classify_runs_kernel<<<(ng + 3) / 4, 128, 0, stream>>>(indices, indices_row_stride, topk, counts, ng, s_kv,
+                                                         runs, gate);
+  const int G = 128 / h_per_q;
+  CUtensorMap mq, mk32, mk64, mout;
+  const auto BF = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const uint64_t q_hs = (q_head_stride ? (uint64_t)q_head_stride : (uint64_t)q_row_stride) * 2;
+  const uint64_t q_ts = q_token_stride ? (uint64_t)q_token_stride * 2 : (uint64_t)h_per_q * q_hs;
+  const uint64_t o_hs = (out_head_stride ? (uint64_t)out_head_stride : (uint64_t)kDV) * 2;
+  const uint64_t o_ts = out_token_stride ? (uint64_t)out_token_stride * 2 : (uint64_t)h_per_q * o_hs;
+  const uint32_t qb_h = (uint32_t)min(h_per_q, 64), ob_h = (uint32_t)min(h_per_q, 32);
+  // tensors are declared d columns wide: for d = 512 the kernel's ninth 64-dim chunk lies
+  // outside and is zero-filled by TMA, so the 576-dim kernel serves both widths
+  if (!make_map_3d(&mq, q, BF, (uint64_t)d, (uint64_t)h_per_q, (uint64_t)ng * G, q_hs, q_ts, 64, qb_h, 64 / qb_h) ||
+      !make_map_2d(&mk32, kv, BF, (uint64_t)d, (uint64_t)s_kv, (uint64_t)kv_row_stride * 2, 64, 32) ||
+      !make_map_2d(&mk64, kv, BF, (uint64_t)d, (uint64_t)s_kv, (uint64_t)kv_row_stride * 2, 64, 64) ||
+      !make_map_3d(&mout, out, BF, kDV, (uint64_t)h_per_q, (uint64_t)ng * G, o_hs, o_ts, 32, ob_h, 32 / ob_h,
+                   CU_TENSOR_MAP_SWIZZLE_64B))
+    return LITEDSA_ERR_CUDA;
+  Params p;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out); p.lse = lse; p.sink = attn_sink;
+  p.ng = ng; p.n_comp = 0; p.s_raw = s_kv; p.G = G; p.h_per_q = h_per_q; p.pos0 = 0;
+  p.window = 1; p.ratio = 1; p.scale_log2 = sm_scale * kLog2e;
+  p.epoch = next_launch_epoch(); p.wait_limit_ns = wait_limit_ns();
+  p.runs = runs; p.pref = pref; p.win_lo = win_lo; p.win_hi = win_hi; p.counts = counts;
+  p.gate = gate; p.gate_value = 0;
+  if (cudaFuncSetAttribute(dsv4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) !=
+      cudaSuccess)
+    return LITEDSA_ERR_CUDA;
+  dsv4_kernel<true><<<2 * min(ng, max_clusters()), kThreads, kSmem, stream>>>(mq, mk32, mk32, mk64, mk64, mout, p);
+  return cudaGetLastError() == cudaSuccess ? LITEDSA_OK : LITEDSA_ERR_CUDA;
+}
+
+namespace dsv4 {
 }  // namespace dsv4
 }  // namespace lt
 
@@ -583,10 +727,11 @@ extern "C" int litedsa_dsv4_c128a_bf16(const void* q, const void* kv_comp, const
   p.window = window; p.ratio = ratio; p.scale_log2 = sm_scale * kLog2e;
   p.epoch = next_launch_epoch(); p.wait_limit_ns = wait_limit_ns();
   if (!smem_alignment_ok()) return LITEDSA_ERR_UNSUPPORTED;   // first call per device: synchronous probe
-  if (cudaFuncSetAttribute(dsv4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) !=
+  p.runs = nullptr; p.pref = p.win_lo = p.win_hi = p.counts = nullptr; p.gate = nullptr; p.gate_value = 0;
+  if (cudaFuncSetAttribute(dsv4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) !=
       cudaSuccess)
     return LITEDSA_ERR_CUDA;
-  dsv4_kernel<<<2 * min(ng, max_clusters()), kThreads, kSmem, reinterpret_cast<cudaStream_t>(stream)>>>(
+  dsv4_kernel<false><<<2 * min(ng, max_clusters()), kThreads, kSmem, reinterpret_cast<cudaStream_t>(stream)>>>(
       mq, mkc32, mkr32, mkc64, mkr64, mout, p);
   return cudaGetLastError() == cudaSuccess ? LITEDSA_OK : LITEDSA_ERR_CUDA;
 }

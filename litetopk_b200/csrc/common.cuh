@@ -44,6 +44,15 @@ struct Fp8Args {
   int64_t q_token_stride, q_head_stride, out_token_stride, out_head_stride;
 };
 int check_fp8_args(const Fp8Args& a);                                   // no CUDA call
+// attn_dsv4.cu: classify the tiles' index lists and enqueue the range kernel in rank mode, gated on
+// "every list is two contiguous runs" (workspace: 16 + 16 * ng bytes; word 0 is the gate)
+int dsv4_rank_enqueue(const void* q, const void* kv, const int32_t* indices, const int32_t* pref,
+                      const int32_t* win_lo, const int32_t* win_hi, const int32_t* counts,
+                      float sm_scale, int h_per_q, void* out, float* lse, const float* attn_sink,
+                      int ng, int s_kv, int topk, int d, int64_t q_row_stride, int64_t kv_row_stride,
+                      int64_t indices_row_stride, int64_t q_token_stride, int64_t q_head_stride,
+                      int64_t out_token_stride, int64_t out_head_stride, void* workspace,
+                      cudaStream_t stream);
 int run_fp8(const Fp8Args& a, void* const* outs, int n_outs, void* stream);
 
 // ---------------------------------------------------------------- addresses / cluster

@@ -27,7 +27,7 @@ def test_library_exports_every_declared_symbol(built_lib):
     assert sorted(_lib.SIGNATURES) == names, "ctypes table and header disagree"
     for n in names:
         assert getattr(built_lib, n) is not None
-    assert built_lib.litedsa_abi_version() >= 2
+    assert built_lib.litedsa_abi_version() >= 3
     assert b"shape" in built_lib.litedsa_error_string(2)
 
 
@@ -104,11 +104,14 @@ def test_entry_points_reject_bad_arguments_before_any_cuda_call(built_lib):
     assert na(P, P, P, ok["sm"], ok["os"], None, P, 64, P, None, P, 2, 65537, 128, 576, 128, None, None) == UNSUP
     # bf16 operators: missing range arrays, width other than 512 / 576, list not in 64-key blocks
     assert L.litedsa_dsv4_masked_mla_bf16(P, P, P, None, P, P, P, 0.1, 64, P, P, None,
-                                          2, 128, 128, 512, 512, 512, 128, 0, 0, 0, 0, None) == ARG
+                                          2, 128, 128, 512, 512, 512, 128, 0, 0, 0, 0, None, 0, None) == ARG
     assert L.litedsa_dsv4_masked_mla_bf16(P, P, P, P, P, P, P, 0.1, 64, P, P, None,
-                                          2, 128, 128, 500, 512, 512, 128, 0, 0, 0, 0, None) == SHAPE
+                                          2, 128, 128, 500, 512, 512, 128, 0, 0, 0, 0, None, 0, None) == SHAPE
     assert L.litedsa_dsv4_masked_mla_bf16(P, P, P, P, P, P, P, 0.1, 64, P, P, None,
-                                          2, 128, 96, 512, 512, 512, 96, 0, 0, 0, 0, None) == SHAPE
+                                          2, 128, 96, 512, 512, 512, 96, 0, 0, 0, 0, None, 0, None) == SHAPE
+    # a workspace too small for the tiles (16 + 16 * ng bytes) is rejected before any CUDA call
+    assert L.litedsa_dsv4_masked_mla_bf16(P, P, P, P, P, P, P, 0.1, 64, P, P, None,
+                                          2, 128, 128, 512, 512, 512, 128, 0, 0, 0, 0, P, 32, None) == SHAPE
     assert L.litedsa_masked_mla_bf16(P, P, P, 0.1, None, None, 64, P, None, P,
                                      2, 128, 128, 576, 576, 576, 128, None, None) == ARG
     assert L.litedsa_masked_mla_bf16(P, P, P, 0.1, None, P, 64, P, None, P,

@@ -246,3 +246,95 @@ def test_dsv4_signature_in_place_padded_heads(heads, hpad, d):
     assert api.bf16_status()[0] == 0
     assert torch.equal(out_pad[:, :heads].reshape(ng, 128, 512), out_p) and torch.equal(lse_i, lse_p)
     assert bool((out_pad[:, heads:] == 7.0).all())
+
+
+# --------------------------------------------------------------------------- two-run lists: the range kernel's rank mode
+def _two_run_case(ng, heads, topk, s_kv, d, seed, sink=False):
+    """Index lists that are two contiguous ascending runs of rows (lengths 0 .. topk, also one
+    run only, an empty list, a run that ends at the last row), -1 padded, with arbitrary
+    per-token rank ranges (overlapping, empty, spanning both runs, beyond the live count)."""
+    g = torch.Generator().manual_seed(seed)
+    G = 128 // heads
+    q = torch.randn((ng, 128, d), generator=g).to(torch.bfloat16)
+    kv = torch.randn((s_kv, d), generator=g).to(torch.bfloat16)
+    idx = torch.full((ng, topk), -1, dtype=torch.int32)
+    counts = torch.zeros((ng,), dtype=torch.int32)
+    for t in range(ng):
+        l0 = int(torch.randint(0, topk // 2 + 1, (1,), generator=g))
+        l1 = int(torch.randint(0, topk - l0 + 1, (1,), generator=g))
+        if t == 1:
+            l1 = 0                                     # one run only
+        if t == 2:
+            l0, l1 = 0, 0                              # an empty list
+        if t == 3:
+            l0 = 0                                     # the second run alone
+        a0 = int(torch.randint(0, s_kv // 2 - l0, (1,), generator=g))
+        b0 = int(torch.randint(a0 + l0 + 1, s_kv - l1 + 1, (1,), generator=g))
+        if t == 4:
+            b0 = s_kv - l1                             # ends at the last row of the workspace
+        idx[t, :l0] = torch.arange(a0, a0 + l0, dtype=torch.int32)
+        idx[t, l0:l0 + l1] = torch.arange(b0, b0 + l1, dtype=torch.int32)
+        counts[t] = l0 + l1
+    if ng > 5:
+        counts[5] = max(int(counts[5]) - 7, 0)         # fewer live entries than the list holds
+    pref = torch.randint(0, topk // 2, (ng, G), generator=g, dtype=torch.int32)
+    wlo = torch.randint(0, topk, (ng, G), generator=g, dtype=torch.int32)
+    whi = wlo + torch.randint(0, 300, (ng, G), generator=g, dtype=torch.int32)
+    pref[0, 0] = 0
+    whi[0, 0] = wlo[0, 0]                              # a token with both ranges empty
+    sk = torch.randn((128,), generator=g) if sink else None
+    return q, kv, idx, pref, wlo, whi, counts, sk
+
+
+@pytest.mark.parametrize("ng,heads,topk,s_kv,d,sink", [
+    (8, 64, 512, 4096, 512, False),       # the reference's width
+    (7, 32, 1088, 8192, 512, True),       # config 3's list length (17 x 64)
+    (6, 16, 320, 4096, 576, True),
+    (9, 8, 256, 2048, 576, False),
+])
+def test_dsv4_two_run_lists_take_the_range_kernel(ng, heads, topk, s_kv, d, sink):
+    q, kv, idx, pref, wlo, whi, counts, sk = _two_run_case(ng, heads, topk, s_kv, d, seed=23, sink=sink)
+    dev = [t.to(DEV) for t in (q, kv, idx, pref, wlo, whi, counts)]
+    skd = None if sk is None else sk.to(DEV)
+    outs = []
+    for detect in (True, False):
+        out = torch.full((ng, 128, 512), float("nan"), dtype=torch.bfloat16, device=DEV)
+        lse = torch.full((ng, 128), float("nan"), dtype=torch.float32, device=DEV)
+        api.bf16_status(reset=True)
+        api.dsv4_status(reset=True)
+        api.dsv4_masked_mla_bf16_out(*dev, synth.SM_SCALE, heads, out, lse, skd, detect_runs=detect)
+        torch.cuda.synchronize()
+        # exactly one of the two kernels did the work
+        assert api.bf16_status()[0] == 0 and api.dsv4_status()[0] == 0
+        assert api.dsv4_status()[3] == (1 if detect else 0), "range kernel launches completed"
+        outs.append((out, lse))
+    rank = torch.arange(topk)[None, None, :]
+    tok = (rank < pref[:, :, None]) | ((rank >= wlo[:, :, None]) & (rank < whi[:, :, None]))
+    out_e, lse_e = ao.masked_union_exact(q.float(), kv.float(), idx, counts, tok, synth.SM_SCALE, heads,
+                                         attn_sink=sk)
+    scale = max(1.0, float(out_e.abs().max()))
+    for out, lse in outs:
+        _check(out, lse, out_e, lse_e, scale=scale)
+    # the two kernels agree with each other to rounding (their softmax block boundaries differ)
+    mad, cos = ao.compare(outs[0][0].cpu(), outs[1][0].cpu().float())
+    assert mad <= TOL_ABS * scale and cos >= TOL_COS, (mad, cos)
+
+
+def test_dsv4_one_scattered_list_sends_the_whole_call_to_the_gather_kernel():
+    ng, heads, topk, s_kv, d = 6, 64, 256, 4096, 512
+    q, kv, idx, pref, wlo, whi, counts, _ = _two_run_case(ng, heads, topk, s_kv, d, seed=29)
+    # tile 0: three runs -> not the two-run pattern
+    idx[0] = -1
+    idx[0, :30] = torch.cat([torch.arange(100, 110), torch.arange(200, 210), torch.arange(300, 310)]).to(torch.int32)
+    counts[0] = 30
+    dev = [t.to(DEV) for t in (q, kv, idx, pref, wlo, whi, counts)]
+    res = []
+    for detect in (True, False):
+        out = torch.empty((ng, 128, 512), dtype=torch.bfloat16, device=DEV)
+        lse = torch.empty((ng, 128), dtype=torch.float32, device=DEV)
+        api.dsv4_status(reset=True)
+        api.dsv4_masked_mla_bf16_out(*dev, synth.SM_SCALE, heads, out, lse, None, detect_runs=detect)
+        torch.cuda.synchronize()
+        assert api.dsv4_status()[3] == 0, "the range kernel must have returned at its gate"
+        res.append((out, lse))
+    assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1], res[1][1])
