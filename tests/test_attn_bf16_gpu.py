@@ -338,3 +338,24 @@ def test_dsv4_one_scattered_list_sends_the_whole_call_to_the_gather_kernel():
         assert api.dsv4_status()[3] == 0, "the range kernel must have returned at its gate"
         res.append((out, lse))
     assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1], res[1][1])
+
+
+def test_dsv4_two_run_lists_in_place_padded_heads():
+    # rank mode of the range kernel with q / out addressed inside [T, 64, d] / [T, 64, 512]
+    ng, heads, hpad, topk, s_kv, d = 6, 16, 64, 320, 4096, 512
+    q, kv, idx, pref, wlo, whi, counts, sk = _two_run_case(ng, heads, topk, s_kv, d, seed=31, sink=True)
+    G = 128 // heads
+    args = (kv.to(DEV), idx.to(DEV), pref.to(DEV), wlo.to(DEV), whi.to(DEV), counts.to(DEV), synth.SM_SCALE, heads)
+    out_p = torch.empty((ng, 128, 512), dtype=torch.bfloat16, device=DEV)
+    lse_p = torch.empty((ng, 128), dtype=torch.float32, device=DEV)
+    api.dsv4_status(reset=True)
+    api.dsv4_masked_mla_bf16_out(q.to(DEV), *args, out_p, lse_p, sk.to(DEV))
+    q_pad = torch.randn((ng * G, hpad, d), dtype=torch.bfloat16, device=DEV)
+    q_pad[:, :heads] = q.view(ng * G, heads, d).to(DEV)
+    out_pad = torch.full((ng * G, hpad, 512), 7.0, dtype=torch.bfloat16, device=DEV)
+    lse_i = torch.empty((ng, 128), dtype=torch.float32, device=DEV)
+    api.dsv4_masked_mla_bf16_out(q_pad, *args, out_pad, lse_i, sk.to(DEV), in_place_heads=True)
+    torch.cuda.synchronize()
+    assert api.dsv4_status()[0] == 0 and api.dsv4_status()[3] == 2      # both calls ran in the range kernel
+    assert torch.equal(out_pad[:, :heads].reshape(ng, 128, 512), out_p) and torch.equal(lse_i, lse_p)
+    assert bool((out_pad[:, heads:] == 7.0).all())
