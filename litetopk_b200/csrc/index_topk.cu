@@ -686,18 +686,23 @@ topk_select_stream_kernel(const SelParams p) {
     float t_lo = -INFINITY;
     if (n > kSurvCap / 2) t_lo = sampled_threshold<NT>(sh, red_a, red_b, smp, n, p.k);
 
-    // ---- 2. filter: count the thread's survivors, block-wide exclusive scan
-    uint32_t nsel = 0;
+    // ---- 2. filter: one 4-bit mask per quad (kept for the extraction below), survivor count,
+    // block-wide exclusive scan
+    unsigned long long selm = 0ull;
 #pragma unroll
     for (int q = 0; q < NQ; ++q) {
+      uint32_t m4;
       if (q < nfull) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c) nsel += vr[4 * q + c] >= t_lo;
+        m4 = (uint32_t)(vr[4 * q] >= t_lo) | ((uint32_t)(vr[4 * q + 1] >= t_lo) << 1) |
+             ((uint32_t)(vr[4 * q + 2] >= t_lo) << 2) | ((uint32_t)(vr[4 * q + 3] >= t_lo) << 3);
       } else {
+        m4 = 0;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) nsel += live(q, c) && vr[4 * q + c] >= t_lo;
+        for (int c = 0; c < 4; ++c) m4 |= (uint32_t)(live(q, c) && vr[4 * q + c] >= t_lo) << c;
       }
+      selm |= (unsigned long long)m4 << (4 * q);
     }
+    const uint32_t nsel = __popcll(selm);
     uint32_t slot = 0, m_s = 0;
     {
       const uint32_t cnt = nsel;
@@ -722,17 +727,19 @@ topk_select_stream_kernel(const SelParams p) {
     if (m_s < (uint32_t)p.k || m_s > (uint32_t)kSurvCap) fast = false;   // too few (threshold too high) / too many
 
     if (fast) {
-      // ---- 3. survivors: values and positions out of the registers into shared memory
+      // ---- 3. survivors: values and positions out of the registers into shared memory; about
+      // one element in ten survives, so most quads are skipped on their mask nibble
 #pragma unroll
       for (int q = 0; q < NQ; ++q) {
+        const uint32_t m4 = (uint32_t)(selm >> (4 * q)) & 15u;
+        if (m4) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const bool keep = (q < nfull || live(q, c)) && vr[4 * q + c] >= t_lo;
-          if (keep) {
-            sval[slot] = vr[4 * q + c];
-            spos[slot] = (uint16_t)(4 * (q * NT + tid) + c);
-            ++slot;
-          }
+          for (int c = 0; c < 4; ++c)
+            if (m4 & (1u << c)) {
+              sval[slot] = vr[4 * q + c];
+              spos[slot] = (uint16_t)(4 * (q * NT + tid) + c);
+              ++slot;
+            }
         }
       }
       __syncthreads();
