@@ -710,6 +710,29 @@ def _host_workspace(device, T: int, h: int, k: int, q_dtype, idx_dtype):
     return ws
 
 
+def _chunk_schedule(T: int, chunk: int, G: int):
+    """Token bounds of the pipelined chunks: full chunks in the middle, a quarter and a half
+    chunk at either end.  The first upload and the last download are the two copies nothing
+    overlaps, so they are kept short."""
+    ramp = [max(G, chunk // 4 // G * G), max(G, chunk // 2 // G * G)]
+    if T < 4 * chunk:
+        ramp = []
+    head = sum(ramp)
+    bounds = [0]
+    for r in ramp:
+        bounds.append(bounds[-1] + r)
+    tail_start = T - head
+    while bounds[-1] + chunk <= tail_start:
+        bounds.append(bounds[-1] + chunk)
+    if bounds[-1] < tail_start:
+        bounds.append(tail_start)
+    for r in reversed(ramp):
+        bounds.append(bounds[-1] + r)
+    if not ramp and bounds[-1] != T:
+        bounds.append(T)
+    return bounds
+
+
 def sparse_prefill_host(q_host: torch.Tensor, kv_cache_fp8: torch.Tensor, topk_host: torch.Tensor,
                         sm_scale: float, *, out_host: Optional[torch.Tensor] = None,
                         lse_host: Optional[torch.Tensor] = None, kv_scale: Optional[float] = None,
@@ -721,7 +744,8 @@ def sparse_prefill_host(q_host: torch.Tensor, kv_cache_fp8: torch.Tensor, topk_h
     ``kv_cache_fp8`` is resident on the device.  The tokens are cut into tile-aligned chunks
     and pipelined over three streams: the upload of chunk i+1, the kernels of chunk i (on
     the caller's current stream) and the download of chunk i-1 run concurrently, so a step
-    costs about max(upload, download) instead of their sum plus the kernels.  Results are
+    costs about max(upload, download) instead of their sum plus the kernels (the first and
+    the last chunks are shorter: their upload / download is not overlapped).  Results are
     written to ``out_host`` [T,h,512] bf16 and ``lse_host`` [T,h] f32 (allocated pinned when
     not given); they are complete once the caller's current stream has been synchronised.
     The device staging buffers are cached per shape (see :func:`_host_workspace`); calls on
@@ -759,8 +783,8 @@ def sparse_prefill_host(q_host: torch.Tensor, kv_cache_fp8: torch.Tensor, topk_h
         s_in, s_out = _side_streams(dev)
         s_in.wait_stream(cur)      # earlier kernels may still read the staging buffers
         s_out.wait_stream(cur)
-        for t0 in range(0, T, chunk):
-            t1 = min(T, t0 + chunk)
+        bounds = _chunk_schedule(T, chunk, G)
+        for t0, t1 in zip(bounds[:-1], bounds[1:]):
             with torch.cuda.stream(s_in):
                 qd[t0:t1].copy_(q_host[t0:t1], non_blocking=True)
                 idd[t0:t1].copy_(topk_host[t0:t1], non_blocking=True)

@@ -129,3 +129,17 @@ def test_entry_points_reject_bad_arguments_before_any_cuda_call(built_lib):
                                      576, 576, 576, 0, 0, 0, 0, None) == SHAPE
     assert L.litedsa_dsv4_c128a_bf16(P, None, P, 1, 48, 0, 64, 0, 128, 128, 0.1, None, P, P,
                                      576, 576, 576, 0, 0, 0, 0, None) == SHAPE
+
+
+def test_host_pipeline_chunk_schedule():
+    """Chunks of sparse_prefill_host: cover [0, T) once, tile-aligned cuts, short first / last chunk."""
+    from litetopk_b200.api import _chunk_schedule
+    for T, chunk, G in [(8192, 512, 2), (8192, 512, 8), (100, 512, 2), (2048, 512, 2), (2050, 512, 2),
+                        (2046, 512, 2), (4100, 512, 4), (1, 512, 1), (3000, 512, 8), (65536, 512, 8)]:
+        b = _chunk_schedule(T, chunk, G)
+        assert b[0] == 0 and b[-1] == T
+        assert all(x < y for x, y in zip(b, b[1:]))
+        assert all(x % G == 0 for x in b[:-1])
+        assert max(y - x for x, y in zip(b, b[1:])) <= chunk
+        if T >= 4 * chunk:
+            assert b[1] - b[0] <= chunk // 4 and b[-1] - b[-2] <= chunk // 4
