@@ -288,6 +288,23 @@ int litedsa_masked_mla_bf16(const void* q, const void* kv, const int32_t* indice
 int litedsa_dequant_kv656(const void* kv656, void* kv_bf16, int s_kv, int64_t out_pitch,
                           void* stream);
 
+/*
+ * Merge of KV-split attention outputs: the q_group_div consecutive tiles that shared one Q tile
+ * in litedsa_masked_mla_fp8_ex are combined with their lse into the attention over the whole
+ * union list.  The reference carries q_group_div in its kernel and leaves the merge to the
+ * caller (kernels/b200/dsa/litedsa_attention_sm100.cuh:1383-1385, 1909).
+ *
+ *   out_parts [ng, 128, 512] bf16, lse_parts [ng, 128] fp32 (+inf = a part without keys),
+ *   max_parts [ng, 128] or NULL; attn_sink [128] or NULL: the array the attention call got
+ *   (a part is normalised by its own row sum plus the sink, lse excludes the sink);
+ *   out [ng / q_group_div, 128, 512] bf16, lse [ng / q_group_div, 128], max_logits likewise
+ *   or NULL (given exactly when max_parts is).  q_group_div <= 32; out_parts and out 16-byte
+ *   aligned.  A row all of whose parts are empty gets out = 0, lse = +inf.
+ */
+int litedsa_merge_kv_splits(const void* out_parts, const float* lse_parts, const float* max_parts,
+                            const float* attn_sink, void* out, float* lse, float* max_logits,
+                            int ng, int q_group_div, void* stream);
+
 /* Status block of the bf16 gather kernel; same meaning and use as litedsa_attn_status. */
 int litedsa_bf16_status(int* out4_host, int reset);
 

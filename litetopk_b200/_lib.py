@@ -56,6 +56,8 @@ SIGNATURES = {
                                         c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                         c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "litedsa_dequant_kv656": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_void_p]),
+    "litedsa_merge_kv_splits": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                        c_void_p, c_int, c_int, c_void_p]),
     "litedsa_bf16_status": (c_int, [c_void_p, c_int]),
     "litedsa_probe_mma_tflops": (c_int, [c_int, c_int, c_int, c_void_p]),
     "litedsa_index_logits_fp8": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,

@@ -577,6 +577,53 @@ def dequant_kv656(kv_rows: torch.Tensor, out: Optional[torch.Tensor] = None) -> 
     return out
 
 
+def merge_kv_splits(out_parts: torch.Tensor, lse_parts: torch.Tensor, q_group_div: int, *,
+                    max_parts: Optional[torch.Tensor] = None,
+                    attn_sink: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                    lse: Optional[torch.Tensor] = None):
+    """Combine the outputs of ``q_group_div`` consecutive tiles that shared one Q tile
+    (:func:`masked_mla_fp8_out` with ``q_group_div > 1``: slices of one long union list) into
+    the attention over the whole list.
+
+    ``out_parts`` [ng,128,512] bf16, ``lse_parts`` [ng,128] f32 (+inf marks a slice without
+    keys), ``max_parts`` [ng,128] optional, ``attn_sink`` [128] f32: the array the attention
+    call got.  Returns ``(out [ng/div,128,512] bf16, lse [ng/div,128] f32)`` and, with
+    ``max_parts``, the merged ``max_logits``.  The reference leaves this step to its callers
+    (kernels/b200/dsa/litedsa_attention_sm100.cuh:1383-1385).
+    """
+    _need(out_parts, "out_parts", torch.bfloat16, 3)
+    _need(lse_parts, "lse_parts", torch.float32, 2)
+    ng = out_parts.shape[0]
+    div = int(q_group_div)
+    if tuple(out_parts.shape) != (ng, 128, 512) or tuple(lse_parts.shape) != (ng, 128) \
+            or not out_parts.is_contiguous() or not lse_parts.is_contiguous():
+        raise ValueError("out_parts must be contiguous [ng,128,512] bf16 and lse_parts [ng,128] f32")
+    if div < 1 or ng % div:
+        raise ValueError("q_group_div must divide the number of tiles")
+    dev = out_parts.device
+    for name, t in (("max_parts", max_parts), ("attn_sink", attn_sink)):
+        if t is not None:
+            _need(t, name, torch.float32, 2 if name == "max_parts" else 1)
+            if t.device != dev or not t.is_contiguous() or \
+                    tuple(t.shape) != ((ng, 128) if name == "max_parts" else (128,)):
+                raise ValueError(f"{name} has the wrong shape, layout or device")
+    nm = ng // div
+    if out is None:
+        out = torch.empty((nm, 128, 512), dtype=torch.bfloat16, device=dev)
+    if lse is None:
+        lse = torch.empty((nm, 128), dtype=torch.float32, device=dev)
+    if tuple(out.shape) != (nm, 128, 512) or out.dtype != torch.bfloat16 or not out.is_contiguous() \
+            or tuple(lse.shape) != (nm, 128) or lse.dtype != torch.float32 or not lse.is_contiguous() \
+            or out.device != dev or lse.device != dev:
+        raise ValueError("out must be contiguous [ng/div,128,512] bf16 and lse [ng/div,128] f32")
+    mx = torch.empty((nm, 128), dtype=torch.float32, device=dev) if max_parts is not None else None
+    with torch.cuda.device(dev):
+        check(_lib.lib().litedsa_merge_kv_splits(_ptr(out_parts), _ptr(lse_parts), _ptr(max_parts),
+                                                 _ptr(attn_sink), _ptr(out), _ptr(lse), _ptr(mx),
+                                                 ng, div, _stream(out_parts)), "merge_kv_splits")
+    return (out, lse, mx) if max_parts is not None else (out, lse)
+
+
 def prepare_kv(kv_cache_fp8: torch.Tensor, kv_scale: Optional[float] = None,
                *, check_scales: bool = False) -> torch.Tensor:
     """Bring a KV cache into the form one of the attention kernels gathers from.

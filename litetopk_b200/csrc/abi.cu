@@ -14,7 +14,7 @@ int next_launch_epoch() {
 unsigned long long wait_limit_ns() { return g_wait_limit_ns.load(std::memory_order_relaxed); }
 }  // namespace lt
 
-extern "C" int litedsa_abi_version(void) { return 3; }
+extern "C" int litedsa_abi_version(void) { return 4; }
 
 // Limit of a single device-side wait for all later launches of this process (0 = the
 // default of 2 s).  Returns the previous value through *previous_ns when given.

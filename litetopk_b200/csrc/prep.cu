@@ -61,6 +61,71 @@ __global__ void __launch_bounds__(256) repack_kv656_kernel(const uint8_t* __rest
   }
 }
 
+// KV-split merge: the outputs of q_group_div consecutive tiles that share one Q tile (slices of
+// one long union list) are combined with their lse into the attention over the whole list.
+// One warp per merged row; lane j holds part j's lse, lane i the dims [8i, 8i + 8) and
+// [256 + 8i, 256 + 8i + 8) of the row (two fully coalesced 512-byte requests per part).
+// Part j of row (t, r) weighs (e^lse_j + e^sink_r) / (sum_k e^lse_k + e^sink_r): the kernels
+// normalise a part by its own row sum plus the sink, while lse never contains the sink.
+__global__ void __launch_bounds__(256) merge_kv_splits_kernel(
+    const uint4* __restrict__ out_parts, const float* __restrict__ lse_parts,
+    const float* __restrict__ max_parts, const float* __restrict__ sink, uint4* __restrict__ out,
+    float* __restrict__ lse, float* __restrict__ max_logits, int n_rows, int div) {
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  for (int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < n_rows; row += warps) {
+    const int t = row >> 7, r = row & 127;
+    const size_t prow0 = ((size_t)t * div) * 128 + r;          // part j: prow0 + 128 j
+    float lj = -INFINITY, mj = -INFINITY;
+    if (lane < div) {
+      const float v = __ldcs(lse_parts + prow0 + (size_t)lane * 128);
+      lj = (v == INFINITY || v != v) ? -INFINITY : v;          // +inf marks a part without keys
+      if (max_parts) mj = __ldcs(max_parts + prow0 + (size_t)lane * 128);
+    }
+    float m = lj;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+      mj = fmaxf(mj, __shfl_xor_sync(0xffffffffu, mj, off));
+    }
+    const float e = lj == -INFINITY ? 0.f : __expf(lj - m);
+    float sum = e;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    const float es = (sink && m != -INFINITY) ? __expf(__ldg(sink + r) - m) : 0.f;
+    const float w = e > 0.f ? __fdividef(e + es, sum + es) : 0.f;
+    float acc[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+    for (int j = 0; j < div; ++j) {
+      const float wj = __shfl_sync(0xffffffffu, w, j);
+      if (wj == 0.f) continue;                                  // warp-uniform
+      const uint4* src = out_parts + (prow0 + (size_t)j * 128) * 64;
+      const uint4 a = __ldcs(src + lane), b = __ldcs(src + 32 + lane);
+      const uint32_t u[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u[i]));
+        acc[2 * i] = fmaf(wj, f.x, acc[2 * i]);
+        acc[2 * i + 1] = fmaf(wj, f.y, acc[2 * i + 1]);
+      }
+    }
+    uint32_t o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const __nv_bfloat162 v = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+      o[i] = *reinterpret_cast<const uint32_t*>(&v);
+    }
+    uint4* dst = out + (size_t)row * 64;
+    __stcs(dst + lane, make_uint4(o[0], o[1], o[2], o[3]));
+    __stcs(dst + 32 + lane, make_uint4(o[4], o[5], o[6], o[7]));
+    if (lane == 0) {
+      lse[row] = m == -INFINITY ? INFINITY : m + __logf(sum);
+      if (max_logits) max_logits[row] = mj;
+    }
+  }
+}
+
 }  // namespace lt
 
 // bf16 -> e4m3 with a scalar scale: out = e4m3(in / scale).  n must be a multiple of 8 and
@@ -91,5 +156,28 @@ extern "C" int litedsa_repack_kv656(const void* kv656, void* kv576, int s_kv, in
   repack_kv656_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const uint8_t*>(kv656), reinterpret_cast<uint8_t*>(kv576), s_kv, out_pitch,
       scale, mismatch_flag);
+  return cudaGetLastError() == cudaSuccess ? LITEDSA_OK : LITEDSA_ERR_CUDA;
+}
+
+// Merge of KV-split outputs (see merge_kv_splits_kernel).  out_parts [ng, 128, 512] bf16 and
+// lse_parts [ng, 128] are what litedsa_masked_mla_fp8_ex wrote with q_group_div > 1; out
+// [ng / q_group_div, 128, 512] bf16, lse [ng / q_group_div, 128].  max_parts / max_logits and
+// attn_sink ([128], natural-log units, the same array the attention call got) are optional.
+// The reference leaves this step to its callers (litedsa_attention_sm100.cuh:1383-1385).
+extern "C" int litedsa_merge_kv_splits(const void* out_parts, const float* lse_parts,
+                                       const float* max_parts, const float* attn_sink, void* out,
+                                       float* lse, float* max_logits, int ng, int q_group_div,
+                                       void* stream) {
+  using namespace lt;
+  if (!out_parts || !lse_parts || !out || !lse) return LITEDSA_ERR_ARG;
+  if ((max_parts == nullptr) != (max_logits == nullptr)) return LITEDSA_ERR_ARG;
+  if (ng <= 0 || q_group_div < 1 || ng % q_group_div) return LITEDSA_ERR_SHAPE;
+  if (q_group_div > 32) return LITEDSA_ERR_UNSUPPORTED;
+  if (((uintptr_t)out_parts | (uintptr_t)out) & 15) return LITEDSA_ERR_UNSUPPORTED;
+  const int n_rows = ng / q_group_div * 128;
+  const int blocks = min(148 * 8, (n_rows + 7) / 8);
+  merge_kv_splits_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint4*>(out_parts), lse_parts, max_parts, attn_sink,
+      reinterpret_cast<uint4*>(out), lse, max_logits, n_rows, q_group_div);
   return cudaGetLastError() == cudaSuccess ? LITEDSA_OK : LITEDSA_ERR_CUDA;
 }

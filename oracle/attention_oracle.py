@@ -326,6 +326,33 @@ def dsv4_exact(q: torch.Tensor, kv_comp: torch.Tensor, kv_raw: torch.Tensor, pos
     return out, lse
 
 
+def merge_kv_splits_exact(out_parts: torch.Tensor, lse_parts: torch.Tensor, div: int,
+                          max_parts: Optional[torch.Tensor] = None,
+                          sink: Optional[torch.Tensor] = None):
+    """fp64 merge of KV-split outputs: ``div`` consecutive tiles share one Q tile; a part with
+    lse = +inf holds no keys.  A part was normalised by its own row sum plus e^sink (lse excludes
+    the sink), so part j weighs (e^lse_j + e^sink) / (sum_k e^lse_k + e^sink).  The reference
+    leaves the merge to its callers (kernels/b200/dsa/litedsa_attention_sm100.cuh:1383-1385).
+    Returns (out [ng/div,128,512] f64, lse [ng/div,128] f64, max or None)."""
+    ng = out_parts.shape[0]
+    o = out_parts.double().view(ng // div, div, 128, -1)
+    l = lse_parts.double().view(ng // div, div, 128)
+    lf = torch.where(torch.isinf(l) & (l > 0), torch.full_like(l, -float("inf")), l)
+    m = lf.max(dim=1, keepdim=True).values
+    msafe = torch.where(torch.isinf(m), torch.zeros_like(m), m)
+    e = torch.exp(lf - msafe)                                   # 0 for empty parts
+    tot = e.sum(dim=1, keepdim=True)
+    es = torch.zeros_like(tot)
+    if sink is not None:
+        es = torch.exp(sink.double().view(1, 1, 128) - msafe) * (~torch.isinf(m))
+    w = torch.where(e > 0, (e + es) / (tot + es).clamp_min(1e-300), torch.zeros_like(e))
+    out = (o * w[..., None]).sum(dim=1)
+    lse = torch.where(tot.squeeze(1) > 0, msafe.squeeze(1) + torch.log(tot.squeeze(1).clamp_min(1e-300)),
+                      torch.full_like(tot.squeeze(1), float("inf")))
+    mx = None if max_parts is None else max_parts.double().view(ng // div, div, 128).max(dim=1).values
+    return out, lse, mx
+
+
 def compare(out: torch.Tensor, ref: torch.Tensor):
     """(max-abs difference, cosine similarity) of two tensors, computed in fp64."""
     a, b = out.double().flatten(), ref.double().flatten()

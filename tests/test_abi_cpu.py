@@ -117,6 +117,14 @@ def test_entry_points_reject_bad_arguments_before_any_cuda_call(built_lib):
     assert L.litedsa_masked_mla_bf16(P, P, P, 0.1, None, P, 64, P, None, P,
                                      2, 128, 64, 576, 576, 576, 64, None, None) == SHAPE
     assert L.litedsa_dequant_kv656(P, P, 16, 1000, None) == SHAPE
+    # KV-split merge: null output, max arrays given on one side only, div not dividing ng, div > 32,
+    # misaligned rows
+    mg = L.litedsa_merge_kv_splits
+    assert mg(P, P, None, None, None, P, None, 4, 2, None) == ARG
+    assert mg(P, P, P, None, P, P, None, 4, 2, None) == ARG
+    assert mg(P, P, None, None, P, P, None, 5, 2, None) == SHAPE
+    assert mg(P, P, None, None, P, P, None, 66, 33, None) == UNSUP
+    assert mg(P + 8, P, None, None, P, P, None, 4, 2, None) == UNSUP
     # multi-destination form: destination count out of range, null destination
     outs = (ctypes.c_void_p * 9)(*([P] * 9))
     assert L.litedsa_masked_mla_fp8_multi(P, P, P, ok["sm"], ok["os"], None, P, 64, outs, 9, None, P,

@@ -259,6 +259,51 @@ def test_q_group_div_kv_split_merges_to_the_unsplit_result():
     # (relative 2^-4 per element), so this semantic check is looser than the parity check above
     mad, cos = ao.compare(merged, ref[0])
     assert mad <= 0.1 and cos >= 0.9995, (mad, cos)
+    # the library's merge kernel does the same on the device
+    om, lm, mm = api.merge_kv_splits(out.view(ng * 2, 128, 512), lse.view(ng * 2, 128), 2,
+                                     max_parts=ml.view(ng * 2, 128))
+    want_o, want_l, want_m = ao.merge_kv_splits_exact(out.cpu().view(ng * 2, 128, 512),
+                                                      lse.cpu().view(ng * 2, 128), 2,
+                                                      max_parts=ml.cpu().view(ng * 2, 128))
+    assert float((om.cpu().double() - want_o).abs().max()) <= 2.0 ** -8 * float(want_o.abs().max()) + 1e-6
+    assert float((lm.cpu().double() - want_l).abs().max()) <= 1e-5
+    assert torch.equal(mm.cpu().double(), want_m)
+    mad, cos = ao.compare(om.cpu().float(), ref[0])
+    assert mad <= 0.1 and cos >= 0.9995, (mad, cos)
+
+
+@pytest.mark.parametrize("div,with_sink", [(1, False), (2, True), (3, False), (8, True), (32, False)])
+def test_merge_kv_splits_matches_the_exact_merge(div, with_sink):
+    # random slices, some of them empty (out 0, lse +inf, max -inf), rows with every slice empty
+    g = torch.Generator().manual_seed(100 + div)
+    nm = 5
+    ng = nm * div
+    outp = (torch.randn(ng, 128, 512, generator=g) * 2).to(torch.bfloat16)
+    lsep = torch.randn(ng, 128, generator=g) * 4
+    maxp = torch.randn(ng, 128, generator=g)
+    empty = torch.rand(ng, 128, generator=g) < 0.25
+    empty.view(nm, div, 128)[0, :, :7] = True                      # rows without any key
+    outp[empty] = 0
+    lsep[empty] = float("inf")
+    maxp[empty] = -float("inf")
+    sink = torch.randn(128, generator=g) if with_sink else None
+    want_o, want_l, want_m = ao.merge_kv_splits_exact(outp, lsep, div, max_parts=maxp, sink=sink)
+    got = api.merge_kv_splits(outp.to(DEV), lsep.to(DEV), div, max_parts=maxp.to(DEV),
+                              attn_sink=None if sink is None else sink.to(DEV))
+    o, l, m = [t.cpu().double() for t in got]
+    tol = 2.0 ** -8 * float(want_o.abs().max()) + 1e-6              # one bf16 rounding of the result
+    assert float((o - want_o).abs().max()) <= tol
+    assert torch.equal(torch.isinf(l), torch.isinf(want_l))
+    fin = ~torch.isinf(want_l)
+    assert float((l[fin] - want_l[fin]).abs().max()) <= 1e-5
+    assert torch.equal(m, want_m)
+    assert float(o[0, :7].abs().max()) == 0.0
+    # without the optional arrays: two results, same values
+    o2, l2 = api.merge_kv_splits(outp.to(DEV), lsep.to(DEV), div,
+                                 attn_sink=None if sink is None else sink.to(DEV))
+    assert torch.equal(o2, got[0]) and torch.equal(l2.cpu().double()[fin], l[fin])
+    with pytest.raises(ValueError):
+        api.merge_kv_splits(outp.to(DEV), lsep.to(DEV), div + 1 if ng % (div + 1) else 7)
 
 
 def test_bounded_wait_gives_up_reports_and_later_launches_are_unaffected():

@@ -139,3 +139,37 @@ def test_dsv4_exact_matches_dense_reference():
         w_ = torch.softmax(s, dim=1)
         assert (out[t] - w_ @ keys[:, :32]).abs().max() < 1e-12
         assert (lse[t] - torch.logsumexp(s, dim=1)).abs().max() < 1e-12
+
+
+def test_merge_kv_splits_oracle_equals_unsplit_softmax():
+    # attention of 128 rows over 96 keys, computed whole and as three slices (one of them empty,
+    # one seeing a key subset per row) merged with their lse; with and without a sink
+    g = torch.Generator().manual_seed(5)
+    rows, dims = 128, 512
+    s = torch.randn(rows, 96, generator=g, dtype=torch.float64) * 3
+    v = torch.randn(96, dims, generator=g, dtype=torch.float64)
+    sink = torch.randn(rows, generator=g, dtype=torch.float64)
+    bounds = [(0, 40), (40, 40), (40, 96)]                      # the middle slice is empty
+    for use_sink in (False, True):
+        es = torch.exp(sink) if use_sink else torch.zeros(rows, dtype=torch.float64)
+        whole = (torch.exp(s) @ v) / (torch.exp(s).sum(1) + es)[:, None]
+        whole_lse = torch.log(torch.exp(s).sum(1))
+        outs, lses = [], []
+        for a, b in bounds:
+            if a == b:
+                outs.append(torch.zeros(rows, dims, dtype=torch.float64))
+                lses.append(torch.full((rows,), float("inf"), dtype=torch.float64))
+                continue
+            p = torch.exp(s[:, a:b])
+            outs.append((p @ v[a:b]) / (p.sum(1) + es)[:, None])
+            lses.append(torch.log(p.sum(1)))
+        maxes = torch.stack([torch.where(torch.isinf(x), -x, x) for x in lses])   # empty: -inf
+        o, l, mx = ao.merge_kv_splits_exact(torch.stack(outs), torch.stack(lses), 3,
+                                            max_parts=maxes,
+                                            sink=sink if use_sink else None)
+        assert torch.allclose(o[0], whole, rtol=1e-10, atol=1e-12)
+        assert torch.allclose(l[0], whole_lse, rtol=1e-12, atol=1e-12)
+        assert torch.equal(mx[0], torch.stack([lses[0], lses[2]]).max(0).values)
+    # every part empty: out 0, lse +inf
+    o, l, _ = ao.merge_kv_splits_exact(torch.zeros(2, 128, 512), torch.full((2, 128), float("inf")), 2)
+    assert float(o.abs().max()) == 0.0 and bool(torch.isinf(l).all())
