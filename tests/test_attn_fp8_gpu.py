@@ -367,3 +367,53 @@ def test_in_place_padded_heads_equal_the_packed_path_bit_for_bit(heads, hpad):
     assert torch.equal(out_pad[:, :heads].reshape(ng, 128, 512), out_p) and torch.equal(lse_i, lse_p)
     assert bool((out_pad[:, heads:] == 7.0).all())            # the padding slots are never written
     _check(out_p, lse_p, None, ref)
+
+
+def test_out_operators_replay_from_a_cuda_graph():
+    # union_qm_out + masked_mla_fp8_out allocate nothing and never synchronise, so a caller can
+    # capture them in a CUDA graph; replays on new inputs in the same buffers give the same
+    # result as direct calls
+    w, idx, kv, q = _case(64, 64, 256, 2048, (0.8, 0.8), seed=21)
+    _, idx_b, _, q_b = _case(64, 64, 256, 2048, (0.8, 0.8), seed=22)
+    _, _, (q8, kv8, qs, ks) = _oracle(w, idx, kv, q)
+    q8_b = synth.refcompat_operands(q_b, kv)[0]
+    ng, cap, G = w.tiles, w.cap, w.group
+    d_idx = idx.to(DEV).clone()
+    d_q = q8.view(ng, 128, 576).to(DEV).clone()
+    d_kv = kv8.to(DEV)
+    u = torch.empty((ng, cap), dtype=torch.int32, device=DEV)
+    c = torch.empty((ng,), dtype=torch.int32, device=DEV)
+    m = torch.empty((ng, G, cap // 32), dtype=torch.int32, device=DEV)
+    out = torch.empty((ng, 128, 512), dtype=torch.bfloat16, device=DEV)
+    lse = torch.empty((ng, 128), dtype=torch.float32, device=DEV)
+    sm = synth.SM_SCALE * qs * ks
+
+    def step():
+        api.union_qm_out(d_idx, u, c, m, None, None, 1, w.s_kv)
+        api.masked_mla_fp8_out(d_q, d_kv, u, sm, ks, c, m, w.heads, out, None, lse)
+
+    def direct(i_host, q_host):
+        d_idx.copy_(i_host); d_q.copy_(q_host.view(ng, 128, 576))
+        step()
+        torch.cuda.synchronize()
+        return out.clone(), lse.clone()
+
+    want_a = direct(idx, q8)
+    want_b = direct(idx_b, q8_b)
+    assert not torch.equal(want_a[0], want_b[0])
+    side = torch.cuda.Stream(device=DEV)
+    side.wait_stream(torch.cuda.current_stream(DEV))
+    with torch.cuda.stream(side):
+        step()                                  # warm-up on the capture stream
+    torch.cuda.current_stream(DEV).wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    for i_host, q_host, want in ((idx, q8, want_a), (idx_b, q8_b, want_b), (idx, q8, want_a)):
+        d_idx.copy_(i_host); d_q.copy_(q_host.view(ng, 128, 576))
+        out.zero_(); lse.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, want[0]) and torch.equal(lse, want[1])
+    assert api.attn_status()[0] == 0
