@@ -359,3 +359,47 @@ def test_dsv4_two_run_lists_in_place_padded_heads():
     assert api.dsv4_status()[0] == 0 and api.dsv4_status()[3] == 2      # both calls ran in the range kernel
     assert torch.equal(out_pad[:, :heads].reshape(ng, 128, 512), out_p) and torch.equal(lse_i, lse_p)
     assert bool((out_pad[:, heads:] == 7.0).all())
+
+
+def test_dsv4_reference_signature_in_a_cuda_graph_switches_kernels_with_the_data():
+    # The list form is classified on the device and the two kernels gate themselves, so one
+    # captured graph serves two-run lists (range kernel) and scattered lists (gather kernel):
+    # replays after the index tensor changed form must match direct calls bit for bit.
+    ng, heads, topk, s_kv, d = 6, 64, 256, 4096, 512
+    q, kv, idx, pref, wlo, whi, counts, _ = _two_run_case(ng, heads, topk, s_kv, d, seed=41)
+    idx_sc, counts_sc = idx.clone(), counts.clone()
+    idx_sc[0] = -1
+    idx_sc[0, :30] = torch.cat([torch.arange(100, 110), torch.arange(200, 210), torch.arange(300, 310)]).to(torch.int32)
+    counts_sc[0] = 30
+    d_q, d_kv, d_idx, d_pref, d_wlo, d_whi, d_cnt = [t.to(DEV) for t in (q, kv, idx, pref, wlo, whi, counts)]
+    out = torch.empty((ng, 128, 512), dtype=torch.bfloat16, device=DEV)
+    lse = torch.empty((ng, 128), dtype=torch.float32, device=DEV)
+
+    def step():
+        api.dsv4_masked_mla_bf16_out(d_q, d_kv, d_idx, d_pref, d_wlo, d_whi, d_cnt, synth.SM_SCALE, heads,
+                                     out, lse, None)
+
+    def direct(i_host, c_host):
+        d_idx.copy_(i_host); d_cnt.copy_(c_host)
+        step()
+        torch.cuda.synchronize()
+        return out.clone(), lse.clone()
+
+    want_runs = direct(idx, counts)
+    want_sc = direct(idx_sc, counts_sc)
+    side = torch.cuda.Stream(device=DEV)
+    side.wait_stream(torch.cuda.current_stream(DEV))
+    with torch.cuda.stream(side):
+        step()                                  # warm-up on the capture stream (its workspace is made here)
+    torch.cuda.current_stream(DEV).wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    for i_host, c_host, want in ((idx, counts, want_runs), (idx_sc, counts_sc, want_sc), (idx, counts, want_runs)):
+        d_idx.copy_(i_host); d_cnt.copy_(c_host)
+        out.zero_(); lse.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, want[0]) and torch.equal(lse, want[1])
+    assert api.dsv4_status()[0] == 0 and api.bf16_status()[0] == 0
