@@ -798,13 +798,17 @@ __global__ void __launch_bounds__(256) dequant_kv656_kernel(const uint8_t* __res
        row += gridDim.x * warps_per_block) {
     const uint8_t* src = in + (size_t)row * 656;
     uint8_t* dst = out + (size_t)row * out_pitch;
-    // lane: 16 codes [16 lane, +16) of chunk lane / 8
-    const uint4 cd = __ldg(reinterpret_cast<const uint4*>(src) + lane);
-    const float sc = __ldg(reinterpret_cast<const float*>(src + 512) + (lane >> 3));
-    const uint32_t w[4] = {cd.x, cd.y, cd.z, cd.w};
+    // lane: codes [8 lane, +8) (chunk lane / 16) and [256 + 8 lane, +8) (chunk 2 + lane / 16):
+    // two coalesced 256-byte loads in, two coalesced 512-byte stores out
+    const uint2 c0 = __ldcs(reinterpret_cast<const uint2*>(src) + lane);
+    const uint2 c1 = __ldcs(reinterpret_cast<const uint2*>(src) + 32 + lane);
+    const float s0 = __ldg(reinterpret_cast<const float*>(src + 512) + (lane >> 4));
+    const float s1 = __ldg(reinterpret_cast<const float*>(src + 512) + 2 + (lane >> 4));
+    const uint32_t w[4] = {c0.x, c0.y, c1.x, c1.y};
     uint32_t o[8];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
+      const float sc = j < 2 ? s0 : s1;
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
         const __nv_fp8x2_storage_t two = (__nv_fp8x2_storage_t)((w[j] >> (16 * hh)) & 0xffffu);
@@ -814,12 +818,12 @@ __global__ void __launch_bounds__(256) dequant_kv656_kernel(const uint8_t* __res
         o[2 * j + hh] = *reinterpret_cast<uint32_t*>(&b2);
       }
     }
-    uint4* d4 = reinterpret_cast<uint4*>(dst) + 2 * lane;
-    d4[0] = make_uint4(o[0], o[1], o[2], o[3]);
-    d4[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+    d4[lane] = make_uint4(o[0], o[1], o[2], o[3]);
+    d4[32 + lane] = make_uint4(o[4], o[5], o[6], o[7]);
     // rope: 128 bytes = 8 x 16
     if (lane < 8)
-      reinterpret_cast<uint4*>(dst + 1024)[lane] = __ldg(reinterpret_cast<const uint4*>(src + 528) + lane);
+      reinterpret_cast<uint4*>(dst + 1024)[lane] = __ldcs(reinterpret_cast<const uint4*>(src + 528) + lane);
   }
 }
 
