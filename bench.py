@@ -18,6 +18,8 @@ The ONE JSON line rank 0 prints carries, beside the headline contract keys:
                   process (the product process never maps the checker)
   configs         secondary records for configs 2, 3 and 4 (N = 1 only)
   native          config 1 on a cache whose per-128 scales differ, bf16 q (the bf16 route)
+  indexer         the step before: FP8 index logits + exact top-k selection on the config-1 shape
+  merge_kv_splits the lse merge of KV-split outputs (HBM-bound)
   c4_strong       config 4 split over the N ranks (strong scaling) with its all-gather
   e2e             through api.sparse_prefill_host with pinned host buffers and bf16 queries:
                   median step of a window, the better of two windows (both arms alike; the
@@ -584,6 +586,20 @@ def indexer_record(api, w, dev, steps, fp8_peak, hbm_gbs, index_heads=64):
     return rec
 
 
+def merge_record(api, dev, steps, hbm_gbs, part_tiles=8192, div=2):
+    """The lse merge of KV-split outputs (HBM-bound): `part_tiles` slices of 128 rows merged `div` to one."""
+    o = torch.randn((part_tiles, 128, 512), device=dev).to(torch.bfloat16)
+    lsep = torch.randn((part_tiles, 128), device=dev)
+    out = torch.empty((part_tiles // div, 128, 512), dtype=torch.bfloat16, device=dev)
+    lse = torch.empty((part_tiles // div, 128), dtype=torch.float32, device=dev)
+    ms = cuda_time(lambda: api.merge_kv_splits(o, lsep, div, out=out, lse=lse), steps)
+    nbytes = o.numel() * 2 + lsep.numel() * 4 + out.numel() * 2 + lse.numel() * 4
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    del o, lsep, out, lse
+    return {"workload": f"{part_tiles} part tiles, q_group_div {div}", "ms": ms, "gbs": gbs,
+            "frac": gbs / hbm_gbs, "peak_gbs": hbm_gbs, "bytes": nbytes}
+
+
 def host_copy_bandwidth(dev, mb=256):
     """Plain pinned-memory copy rates of this rank (GB/s): the bound of the end-to-end leg."""
     n = mb << 20
@@ -995,6 +1011,7 @@ def main():
                              "note": "config 4 on one GPU: the base of the strong-scaling curve"}
         line["native"] = native_record(api, synth.CONFIGS["c1"], dev, sec_steps, peaks["bf16_tflops"])
         line["indexer"] = indexer_record(api, synth.CONFIGS["c1"], dev, sec_steps, fp8_peak, peaks["hbm_gbs"])
+        line["merge_kv_splits"] = merge_record(api, dev, sec_steps, peaks["hbm_gbs"])
     elif extras:
         # config 4 split over the ranks (strong scaling) with the all-gather of its outputs
         w4 = synth.CONFIGS["c4"]
