@@ -357,7 +357,7 @@ masked_mla_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
     Cursor ck, cv;
     cur_init(ck);
     cur_init(cv);
-    const uint64_t pol_keep = l2_policy_evict_last(), pol_stream = l2_policy_evict_first();
+    const uint64_t pol_stream = l2_policy_evict_first();
     // lane l < 4 holds the index of own key 4pw + l (K rows), lane 8 + l (l < 8) of key
     // 8pw + l of the block's 64 keys (V rows)
     const int my_key = lane < 8 ? 32 * (int)cta + 4 * pw + (lane & 3) : 8 * pw + ((lane - 8) & 7);
@@ -409,8 +409,8 @@ masked_mla_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
             const int ri = __shfl_sync(0xffffffffu, kidx, rl);
             const int row = 4 * pw + rl;
             const int cj = pi >> 3, cc = pi & 7;
-            cp_async16_hint(kst + cj * kKChunkBytes + row * 128 + ((cc ^ (row & 7)) << 4),
-                            kvb + (size_t)ri * pitch + 16 * pi, pol_keep);
+            cp_async16(kst + cj * kKChunkBytes + row * 128 + ((cc ^ (row & 7)) << 4),
+                            kvb + (size_t)ri * pitch + 16 * pi);
           }
           cp_async_mbar_arrive_noinc(&ms.k_land[s]);
           cur_next(ck);
@@ -431,8 +431,8 @@ masked_mla_bf16_kernel(const __grid_constant__ CUtensorMap map_q,
           for (int i = 0; i < 8; ++i) {
             const int ri = __shfl_sync(0xffffffffu, vidx, 8 + i);
             const int row = 8 * pw + i;
-            cp_async16_hint(vst + cj * kVChunkBytes + row * 128 + ((cc ^ (row & 7)) << 4),
-                            kvb + (size_t)ri * pitch + 512 * (int)cta + 16 * lane, pol_keep);
+            cp_async16(vst + cj * kVChunkBytes + row * 128 + ((cc ^ (row & 7)) << 4),
+                            kvb + (size_t)ri * pitch + 512 * (int)cta + 16 * lane);
           }
           cp_async_mbar_arrive_noinc(&ms.v_land[s]);
           cur_next(cv);

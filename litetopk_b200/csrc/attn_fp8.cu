@@ -441,9 +441,9 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
     Cursor ck, cv;   // K gather, V gather
     cur_init(ck);
     cur_init(cv);
-    // the KV cache is re-read by every tile (keep it in L2); q and out stream through once, and
-    // so do the index lists and membership words (streaming loads: they must not push KV rows out)
-    const uint64_t pol_keep = l2_policy_evict_last(), pol_stream = l2_policy_evict_first();
+    // q and out stream through once (evict-first TMA traffic), and so do the index lists and
+    // membership words (streaming loads): they must not push the re-read KV rows out of L2
+    const uint64_t pol_stream = l2_policy_evict_first();
     // lane l < 16 holds the index of own key 8pw + l%8 (K tile rows), lane l >= 16 of key
     // 16pw + l - 16 of the block's 128 keys (V tile rows)
     const int my_key = lane < 16 ? 64 * (int)cta + 8 * pw + (lane & 7) : 16 * pw + (lane - 16);
@@ -499,15 +499,15 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
           for (int i = 0; i < 8; ++i) {
             const int ri = __shfl_sync(0xffffffffu, kidx, i);
             const int row = 8 * pw + i;
-            cp_async16_hint(kst + cj * kChunkBytes + row * 128 + ((cc ^ (row & 7)) << 4),
-                       kvb + (size_t)ri * pitch + 16 * lane, pol_keep);
+            cp_async16(kst + cj * kChunkBytes + row * 128 + ((cc ^ (row & 7)) << 4),
+                       kvb + (size_t)ri * pitch + 16 * lane);
           }
           {
             const int ri = __shfl_sync(0xffffffffu, kidx, lane >> 2);
             const int row = 8 * pw + (lane >> 2);
             // rope bytes: compact 64-byte rows, 64-byte swizzle (16-byte unit ^ ((row / 2) % 4))
-            cp_async16_hint(kst + 4 * kChunkBytes + row * 64 + (((lane & 3) ^ ((row >> 1) & 3)) << 4),
-                       kvb + (size_t)ri * pitch + 512 + 16 * (lane & 3), pol_keep);
+            cp_async16(kst + 4 * kChunkBytes + row * 64 + (((lane & 3) ^ ((row >> 1) & 3)) << 4),
+                       kvb + (size_t)ri * pitch + 512 + 16 * (lane & 3));
           }
           cp_async_mbar_arrive_noinc(&ms.k_land[s]);
           cur_next(ck);
@@ -531,8 +531,8 @@ masked_mla_fp8_kernel(const __grid_constant__ CUtensorMap map_q,
             const int rloc = 2 * i + (lane >> 4);
             const int ri = __shfl_sync(0xffffffffu, vidx, 16 + rloc);
             const int row = 16 * pw + rloc;
-            cp_async16_hint(vst + nbk * kVChunk + row * 128 + ((c8 ^ (row & 7)) << 4),
-                       kvb + (size_t)ri * pitch + 256 * cta + 16 * pc, pol_keep);
+            cp_async16(vst + nbk * kVChunk + row * 128 + ((c8 ^ (row & 7)) << 4),
+                       kvb + (size_t)ri * pitch + 256 * cta + 16 * pc);
           }
           cp_async_mbar_arrive_noinc(&ms.v_land[s]);
           cur_next(cv);

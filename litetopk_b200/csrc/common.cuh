@@ -286,12 +286,15 @@ __device__ __forceinline__ uint64_t l2_policy_evict_last() {
   return pol;
 }
 
-// 16-byte asynchronous global -> shared copy (LSU path, any shared destination) with an L2
-// eviction hint, and below the asynchronous arrival that fires when all earlier cp.async of
-// the thread have landed (.noinc: the arrival counts against the barrier's expected count)
-__device__ __forceinline__ void cp_async16_hint(uint32_t dst_smem, const void* src, uint64_t pol) {
-  asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;"
-               ::"r"(dst_smem), "l"(src), "l"(pol) : "memory");
+// 16-byte asynchronous global -> shared copy (LSU path, any shared destination), and below the
+// asynchronous arrival that fires when all earlier cp.async of the thread have landed (.noinc:
+// the arrival counts against the barrier's expected count).  No L2 cache-policy operand on
+// purpose: with `.L2::cache_hint` the copy raised "illegal instruction" at its first execution
+// in several builds of the attention kernels that differed from a working build only in the
+// surrounding code of the gather warps (located with a per-warp progress log in pinned host
+// memory); without the operand the same builds run, bit-identical and at the same speed.
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
 }
 __device__ __forceinline__ void tma_store_2d_hint(const void* map, uint32_t src_smem, int x, int y,
                                                   uint64_t pol) {
