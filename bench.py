@@ -54,9 +54,9 @@ from litetopk_b200 import synth  # noqa: E402
 
 METRIC = "sparse_mla_prefill_query_tokens_per_s"
 # DRAM bytes per launch of masked_mla_fp8_kernel on the benchmark workload: ncu capture of the
-# kernel on 2048 tokens of config 1 (191.1 MB read + written), q / out / index part scaled x 4
-# ((191.1 - 18.9 MB of KV cache) x 4 + 18.9)
-ATTN_DRAM_TRAFFIC_BYTES = 708_000_000
+# kernel on 2048 tokens of config 1 (197.8 MB read + written), q / out / index part scaled x 4
+# ((197.8 - 18.9 MB of KV cache) x 4 + 18.9)
+ATTN_DRAM_TRAFFIC_BYTES = 735_000_000
 REF_SO = os.path.join(ROOT, "oracle", "_ref", "litedsa_ref.so")
 REF_DSV4_SO = os.path.join(ROOT, "oracle", "_ref", "litedsa_dsv4_ref.so")
 
