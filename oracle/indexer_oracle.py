@@ -3,14 +3,18 @@
 TEST INFRASTRUCTURE ONLY.  Nothing in the shipped package imports this file; it is the
 checker used by tests/ and by the benchmark's checks.
 
-Parity unpinned: the reference repository removed its indexer and top-k kernels
-("The repository-local LiteTopK indexer and standalone MS MARCO top-k kernels have been
-removed", README.md:3-6) and points to pull requests of other projects that are not
-part of it.  There is therefore no reference implementation, test or golden vector for
-these functions.  What pins them is (i) the published formulation of the DeepSeek-V3.2
-lightning indexer, restated below, and (ii) the consumer's contract: the result is the
-`topk_indices [T, k] i32` tensor with -1 padding that the reference's union operator
-takes (kernels/b200/dsa/litedsa.cu:31-33, kernels/b200/dsa/litedsa_union.cuh:63).
+Parity unpinned against the reference: its repository removed the indexer and top-k
+kernels ("The repository-local LiteTopK indexer and standalone MS MARCO top-k kernels have
+been removed", README.md:3-6) and points to pull requests of other projects that are not
+part of it, so the reference holds no implementation, test or golden vector for these
+functions.  What pins them instead: (i) the published formulation of the DeepSeek-V3.2
+lightning indexer, restated below; (ii) for the logits, golden vectors from an independent
+statement of that formulation, the pure-torch `fp8_mqa_logits_torch` of the vLLM package
+(tests/golden/make_indexer_golden.py -> tests/golden/golden_indexer.npz, checked by
+tests/test_indexer_cpu.py: exact where that function's bf16 arithmetic is exact, within its
+rounding elsewhere); (iii) the consumer's contract: the result is the `topk_indices [T, k]
+i32` tensor with -1 padding that the reference's union operator takes
+(kernels/b200/dsa/litedsa.cu:31-33, kernels/b200/dsa/litedsa_union.cuh:63).
 
     logit[t, s] = k_scale[s] * sum_h weights[t, h] * relu( q[t, h, :] . k[s, :] )
     topk[t]     = the k positions s <= q_pos0 + t with the largest logits

@@ -64,3 +64,29 @@ def test_entry_points_check_arguments_before_cuda(built_lib):
     assert g(None, None, p, 4, 16, 2, 0, 16, None) == _lib.ERR_ARG
     assert g(p, None, p, 4, 16, 0, 0, 16, None) == _lib.ERR_SHAPE
     assert g(p, None, p, 4, 16, 2, 0, 8, None) == _lib.ERR_SHAPE
+
+
+def test_index_logits_oracle_matches_an_independent_statement_of_the_indexer():
+    """tests/golden/golden_indexer.npz holds the outputs of vLLM's pure-torch
+    `fp8_mqa_logits_torch` (made by tests/golden/make_indexer_golden.py): the oracle's formula is
+    pinned to it, exactly where that function's bf16 arithmetic is exact, within its rounding
+    elsewhere."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "golden_indexer.npz"))
+    for name in ("exact", "random"):
+        q8 = torch.from_numpy(g[f"{name}_q8"]); k8 = torch.from_numpy(g[f"{name}_k8"])
+        w = torch.from_numpy(g[f"{name}_w"]); ks = torch.from_numpy(g[f"{name}_ks"])
+        q_pos0 = int(g[f"{name}_q_pos0"])
+        want = torch.from_numpy(g[f"{name}_logits"]).double()
+        got = io.index_logits(q8, k8, w, ks, q_pos0)
+        assert torch.equal(torch.isinf(got), torch.isinf(want))          # the same causal mask
+        fin = ~torch.isinf(want)
+        # magnitude each logit is a sum over: sum_h |w_h| |q_h . k| k_scale
+        qf = io.decode_e4m3(q8).double(); kf = io.decode_e4m3(k8).double()
+        mag = (torch.einsum("thd,sd->ths", qf, kf).abs() * w.double().abs()[:, :, None]).sum(1) * ks.double()[None, :]
+        err = (got - want).abs()[fin]
+        if name == "exact":
+            assert float((err / (mag[fin] + 1e-30)).max()) <= 1e-6       # fp32 head sum only
+        else:
+            assert float((err - 2.0 ** -8 * mag[fin]).max()) <= 1e-7     # bf16 rounding of each dot product
+        assert float(err.max()) > 0 or name == "exact"
