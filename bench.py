@@ -586,6 +586,40 @@ def indexer_record(api, w, dev, steps, fp8_peak, hbm_gbs, index_heads=64):
     return rec
 
 
+def deepgemm_index_logits(w, dev, steps, index_heads=64):
+    """DeepGEMM's FP8 MQA-logits kernel (the production kernel of the same operator, as shipped
+    inside the vLLM package of this image; library code, JIT-compiled on first use) on the
+    indexer record's operands: its time, and its agreement with the library's kernel."""
+    try:
+        import vllm.third_party.deep_gemm as dg
+        fn = dg.fp8_fp4_mqa_logits
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": f"DeepGEMM not importable ({type(e).__name__})"}
+    from litetopk_b200 import api
+    T, S = w.tokens, w.s_kv
+    pos0 = S - T
+    q8, k8, wts, ks = synth.make_indexer_operands(T, S, index_heads, seed=1, device=dev)
+    start = torch.zeros((T,), dtype=torch.int32, device=dev)
+    end = (pos0 + torch.arange(T, device=dev) + 1).to(torch.int32)
+    qf, kf = q8.view(torch.float8_e4m3fn), k8.view(torch.float8_e4m3fn)
+    call = lambda: fn((qf, None), (kf, ks), wts, start, end, clean_logits=True)  # noqa: E731
+    try:
+        ref = call()
+        torch.cuda.synchronize()
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": f"DeepGEMM kernel could not be built or run ({type(e).__name__})"}
+    ms = cuda_time(call, steps)
+    mine = api.index_logits_fp8(q8, k8, wts, ks, pos0)
+    fin = torch.isfinite(mine)
+    same_mask = bool(torch.equal(fin, torch.isfinite(ref[:, :S])))
+    diff = float((mine[fin] - ref[:, :S][fin]).abs().max()) if same_mask else None
+    rec = {"kernel": "DeepGEMM fp8_fp4_mqa_logits (vllm.third_party.deep_gemm)", "ms": ms,
+           "same_mask": same_mask, "max_abs_diff": diff, "max_abs_logit": float(mine[fin].abs().max())}
+    del q8, k8, wts, ks, ref, mine
+    torch.cuda.empty_cache()
+    return rec
+
+
 def merge_record(api, dev, steps, hbm_gbs, part_tiles=8192, div=2):
     """The lse merge of KV-split outputs (HBM-bound): `part_tiles` slices of 128 rows merged `div` to one."""
     o = torch.randn((part_tiles, 128, 512), device=dev).to(torch.bfloat16)
@@ -1029,6 +1063,12 @@ def main():
             run4.free()
     if world == 1:
         e2e_window()          # the second window, after everything else this run measures
+        if "indexer" in line:
+            # last, so that importing the other package cannot disturb any figure above
+            dgr = deepgemm_index_logits(synth.CONFIGS["c1"], dev, sec_steps)
+            if "ms" in dgr:
+                dgr["ratio"] = dgr["ms"] / line["indexer"]["logits_ms"]
+            line["indexer"]["deepgemm"] = dgr
     line["e2e"] = e2e_record()
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:

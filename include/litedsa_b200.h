@@ -364,9 +364,9 @@ int litedsa_masked_mla_fp8_kv656_noalloc(const void* q8, const void* kv656, cons
  *   k_idx8   [S, 128] e4m3 codes, rows k_row_stride bytes apart (multiple of 16)
  *   weights  [T, Hi] fp32 (head weight x query scale x softmax scale)
  *   k_scale  [S] fp32 or NULL (1.0)
- *   logits   [T, logits_row_stride] fp32.  Written: every s <= q_pos0 + t.  Entries beyond a
- *            token's position are -inf inside the key tiles its CTA processed and untouched
- *            beyond; litedsa_topk_select never reads them.
+ *   logits   [T, logits_row_stride] fp32.  All S entries of every row are written: the
+ *            logit for s <= q_pos0 + t, -inf beyond the token's position (litedsa_topk_select
+ *            never reads those).
  * Asynchronous on `stream`; bounded waits report through litedsa_index_status.
  */
 int litedsa_index_logits_fp8(const void* q_idx8, const void* k_idx8, const float* weights,

@@ -441,7 +441,7 @@ def index_logits_fp8(q_idx8: torch.Tensor, k_idx8: torch.Tensor, weights: torch.
 
     ``q_idx8`` [T, Hi, 128] and ``k_idx8`` [S, 128] hold e4m3 codes (uint8 or float8_e4m3fn),
     ``weights`` [T, Hi] fp32, ``k_scale`` [S] fp32 or None.  Entries beyond a token's position
-    are -inf or untouched (see include/litedsa_b200.h); ``topk_select`` never reads them.
+    are written as -inf (``topk_select`` never reads them).
     """
     for t, n in ((q_idx8, "q_idx8"), (k_idx8, "k_idx8")):
         if not t.is_cuda or t.element_size() != 1:

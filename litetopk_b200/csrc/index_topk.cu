@@ -175,6 +175,19 @@ index_logits_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const float* w = wsm + a * kCols + 128 * hf;
     constexpr int tph = tpa / 2;                        // tokens per column half
     const int t_base = tok0 + a * tpa + hf * tph;
+    // Key tiles beyond the causal bound of the CTA's last token are not computed: their entries
+    // are -inf for every token of the CTA (this warp's tokens and key rows).  Written first,
+    // while the tensor core fills the first accumulators.
+    for (int j = n_tiles; j * kKeyTile < p.S; ++j) {
+      const int s_key = j * kKeyTile + krow;
+      if (s_key < p.S) {
+#pragma unroll
+        for (int tt = 0; tt < tph; ++tt) {
+          const int t = t_base + tt;
+          if (t < p.T) p.logits[(long long)t * p.ld + s_key] = -INFINITY;
+        }
+      }
+    }
     for (int j = 0; j < n_tiles; ++j) {
       // this key's scale is fetched before the wait, so its latency hides behind the MMAs
       const int s_key = j * kKeyTile + krow;

@@ -51,6 +51,37 @@ def test_index_logits_match_the_formula(T, S, Hi, pos0):
     err = (got[valid] - ref[valid]).abs().max().item()
     # fp32 accumulation of 64..128 exact products per head and of Hi weighted terms
     assert err <= 2e-6 * scale * Hi ** 0.5, (err, scale)
+    # every entry beyond a token's position is written as -inf, key tiles that no CTA computes included
+    assert bool(torch.isinf(got[~valid]).all()) and bool((got[~valid] < 0).all())
+
+
+def test_index_logits_agree_with_the_deepgemm_kernel():
+    # an independent production kernel of the same operator: DeepGEMM's fp8 MQA logits as shipped
+    # inside the vLLM package of this image (JIT-compiled on first use); skipped where it is absent
+    try:
+        import vllm.third_party.deep_gemm as dg
+        fn = dg.fp8_fp4_mqa_logits
+    except Exception as e:  # noqa: BLE001
+        pytest.skip(f"DeepGEMM not available ({type(e).__name__})")
+    T, S, Hi = 512, 4096, 64
+    pos0 = S - T
+    q8, k8, w, ks = [t.to(DEV) for t in _ops(T, S, Hi, seed=77)]
+    start = torch.zeros((T,), dtype=torch.int32, device=DEV)
+    end = (pos0 + torch.arange(T, device=DEV) + 1).to(torch.int32)
+    try:
+        ref = fn((q8.view(torch.float8_e4m3fn), None), (k8.view(torch.float8_e4m3fn), ks), w, start, end,
+                 clean_logits=True)
+        torch.cuda.synchronize()
+    except Exception as e:  # noqa: BLE001
+        pytest.skip(f"DeepGEMM kernel could not be built or run here ({type(e).__name__})")
+    got = api.index_logits_fp8(q8, k8, w, ks, pos0)
+    torch.cuda.synchronize()
+    assert api.index_status(reset=True)[0] == 0
+    ref = ref[:, :S]
+    assert torch.equal(torch.isfinite(got), torch.isfinite(ref))       # the same causal mask, -inf outside
+    fin = torch.isfinite(got)
+    scale = float(got[fin].abs().max())
+    assert float((got[fin] - ref[fin]).abs().max()) <= 2e-6 * scale    # both accumulate in fp32
 
 
 def test_index_logits_without_key_scales_and_strided_keys():
