@@ -620,6 +620,43 @@ def deepgemm_index_logits(w, dev, steps, index_heads=64):
     return rec
 
 
+def vllm_topk_per_row(w, dev, steps, index_heads=64):
+    """vLLM's top_k_per_row_prefill (the selection its DeepSeek-V3.2 indexer uses; library code,
+    precompiled in the package of this image) on the indexer record's logits: its time and its
+    agreement with the library's topk_select."""
+    try:
+        from vllm import _custom_ops as ops
+        fn = ops.top_k_per_row_prefill
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": f"vLLM custom ops not importable ({type(e).__name__})"}
+    from litetopk_b200 import api
+    T, S, k = w.tokens, w.s_kv, w.topk
+    pos0 = S - T
+    q8, k8, wts, ks = synth.make_indexer_operands(T, S, index_heads, seed=1, device=dev)
+    logits = api.index_logits_fp8(q8, k8, wts, ks, pos0)
+    del q8, k8, wts, ks
+    start = torch.zeros((T,), dtype=torch.int32, device=dev)
+    end = (pos0 + torch.arange(T, device=dev) + 1).to(torch.int32)
+    ref = torch.full((T, k), -1, dtype=torch.int32, device=dev)
+    call = lambda: fn(logits, start, end, ref, T, logits.stride(0), logits.stride(1), k)  # noqa: E731
+    try:
+        call()
+        torch.cuda.synchronize()
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": f"vLLM top_k_per_row_prefill could not run ({type(e).__name__})"}
+    ms = cuda_time(call, steps)
+    mine = api.topk_select(logits, k, q_pos0=pos0)
+    vg = torch.sort(torch.gather(logits, 1, mine.clamp_min(0).long()), dim=1).values
+    vr = torch.sort(torch.gather(logits, 1, ref.clamp_min(0).long()), dim=1).values
+    rows_diff = int((torch.sort(mine, dim=1).values != torch.sort(ref, dim=1).values).any(dim=1).sum())
+    rec = {"kernel": "vLLM top_k_per_row_prefill", "ms": ms, "same_selected_values": bool(torch.equal(vg, vr)),
+           "rows_with_other_positions": rows_diff,
+           "note": "rows differ only where the k-th value is tied (the values selected are the same)"}
+    del logits, ref, mine, vg, vr
+    torch.cuda.empty_cache()
+    return rec
+
+
 def merge_record(api, dev, steps, hbm_gbs, part_tiles=8192, div=2):
     """The lse merge of KV-split outputs (HBM-bound): `part_tiles` slices of 128 rows merged `div` to one."""
     o = torch.randn((part_tiles, 128, 512), device=dev).to(torch.bfloat16)
@@ -1069,6 +1106,10 @@ def main():
             if "ms" in dgr:
                 dgr["ratio"] = dgr["ms"] / line["indexer"]["logits_ms"]
             line["indexer"]["deepgemm"] = dgr
+            vtr = vllm_topk_per_row(synth.CONFIGS["c1"], dev, sec_steps)
+            if "ms" in vtr:
+                vtr["ratio"] = vtr["ms"] / line["indexer"]["select_ms"]
+            line["indexer"]["vllm_topk"] = vtr
     line["e2e"] = e2e_record()
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:

@@ -12,7 +12,8 @@ lightning indexer, restated below; (ii) for the logits, golden vectors from an i
 statement of that formulation, the pure-torch `fp8_mqa_logits_torch` of the vLLM package
 (tests/golden/make_indexer_golden.py -> tests/golden/golden_indexer.npz, checked by
 tests/test_indexer_cpu.py: exact where that function's bf16 arithmetic is exact, within its
-rounding elsewhere); (iii) the consumer's contract: the result is the `topk_indices [T, k]
+rounding elsewhere; on a GPU the kernels are also compared with DeepGEMM's logits kernel and
+vLLM's top-k-per-row kernel, tests/test_indexer_gpu.py); (iii) the consumer's contract: the result is the `topk_indices [T, k]
 i32` tensor with -1 padding that the reference's union operator takes
 (kernels/b200/dsa/litedsa.cu:31-33, kernels/b200/dsa/litedsa_union.cuh:63).
 

@@ -95,6 +95,38 @@ def test_index_logits_without_key_scales_and_strided_keys():
     assert (got[valid] - ref[valid]).abs().max().item() <= 2e-5 * ref[valid].abs().max().item()
 
 
+def test_topk_select_agrees_with_the_vllm_kernel():
+    # vLLM's top_k_per_row_prefill (the selection its DeepSeek-V3.2 indexer uses; precompiled in the
+    # package of this image) on the same logits: the same k values per row, and the same
+    # positions wherever the k-th value is not tied; skipped where the operator is absent
+    try:
+        from vllm import _custom_ops as ops
+        fn = ops.top_k_per_row_prefill
+    except Exception as e:  # noqa: BLE001
+        pytest.skip(f"vLLM custom ops not available ({type(e).__name__})")
+    T, S, k, pos0 = 96, 8192, 2048, 8000
+    x = _random_logits(T, S, seed=123).to(DEV)
+    start = torch.zeros((T,), dtype=torch.int32, device=DEV)
+    end = torch.clamp(pos0 + torch.arange(T, device=DEV) + 1, max=S).to(torch.int32)
+    ref = torch.full((T, k), -1, dtype=torch.int32, device=DEV)
+    try:
+        fn(x, start, end, ref, T, x.stride(0), x.stride(1), k)
+        torch.cuda.synchronize()
+    except Exception as e:  # noqa: BLE001
+        pytest.skip(f"vLLM top_k_per_row_prefill could not run here ({type(e).__name__})")
+    got = api.topk_select(x, k, q_pos0=pos0)
+    torch.cuda.synchronize()
+    assert api.index_status(reset=True)[0] == 0
+    assert bool((got >= 0).all()) and bool((ref >= 0).all())          # every row is longer than k
+    vg = torch.sort(torch.gather(x, 1, got.long()), dim=1).values
+    vr = torch.sort(torch.gather(x, 1, ref.long()), dim=1).values
+    assert torch.equal(vg, vr)
+    untied = vg[:, 0] != torch.sort(x.masked_fill(torch.arange(S, device=DEV)[None, :] >= end[:, None].long(),
+                                                  float("-inf")), dim=1, descending=True).values[:, k]
+    assert torch.equal(torch.sort(got, dim=1).values[untied], torch.sort(ref, dim=1).values[untied])
+    assert int(untied.sum()) > T // 2
+
+
 def _random_logits(T, S, seed, levels=None):
     g = torch.Generator().manual_seed(seed)
     x = torch.randn((T, S), generator=g)
