@@ -20,6 +20,7 @@ The ONE JSON line rank 0 prints carries, beside the headline contract keys:
   native          config 1 on a cache whose per-128 scales differ, bf16 q (the bf16 route)
   indexer         the step before: FP8 index logits + exact top-k selection on the config-1 shape
   merge_kv_splits the lse merge of KV-split outputs (HBM-bound)
+  stock_sparse_mla the stock per-token sparse MLA prefill (FlashMLA, library code) on configs 1, 2, 4
   c4_strong       config 4 split over the N ranks (strong scaling) with its all-gather
   e2e             through api.sparse_prefill_host with pinned host buffers and bf16 queries:
                   median step of a window, the better of two windows (both arms alike; the
@@ -657,6 +658,50 @@ def vllm_topk_per_row(w, dev, steps, index_heads=64):
     return rec
 
 
+def stock_sparse_mla(w, dev, steps):
+    """The stock per-token sparse MLA prefill (FlashMLA's sparse_prefill_fwd as shipped inside the
+    vLLM package of this image; library code, bf16, no union / grouping) on a configuration's
+    operands: the attention the reference's method replaces.  It takes 64 or 128 query heads, so
+    configurations with fewer heads are padded with zero heads the way a tensor-parallel caller
+    of the stock kernel pads them.  Also compares its output with the library's path."""
+    try:
+        from vllm.third_party.flashmla.flash_mla_interface import flash_mla_sparse_fwd
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": f"FlashMLA not importable ({type(e).__name__})"}
+    from litetopk_b200 import api
+    idx = synth.make_topk(w, seed=1, device=dev)
+    kv = synth.make_kv_cache(w.s_kv, seed=1, device=dev, mode="refcompat")
+    q = synth.make_q(w.tokens, w.heads, seed=1, device=dev, mode="refcompat")
+    q8, kv8, qs, ks = synth.refcompat_operands(q, kv)
+    del q, kv
+    kv_bf16 = (kv8.view(torch.float8_e4m3fn).float() * ks).to(torch.bfloat16).view(w.s_kv, 1, 576)
+    heads_run = max(64, w.heads)
+    q_bf16 = torch.zeros((w.tokens, heads_run, 576), dtype=torch.bfloat16, device=dev)
+    q_bf16[:, :w.heads] = (q8.view(torch.float8_e4m3fn).float() * qs).to(torch.bfloat16).view(w.tokens, w.heads, 576)
+    ind = idx.view(w.tokens, 1, w.topk).contiguous()
+    call = lambda: flash_mla_sparse_fwd(q_bf16, kv_bf16, ind, float(synth.SM_SCALE))  # noqa: E731
+    try:
+        o_ref, _, lse_ref = call()
+        torch.cuda.synchronize()
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": f"FlashMLA sparse prefill could not run ({type(e).__name__}: {str(e)[:80]})"}
+    ms = cuda_time(call, steps)
+    q8v = q8.view(w.tokens, w.heads, 576)
+    ours = lambda: api.sparse_prefill(q8v, kv8, idx, synth.SM_SCALE, kv_scale=ks, q_scale=qs, seq_space=w.s_kv)  # noqa: E731
+    out, lse = ours()
+    ours_ms = cuda_time(ours, steps)
+    a, b = out.float().flatten(), o_ref[:, :w.heads].float().flatten()
+    rec = {"kernel": "FlashMLA sparse_prefill_fwd (vllm.third_party.flashmla), bf16, per-token lists",
+           "heads_run": heads_run, "ms": ms, "ours_ms": ours_ms, "ratio": ms / ours_ms,
+           "out_cosine": float(torch.nn.functional.cosine_similarity(a, b, dim=0)),
+           "out_max_abs_diff": float((a - b).abs().max()),
+           "lse_max_abs_diff": float((lse - lse_ref[:, :w.heads]).abs().max()),
+           "note": "ours = union_qm + masked_mla_fp8 (e4m3 P): cosine ~0.9998 against a bf16 kernel is its quantisation"}
+    del idx, q8, kv8, kv_bf16, q_bf16, ind, o_ref, lse_ref, out, lse
+    torch.cuda.empty_cache()
+    return rec
+
+
 def merge_record(api, dev, steps, hbm_gbs, part_tiles=8192, div=2):
     """The lse merge of KV-split outputs (HBM-bound): `part_tiles` slices of 128 rows merged `div` to one."""
     o = torch.randn((part_tiles, 128, 512), device=dev).to(torch.bfloat16)
@@ -1110,6 +1155,8 @@ def main():
             if "ms" in vtr:
                 vtr["ratio"] = vtr["ms"] / line["indexer"]["select_ms"]
             line["indexer"]["vllm_topk"] = vtr
+        if extras:
+            line["stock_sparse_mla"] = {c: stock_sparse_mla(synth.CONFIGS[c], dev, sec_steps) for c in ("c1", "c2", "c4")}
     line["e2e"] = e2e_record()
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:

@@ -417,3 +417,30 @@ def test_out_operators_replay_from_a_cuda_graph():
         torch.cuda.synchronize()
         assert torch.equal(out, want[0]) and torch.equal(lse, want[1])
     assert api.attn_status()[0] == 0
+
+
+def test_path_agrees_with_the_stock_per_token_sparse_mla_kernel():
+    # FlashMLA's sparse prefill (bf16, every token attends its own top-k list; shipped inside the
+    # vLLM package of this image) computes the semantics that union_qm + masked_mla_fp8 restate
+    # with a per-tile union and a membership mask; skipped where that kernel is absent
+    try:
+        from vllm.third_party.flashmla.flash_mla_interface import flash_mla_sparse_fwd
+    except Exception as e:  # noqa: BLE001
+        pytest.skip(f"FlashMLA not available ({type(e).__name__})")
+    w, idx, kv, q = _case(256, 64, 512, 4096, (0.8, 0.8), seed=33)
+    q8, kv8, qs, ks = synth.refcompat_operands(q, kv)
+    kv_bf16 = (kv8.view(torch.float8_e4m3fn).float() * ks).to(torch.bfloat16).view(w.s_kv, 1, 576).to(DEV)
+    q_bf16 = (q8.view(torch.float8_e4m3fn).float() * qs).to(torch.bfloat16).view(w.tokens, w.heads, 576).to(DEV)
+    ind = idx.view(w.tokens, 1, w.topk).contiguous().to(DEV)
+    try:
+        o_ref, ml_ref, lse_ref = flash_mla_sparse_fwd(q_bf16, kv_bf16, ind, float(synth.SM_SCALE))
+        torch.cuda.synchronize()
+    except Exception as e:  # noqa: BLE001
+        pytest.skip(f"FlashMLA sparse prefill could not run here ({type(e).__name__})")
+    out, lse = api.sparse_prefill(q8.view(w.tokens, w.heads, 576).to(DEV), kv8.to(DEV), idx.to(DEV), synth.SM_SCALE,
+                                  kv_scale=ks, q_scale=qs, seq_space=w.s_kv)
+    torch.cuda.synchronize()
+    mad, cos = ao.compare(out.cpu(), o_ref.float().cpu())
+    assert cos >= 0.9995, (mad, cos)                     # e4m3 P against a bf16 kernel
+    assert float((lse - lse_ref).abs().max()) <= TOL_LSE
+    assert api.attn_status()[0] == 0
