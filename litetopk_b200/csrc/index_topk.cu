@@ -196,17 +196,17 @@ index_logits_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       __syncwarp();
       tc_fence_after();
       float acc[tph];
-#pragma unroll
-      for (int i = 0; i < tph; ++i) acc[i] = 0.f;
       float x[2][32];
       tmem_ld32(tcol, x[0]);
+      // two packed fma chains (four independent partial sums), carried over the 32-column chunks
+      // of one token and folded when the token's last chunk is done (a chunk never straddles two
+      // tokens)
+      float2 s0 = make_float2(0.f, 0.f), s1 = make_float2(0.f, 0.f);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         tmem_wait_ld();
         if (c < 3) tmem_ld32(tcol + 32 * (c + 1), x[(c + 1) & 1]);
         const float* xc = x[c & 1];
-        // two packed fma chains (four independent partial sums) per 32 columns
-        float2 s0 = make_float2(0.f, 0.f), s1 = make_float2(0.f, 0.f);
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
           const float4 w4 = *reinterpret_cast<const float4*>(w + 32 * c + i);
@@ -214,7 +214,11 @@ index_logits_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           s1 = fma2(make_float2(xc[i + 2] + fabsf(xc[i + 2]), xc[i + 3] + fabsf(xc[i + 3])),
                     make_float2(w4.z, w4.w), s1);
         }
-        acc[(32 * c) / HI] += (s0.x + s0.y) + (s1.x + s1.y);   // a chunk never straddles two tokens
+        if ((32 * (c + 1)) % HI == 0 || c == 3) {
+          acc[(32 * c) / HI] = (s0.x + s0.y) + (s1.x + s1.y);
+          s0 = make_float2(0.f, 0.f);
+          s1 = make_float2(0.f, 0.f);
+        }
       }
       tc_fence_before();
       __syncwarp();
